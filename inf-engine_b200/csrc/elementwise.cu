@@ -1,0 +1,209 @@
+// Embedding gather, RMSNorm fused with the residual sum, rotary position
+// encoding fused with the write of keys and values into cache pages, and
+// SiLU(gate) * up.  Statistics, angles and sums are float32 whatever the
+// activation type is.
+#include "common.cuh"
+
+// ------------------------------------------------------------------ embedding
+// residual[n, :] = table[ids[n], :]  (the reference gathers rows without
+// scaling, engine/llama_model.py:128).  The residual stream is float32.
+template <typename TW>
+__global__ void embed_gather_kernel(const int* __restrict__ ids, const TW* __restrict__ table,
+                                    float* __restrict__ residual, int d, int vocab) {
+  const int n = blockIdx.x;
+  int id = ids[n];
+  const bool ok = id >= 0 && id < vocab;
+  const TW* row = table + (size_t)(ok ? id : 0) * d;
+  float* out = residual + (size_t)n * d;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) out[i] = ok ? to_f32(row[i]) : 0.f;
+}
+
+extern "C" int ie_embed_gather(const int* ids, const void* table, int table_dtype, float* residual,
+                               int n_tokens, int d, int vocab, cudaStream_t stream) {
+  if (n_tokens <= 0) return IE_OK;
+  const int threads = d >= 1024 ? 256 : 128;
+  if (table_dtype == IE_F32)
+    embed_gather_kernel<float><<<n_tokens, threads, 0, stream>>>(ids, (const float*)table, residual, d, vocab);
+  else if (table_dtype == IE_BF16)
+    embed_gather_kernel<bf16><<<n_tokens, threads, 0, stream>>>(ids, (const bf16*)table, residual, d, vocab);
+  else
+    return IE_BAD_DTYPE;
+  return launch_status();
+}
+
+// -------------------------------------------------------------------- RMSNorm
+// x = residual[row] (+ delta[row]);  residual[row] = x (unless rows are gathered);
+// out[m] = x / sqrt(mean(x^2) + eps) * gain          (engine/layers.py:24-25)
+// One block per output row; x is staged in shared memory between the two passes.
+template <typename TA, typename TW>
+__global__ void rmsnorm_kernel(float* __restrict__ residual, const TA* __restrict__ delta,
+                               const TW* __restrict__ gain, TA* __restrict__ out,
+                               const int* __restrict__ row_index, int d, float eps) {
+  extern __shared__ float xs[];
+  __shared__ float red[33];
+  const int m = blockIdx.x;
+  const int row = row_index ? row_index[m] : m;
+  float* res = residual + (size_t)row * d;
+  const TA* del = delta ? delta + (size_t)row * d : nullptr;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    float x = res[i];
+    if (del) x += to_f32(del[i]);
+    xs[i] = x;
+    ss += x * x;
+    if (del && !row_index) res[i] = x;
+  }
+  const float total = block_sum(ss, red);
+  const float rms = sqrtf(total / (float)d + eps);
+  TA* o = out + (size_t)m * d;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = from_f32<TA>((xs[i] / rms) * to_f32(gain[i]));
+}
+
+template <typename TA, typename TW>
+static int launch_rmsnorm(float* residual, const void* delta, const void* gain, void* out, const int* row_index,
+                          int n_rows, int d, float eps, cudaStream_t stream) {
+  const size_t smem = (size_t)d * sizeof(float);
+  if (smem > 200 * 1024) return IE_BAD_SIZE;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(rmsnorm_kernel<TA, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  const int threads = d >= 2048 ? 512 : (d >= 512 ? 256 : 128);
+  rmsnorm_kernel<TA, TW><<<n_rows, threads, smem, stream>>>(residual, (const TA*)delta, (const TW*)gain, (TA*)out,
+                                                             row_index, d, eps);
+  return launch_status();
+}
+
+extern "C" int ie_rmsnorm(float* residual, const void* delta, const void* gain, int gain_dtype, void* out,
+                          int act_dtype, const int* row_index, int n_rows, int d, float eps, cudaStream_t stream) {
+  if (n_rows <= 0) return IE_OK;
+  if (act_dtype == IE_F32 && gain_dtype == IE_F32)
+    return launch_rmsnorm<float, float>(residual, delta, gain, out, row_index, n_rows, d, eps, stream);
+  if (act_dtype == IE_F32 && gain_dtype == IE_BF16)
+    return launch_rmsnorm<float, bf16>(residual, delta, gain, out, row_index, n_rows, d, eps, stream);
+  if (act_dtype == IE_BF16 && gain_dtype == IE_F32)
+    return launch_rmsnorm<bf16, float>(residual, delta, gain, out, row_index, n_rows, d, eps, stream);
+  if (act_dtype == IE_BF16 && gain_dtype == IE_BF16)
+    return launch_rmsnorm<bf16, bf16>(residual, delta, gain, out, row_index, n_rows, d, eps, stream);
+  return IE_BAD_DTYPE;
+}
+
+// residual[n, :] += delta[n, :]   (for a block arrangement that has no norm to fuse the sum into)
+template <typename TA>
+__global__ void residual_add_kernel(float* __restrict__ residual, const TA* __restrict__ delta, size_t n) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) residual[i] += to_f32(delta[i]);
+}
+extern "C" int ie_residual_add(float* residual, const void* delta, int act_dtype, int n_rows, int d,
+                               cudaStream_t stream) {
+  const size_t n = (size_t)n_rows * d;
+  if (n == 0) return IE_OK;
+  const unsigned blocks = (unsigned)((n + 255) / 256);
+  if (act_dtype == IE_F32)
+    residual_add_kernel<float><<<blocks, 256, 0, stream>>>(residual, (const float*)delta, n);
+  else if (act_dtype == IE_BF16)
+    residual_add_kernel<bf16><<<blocks, 256, 0, stream>>>(residual, (const bf16*)delta, n);
+  else
+    return IE_BAD_DTYPE;
+  return launch_status();
+}
+
+// ------------------------------------------------- rotary encoding + cache write
+// For token n at position p:  q and k heads are rotated pairwise over (i, i+hd/2)
+//   x'[i]      = x[i]*cos[p,i] - x[i+hd/2]*sin[p,i]
+//   x'[i+hd/2] = x[i+hd/2]*cos[p,i] + x[i]*sin[p,i]          (engine/layers.py:82-115)
+// q is rotated in place; the rotated k and the raw v go to the page slot
+// slot_mapping[n] = page*page_size + offset of pools laid out
+// [page, kv_head, page_size, head_dim]  (engine/paged_cache.py:119-123, 207-220).
+// cos/sin are float32 [max_positions, hd/2]; a null table means no rotation.
+// A negative slot (a padding token) writes nothing to the cache.
+template <typename TA>
+__global__ void rope_kv_write_kernel(TA* __restrict__ q, const TA* __restrict__ k, const TA* __restrict__ v,
+                                     int q_stride, int kv_stride, const float* __restrict__ cos_t,
+                                     const float* __restrict__ sin_t, const int* __restrict__ positions,
+                                     const int* __restrict__ slot_mapping, TA* __restrict__ kpool,
+                                     TA* __restrict__ vpool, int n_heads, int n_kv_heads, int hd, int page_size,
+                                     int write_kv) {
+  const int n = blockIdx.x;
+  const int half = hd >> 1;
+  const int pos = positions[n];
+  const float* c = cos_t ? cos_t + (size_t)pos * half : nullptr;
+  const float* s = sin_t ? sin_t + (size_t)pos * half : nullptr;
+  TA* qrow = q + (size_t)n * q_stride;
+  for (int idx = threadIdx.x; idx < n_heads * half; idx += blockDim.x) {
+    const int h = idx / half, i = idx - h * half;
+    TA* x = qrow + h * hd;
+    const float a = to_f32(x[i]), b = to_f32(x[i + half]);
+    const float cc = c ? c[i] : 1.f, ss = s ? s[i] : 0.f;
+    x[i] = from_f32<TA>(a * cc - b * ss);
+    x[i + half] = from_f32<TA>(b * cc + a * ss);
+  }
+  if (!write_kv) return;
+  const int slot = slot_mapping[n];
+  if (slot < 0) return;
+  const int page = slot / page_size, off = slot - page * page_size;
+  const TA* krow = k + (size_t)n * kv_stride;
+  const TA* vrow = v + (size_t)n * kv_stride;
+  for (int idx = threadIdx.x; idx < n_kv_heads * half; idx += blockDim.x) {
+    const int h = idx / half, i = idx - h * half;
+    const size_t base = (((size_t)page * n_kv_heads + h) * page_size + off) * hd;
+    const float a = to_f32(krow[h * hd + i]), b = to_f32(krow[h * hd + i + half]);
+    const float cc = c ? c[i] : 1.f, ss = s ? s[i] : 0.f;
+    kpool[base + i] = from_f32<TA>(a * cc - b * ss);
+    kpool[base + i + half] = from_f32<TA>(b * cc + a * ss);
+    vpool[base + i] = vrow[h * hd + i];
+    vpool[base + i + half] = vrow[h * hd + i + half];
+  }
+}
+
+extern "C" int ie_rope_kv_write(void* q, const void* k, const void* v, int q_stride, int kv_stride,
+                                const float* cos_t, const float* sin_t, const int* positions,
+                                const int* slot_mapping, void* kpool, void* vpool, int n_tokens, int n_heads,
+                                int n_kv_heads, int hd, int page_size, int write_kv, int act_dtype,
+                                cudaStream_t stream) {
+  if (n_tokens <= 0) return IE_OK;
+  if (hd % 2) return IE_BAD_SIZE;
+  const int work = n_heads * hd / 2;
+  const int threads = work >= 512 ? 256 : 128;
+  if (act_dtype == IE_F32)
+    rope_kv_write_kernel<float><<<n_tokens, threads, 0, stream>>>(
+        (float*)q, (const float*)k, (const float*)v, q_stride, kv_stride, cos_t, sin_t, positions, slot_mapping,
+        (float*)kpool, (float*)vpool, n_heads, n_kv_heads, hd, page_size, write_kv);
+  else if (act_dtype == IE_BF16)
+    rope_kv_write_kernel<bf16><<<n_tokens, threads, 0, stream>>>(
+        (bf16*)q, (const bf16*)k, (const bf16*)v, q_stride, kv_stride, cos_t, sin_t, positions, slot_mapping,
+        (bf16*)kpool, (bf16*)vpool, n_heads, n_kv_heads, hd, page_size, write_kv);
+  else
+    return IE_BAD_DTYPE;
+  return launch_status();
+}
+
+// ---------------------------------------------------------------- SiLU(gate)*up
+// in is [n, 2*inter] with gate in columns [0, inter) and up in [inter, 2*inter);
+// out[n, j] = gate*sigmoid(gate) * up          (engine/llama_mlp.py:32, engine/layers.py:28-30)
+template <typename TA>
+__global__ void silu_mul_kernel(const TA* __restrict__ in, TA* __restrict__ out, int inter, int in_stride,
+                                size_t total) {
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const size_t n = idx / inter;
+  const int j = (int)(idx - n * inter);
+  const float g = to_f32(in[n * in_stride + j]);
+  const float u = to_f32(in[n * in_stride + inter + j]);
+  const float sg = 1.f / (1.f + expf(-g));
+  out[idx] = from_f32<TA>((g * sg) * u);
+}
+
+extern "C" int ie_silu_mul(const void* in, void* out, int n_rows, int inter, int in_stride, int act_dtype,
+                           cudaStream_t stream) {
+  const size_t total = (size_t)n_rows * inter;
+  if (total == 0) return IE_OK;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  if (act_dtype == IE_F32)
+    silu_mul_kernel<float><<<blocks, 256, 0, stream>>>((const float*)in, (float*)out, inter, in_stride, total);
+  else if (act_dtype == IE_BF16)
+    silu_mul_kernel<bf16><<<blocks, 256, 0, stream>>>((const bf16*)in, (bf16*)out, inter, in_stride, total);
+  else
+    return IE_BAD_DTYPE;
+  return launch_status();
+}

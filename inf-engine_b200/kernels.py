@@ -1,0 +1,177 @@
+"""Python face of the CUDA kernels: checks tensors, passes pointers and the
+current stream to the ``extern "C"`` launchers, and raises on a refusal.
+
+Nothing here computes on the host and nothing falls back: a CPU tensor or a
+missing library is an error.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+import torch
+
+from .csrc.build import load_library
+
+IE_F32, IE_BF16 = 0, 1
+_CODES = {torch.float32: IE_F32, torch.bfloat16: IE_BF16}
+_ERRORS = {-1: "unsupported dtype combination", -2: "unsupported size", -3: "misaligned pointer or stride",
+           -4: "size beyond the kernel's static limit"}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    try:
+        return _CODES[dtype]
+    except KeyError:
+        raise KernelError(f"kernels take float32 and bfloat16, not {dtype}") from None
+
+
+def _check(status: int, what: str) -> None:
+    if status == 0:
+        return
+    if status < 0:
+        raise KernelError(f"{what}: refused ({_ERRORS.get(status, status)})")
+    raise KernelError(f"{what}: CUDA error {status} at launch")
+
+
+def _ptr(t: torch.Tensor | None) -> int | None:
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise KernelError("kernels run on CUDA tensors only; there is no CPU path")
+    return t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+_core = None
+
+
+def core():
+    global _core
+    if _core is None:
+        lib = load_library("core")
+        P, I, F, L = c_void_p, c_int, c_float, c_longlong
+        lib.ie_embed_gather.argtypes = [P, P, I, P, I, I, I, P]
+        lib.ie_rmsnorm.argtypes = [P, P, P, I, P, I, P, I, I, F, P]
+        lib.ie_residual_add.argtypes = [P, P, I, I, I, P]
+        lib.ie_rope_kv_write.argtypes = [P, P, P, I, I, P, P, P, P, P, P, I, I, I, I, I, I, I, P]
+        lib.ie_silu_mul.argtypes = [P, P, I, I, I, I, P]
+        lib.ie_attention_general.argtypes = [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P]
+        lib.ie_gemm_simt.argtypes = [P, I, P, I, P, I, I, I, I, I, I, I, P]
+        lib.ie_argmax.argtypes = [P, P, I, I, L, P]
+        lib.ie_repetition_penalty.argtypes = [P, P, P, I, I, L, I, P]
+        lib.ie_sample.argtypes = [P, P, P, I, I, L, P]
+        for name in ("ie_embed_gather", "ie_rmsnorm", "ie_residual_add", "ie_rope_kv_write", "ie_silu_mul",
+                     "ie_attention_general", "ie_gemm_simt", "ie_argmax", "ie_repetition_penalty", "ie_sample"):
+            getattr(lib, name).restype = c_int
+        _core = lib
+    return _core
+
+
+# ------------------------------------------------------------------ elementwise
+def embed_gather(ids: torch.Tensor, table: torch.Tensor, residual: torch.Tensor) -> None:
+    """residual[n] = table[ids[n]] as float32."""
+    assert ids.dtype == torch.int32 and residual.dtype == torch.float32 and table.is_contiguous()
+    n, d = residual.shape
+    _check(core().ie_embed_gather(_ptr(ids), _ptr(table), dtype_code(table.dtype), _ptr(residual), n, d,
+                                  table.shape[0], _stream()), "embed_gather")
+
+
+def rmsnorm(residual: torch.Tensor, delta: torch.Tensor | None, gain: torch.Tensor, out: torch.Tensor,
+            eps: float, row_index: torch.Tensor | None = None) -> None:
+    """out = rmsnorm(residual (+ delta)) * gain; residual takes the sum unless rows are gathered."""
+    d = residual.shape[-1]
+    n_rows = out.shape[0]
+    assert residual.dtype == torch.float32 and residual.is_contiguous() and out.is_contiguous()
+    assert delta is None or (delta.dtype == out.dtype and delta.is_contiguous() and delta.shape == residual.shape)
+    assert gain.shape == (d,) and out.shape[1] == d
+    _check(core().ie_rmsnorm(_ptr(residual), _ptr(delta), _ptr(gain), dtype_code(gain.dtype), _ptr(out),
+                             dtype_code(out.dtype), _ptr(row_index), n_rows, d, float(eps), _stream()), "rmsnorm")
+
+
+def residual_add(residual: torch.Tensor, delta: torch.Tensor) -> None:
+    n, d = residual.shape
+    _check(core().ie_residual_add(_ptr(residual), _ptr(delta), dtype_code(delta.dtype), n, d, _stream()),
+           "residual_add")
+
+
+def rope_kv_write(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cos: torch.Tensor | None,
+                  sin: torch.Tensor | None, positions: torch.Tensor, slot_mapping: torch.Tensor | None,
+                  kpool: torch.Tensor | None, vpool: torch.Tensor | None, n_heads: int, n_kv_heads: int,
+                  head_dim: int, page_size: int) -> None:
+    """Rotate q in place; write rotated k and raw v into their page slots (if pools are given).
+
+    q, k, v are row-strided views [n, heads*head_dim] (columns of one fused buffer, for instance).
+    """
+    n = q.shape[0]
+    assert q.stride(1) == 1 and k.stride(1) == 1 and v.stride(1) == 1 and k.stride(0) == v.stride(0)
+    write = kpool is not None
+    _check(core().ie_rope_kv_write(_ptr(q), _ptr(k), _ptr(v), q.stride(0), k.stride(0), _ptr(cos), _ptr(sin),
+                                   _ptr(positions), _ptr(slot_mapping), _ptr(kpool), _ptr(vpool), n, n_heads,
+                                   n_kv_heads, head_dim, page_size, 1 if write else 0, dtype_code(q.dtype),
+                                   _stream()), "rope_kv_write")
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    n, inter = out.shape
+    assert gate_up.shape == (n, 2 * inter) and gate_up.stride(1) == 1 and out.is_contiguous()
+    _check(core().ie_silu_mul(_ptr(gate_up), _ptr(out), n, inter, gate_up.stride(0), dtype_code(out.dtype),
+                              _stream()), "silu_mul")
+
+
+# --------------------------------------------------------------------- attention
+def attention_general(q: torch.Tensor, out: torch.Tensor, kpool: torch.Tensor, vpool: torch.Tensor,
+                      block_table: torch.Tensor, q_start: torch.Tensor, ctx_before: torch.Tensor,
+                      work_req: torch.Tensor, work_pair0: torch.Tensor, n_work: int, n_heads: int,
+                      n_kv_heads: int, head_dim: int, page_size: int, window: int | None, scale: float) -> None:
+    assert q.stride(1) == 1 and out.stride(1) == 1 and kpool.dtype == q.dtype == out.dtype
+    assert block_table.dtype == torch.int32 and block_table.stride(1) == 1
+    _check(core().ie_attention_general(_ptr(q), _ptr(out), _ptr(kpool), _ptr(vpool), _ptr(block_table),
+                                       _ptr(q_start), _ptr(ctx_before), _ptr(work_req), _ptr(work_pair0),
+                                       q.stride(0), out.stride(0), block_table.stride(0), n_work, n_heads,
+                                       n_kv_heads, head_dim, page_size, int(window or 0), float(scale),
+                                       dtype_code(q.dtype), _stream()),
+           f"attention_general(head_dim={head_dim}, heads={n_heads}/{n_kv_heads})")
+
+
+# -------------------------------------------------------------------------- gemm
+def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[M,N] = a[M,K] @ w[N,K]^T in float32 arithmetic."""
+    m, k = a.shape
+    n = w.shape[0]
+    assert w.shape[1] == k and out.shape == (m, n)
+    assert a.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
+    _check(core().ie_gemm_simt(_ptr(a), dtype_code(a.dtype), _ptr(w), dtype_code(w.dtype), _ptr(out),
+                               dtype_code(out.dtype), m, n, k, a.stride(0), w.stride(0), out.stride(0),
+                               _stream()), f"gemm_simt({a.dtype},{w.dtype}->{out.dtype})")
+
+
+# ---------------------------------------------------------------------- sampling
+def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1 and out.dtype == torch.int32
+    _check(core().ie_argmax(_ptr(logits), _ptr(out), logits.shape[0], logits.shape[1], logits.stride(0),
+                            _stream()), "argmax")
+
+
+def repetition_penalty(logits: torch.Tensor, context: torch.Tensor, penalty: torch.Tensor) -> None:
+    assert logits.dtype == torch.float32 and context.dtype == torch.int32 and penalty.dtype == torch.float32
+    assert context.is_contiguous() and context.shape[0] == logits.shape[0]
+    _check(core().ie_repetition_penalty(_ptr(logits), _ptr(context), _ptr(penalty), logits.shape[0],
+                                        logits.shape[1], logits.stride(0), context.shape[1], _stream()),
+           "repetition_penalty")
+
+
+def sample(logits: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> None:
+    """rows: int32 [n, 7] records (temperature bits, top_p bits, top_k, seed lo/hi, key lo/hi)."""
+    assert logits.dtype == torch.float32 and rows.dtype == torch.int32 and rows.shape == (logits.shape[0], 7)
+    assert rows.is_contiguous() and out.dtype == torch.int32
+    _check(core().ie_sample(_ptr(logits), _ptr(rows), _ptr(out), logits.shape[0], logits.shape[1],
+                            logits.stride(0), _stream()), "sample")

@@ -1,0 +1,101 @@
+"""Grouped-query causal attention over the paged cache
+(engine/llama_attention.py:83-141).
+
+q, k and v come from one matrix product over the row-concatenated weights;
+a fused kernel rotates q and k and writes k and v into the pages of the step's
+tokens; the attention kernel then reads every key and value through the block
+table, so a prompt portion, a decode token and a whole prompt take the same
+path.  kv head c serves query heads c*g .. c*g+g-1 (:27-44) inside the kernel;
+nothing is expanded in memory.  Scores are scaled by head_dim**-0.5 (the
+library default the reference relies on, :123-137).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from .. import kernels
+from ..cache.manager import CacheRequirement
+from ..weights.loader import ExpectedTensor
+from .linear import Linear
+from .registry import build_position, position_class, register_mixer
+
+
+@dataclass
+class CacheView:
+    """The cache of one run of a layer, as its mixer sees it."""
+
+    kind: str                               # "kv" | "state" | "none"
+    group: int = -1                         # index of the kv group (for block tables and slots in ctx)
+    k: torch.Tensor | None = None           # [n_pages, n_kv_heads, page_size, head_dim]
+    v: torch.Tensor | None = None
+    state: torch.Tensor | None = None       # [max_requests, *state_shape]
+    write: bool = True                      # False: this run reads another run's cache
+
+
+@register_mixer("attention")
+class PagedAttention:
+    graph_safe = True
+
+    @staticmethod
+    def expected_tensors(spec):
+        out = {
+            spec.q_proj: ExpectedTensor((spec.n_heads * spec.head_dim, spec.hidden)),
+            spec.k_proj: ExpectedTensor((spec.n_kv_heads * spec.head_dim, spec.hidden)),
+            spec.v_proj: ExpectedTensor((spec.n_kv_heads * spec.head_dim, spec.hidden)),
+            spec.o_proj: ExpectedTensor((spec.hidden, spec.n_heads * spec.head_dim)),
+        }
+        out.update(position_class(spec.position).expected_tensors(spec.position))
+        return out
+
+    def __init__(self, spec, tensors, rt):
+        if spec.n_heads % spec.n_kv_heads:
+            raise ValueError(f"{spec.n_heads} query heads are not a multiple of {spec.n_kv_heads} kv heads")
+        if spec.head_dim % 16 or spec.head_dim > 256:
+            raise ValueError(f"attention kernels take head sizes in steps of 16 up to 256, not {spec.head_dim}")
+        if spec.window is not None and spec.window <= 0:
+            raise ValueError("an attention window must be positive")
+        self.spec = spec
+        self.rt = rt
+        ws = [tensors[spec.q_proj], tensors[spec.k_proj], tensors[spec.v_proj]]
+        dtype = torch.float32 if any(w.dtype is torch.float32 for w in ws) else ws[0].dtype
+        self.qkv = Linear(torch.cat([w.to(dtype) for w in ws], dim=0).contiguous(), rt, "qkv")
+        self.o = Linear(tensors[spec.o_proj], rt, "o")
+        self.position = build_position(spec.position, tensors, rt)
+        self.scale = float(spec.head_dim) ** -0.5
+        self.q_width = spec.n_heads * spec.head_dim
+        self.kv_width = spec.n_kv_heads * spec.head_dim
+
+    def cache_requirement(self) -> CacheRequirement:
+        s = self.spec
+        return CacheRequirement(kind="kv", n_kv_heads=s.n_kv_heads, head_dim=s.head_dim, window=s.window,
+                                dtype=self.rt.act_dtype)
+
+    def forward(self, x: torch.Tensor, ctx, cache: CacheView) -> torch.Tensor:
+        s, rt = self.spec, self.rt
+        n = x.shape[0]
+        qkv = self.qkv(x, rt.ws.take("attn_qkv", (n, self.q_width + 2 * self.kv_width), rt.act_dtype))
+        q = qkv[:, :self.q_width]
+        k = qkv[:, self.q_width:self.q_width + self.kv_width]
+        v = qkv[:, self.q_width + self.kv_width:]
+        kvctx = ctx.kv[cache.group]
+        tables = self.position.rotary_tables()
+        if tables is None:
+            self.position.rotate(q, k, ctx)
+        cos, sin = tables if tables is not None else (None, None)
+        kernels.rope_kv_write(q, k, v, cos, sin, ctx.positions, kvctx.slot_mapping,
+                              cache.k if cache.write else None, cache.v if cache.write else None,
+                              s.n_heads, s.n_kv_heads, s.head_dim, ctx.page_size)
+        out = rt.ws.take("attn_out", (n, self.q_width), rt.act_dtype)
+        self._attend(q, out, cache, ctx, kvctx)
+        return self.o(out, rt.ws.take("mixer_out", (n, s.hidden), rt.act_dtype))
+
+    def _attend(self, q, out, cache, ctx, kvctx) -> None:
+        s = self.spec
+        group = s.n_heads // s.n_kv_heads
+        work_req, work_pair0, n_work = ctx.attention_work(group, 32)
+        kernels.attention_general(q, out, cache.k, cache.v, kvctx.block_table, ctx.q_start, ctx.ctx_before,
+                                  work_req, work_pair0, n_work, s.n_heads, s.n_kv_heads, s.head_dim,
+                                  ctx.page_size, s.window, self.scale)

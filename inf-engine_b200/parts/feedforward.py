@@ -1,0 +1,44 @@
+"""Dense gated feed-forward: ``down(silu(gate(x)) * up(x))`` (engine/llama_mlp.py:30-33).
+
+Gate and up are one matrix product over the row-concatenated weights
+[2*intermediate, hidden]; the activation and the product by ``up`` are one
+kernel in float32 arithmetic.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .. import kernels
+from ..weights.loader import ExpectedTensor
+from .linear import Linear
+from .registry import register_feedforward
+
+
+@register_feedforward("gated_mlp")
+class GatedMLP:
+    @staticmethod
+    def expected_tensors(spec):
+        return {
+            spec.gate_proj: ExpectedTensor((spec.intermediate, spec.hidden)),
+            spec.up_proj: ExpectedTensor((spec.intermediate, spec.hidden)),
+            spec.down_proj: ExpectedTensor((spec.hidden, spec.intermediate)),
+        }
+
+    def __init__(self, spec, tensors, rt):
+        if spec.activation != "silu":
+            raise ValueError(f"activation {spec.activation!r} is not built")
+        self.spec = spec
+        self.rt = rt
+        gate, up = tensors[spec.gate_proj], tensors[spec.up_proj]
+        dtype = torch.float32 if torch.float32 in (gate.dtype, up.dtype) else gate.dtype
+        self.gate_up = Linear(torch.cat([gate.to(dtype), up.to(dtype)], dim=0).contiguous(), rt, "gate_up")
+        self.down = Linear(tensors[spec.down_proj], rt, "down")
+
+    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        n = x.shape[0]
+        s, ws, dt = self.spec, self.rt.ws, self.rt.act_dtype
+        gu = self.gate_up(x, ws.take("ff_gate_up", (n, 2 * s.intermediate), dt))
+        h = ws.take("ff_hidden", (n, s.intermediate), dt)
+        kernels.silu_mul(gu, h)
+        return self.down(h, ws.take("ff_out", (n, s.hidden), dt))

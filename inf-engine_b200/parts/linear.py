@@ -1,0 +1,62 @@
+"""``y = x W^T`` with the weight in the checkpoint's (out, in) layout
+(engine/layers.py:48-50).
+
+Which kernel runs is decided by the dtypes:
+  * float32 activations, or a weight kept in float32: the CUDA-core kernel of
+    this package (float32 products and sums, no tensor cores);
+  * bfloat16 activations and weight: the library matrix product (cuBLAS through
+    ``torch.mm``), which is what the reference's engine uses for every
+    projection, or this package's own kernels where they are registered for the
+    shape.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .. import kernels
+
+
+class Linear:
+    def __init__(self, weight: torch.Tensor, rt, name: str = "linear"):
+        assert weight.dim() == 2 and weight.is_contiguous()
+        self.weight = weight
+        self.rt = rt
+        self.name = name
+        self.out_features, self.in_features = weight.shape
+
+    def __call__(self, x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        """Write ``x @ W^T`` into ``out`` ([M, out_features], may be a column slice)."""
+        w = self.weight
+        assert x.shape[1] == self.in_features and out.shape == (x.shape[0], self.out_features)
+        if x.shape[0] == 0:
+            return out
+        if x.dtype is torch.float32 or w.dtype is torch.float32:
+            kernels.gemm_simt(x, w, out)
+            return out
+        # bfloat16 x bfloat16
+        if out.dtype is torch.bfloat16 and out.is_contiguous():
+            torch.mm(x, w.t(), out=out)
+        elif out.dtype is torch.float32 and out.is_contiguous():
+            _mm_f32_out(x, w, out)
+        else:
+            kernels.gemm_simt(x, w, out)
+        return out
+
+
+_F32_OUT_OK: bool | None = None
+
+
+def _mm_f32_out(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """bfloat16 operands, float32 result (the logits) from the library product."""
+    global _F32_OUT_OK
+    if _F32_OUT_OK is None:
+        try:
+            torch.mm(x[:1], w[:8].t(), out_dtype=torch.float32)
+            _F32_OUT_OK = True
+        except (TypeError, RuntimeError):
+            _F32_OUT_OK = False
+    if _F32_OUT_OK:
+        torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
+    else:
+        kernels.gemm_simt(x, w, out)

@@ -1,0 +1,78 @@
+"""A decoder put together from parts: token table, blocks run in the order of
+the schedule, final norm on the rows whose logits are wanted, head
+(engine/llama_model.py:128-149).  The reference computes logits for every
+position (:148); here the head runs on the gathered rows only and its result
+is float32."""
+
+from __future__ import annotations
+
+import torch
+
+from .. import kernels
+from ..cache.manager import CacheManager, CacheRequirement
+from .attention import CacheView
+from .linear import Linear
+from .registry import build_block, build_norm
+
+
+class DecoderModel:
+    def __init__(self, spec, tensors: dict, rt):
+        self.spec = spec
+        self.rt = rt
+        self.embedding = tensors[spec.embedding]
+        self.layers = [build_block(b, tensors, rt) for b in spec.layers]
+        self.final_norm = build_norm(spec.final_norm, tensors, rt)
+        head = tensors[spec.head] if spec.head is not None else self.embedding   # tied: one buffer
+        self.head = Linear(head, rt, "head")
+        for i, e in enumerate(spec.schedule):
+            if not 0 <= e.layer < len(self.layers):
+                raise ValueError(f"schedule entry {i} names layer {e.layer}, the model has {len(self.layers)}")
+            if e.cache_from is not None and not (0 <= e.cache_from < i and spec.schedule[e.cache_from].cache_from is None):
+                raise ValueError(f"schedule entry {i} must read the cache of an earlier entry that owns one")
+        self.graph_safe = all(getattr(self.layers[e.layer].mixer, "graph_safe", False) for e in spec.schedule)
+        self._views: list[CacheView] | None = None
+
+    # ------------------------------------------------------------------ cache
+    def cache_requirements(self) -> list[CacheRequirement]:
+        """One requirement per schedule entry; a run that reads another run's cache needs none."""
+        reqs = []
+        for e in self.spec.schedule:
+            if e.cache_from is not None:
+                reqs.append(CacheRequirement(kind="none"))
+            else:
+                reqs.append(self.layers[e.layer].mixer.cache_requirement())
+        return reqs
+
+    def bind_cache(self, manager: CacheManager) -> None:
+        views = []
+        for i, e in enumerate(self.spec.schedule):
+            src = i if e.cache_from is None else e.cache_from
+            b = manager.bindings[src]
+            if b.kind == "kv":
+                g = manager.kv_groups[b.group]
+                views.append(CacheView("kv", b.group, g.k[b.row], g.v[b.row], None, write=e.cache_from is None))
+            elif b.kind == "state":
+                g = manager.state_groups[b.group]
+                views.append(CacheView("state", b.group, None, None, g.data[b.row], write=e.cache_from is None))
+            else:
+                views.append(CacheView("none"))
+        self._views = views
+
+    # ---------------------------------------------------------------- forward
+    def forward(self, ctx) -> torch.Tensor | None:
+        """Run the step's tokens through every scheduled layer; float32 logits
+        [n_wanted, vocab] at ``ctx.logit_rows`` (None when nothing is wanted)."""
+        assert self._views is not None, "bind_cache() first"
+        rt, spec = self.rt, self.spec
+        n = ctx.n_tokens
+        residual = rt.ws.take("residual", (n, spec.hidden), torch.float32)
+        kernels.embed_gather(ctx.token_ids, self.embedding, residual)
+        pending = None
+        for i, e in enumerate(spec.schedule):
+            residual, pending = self.layers[e.layer].forward(residual, pending, ctx, self._views[i])
+        m = ctx.n_logits
+        if m == 0:
+            return None
+        h = self.final_norm.gather_norm(residual, pending, ctx.logit_rows, m)
+        logits = rt.ws.take("logits", (m, spec.vocab_size), torch.float32)
+        return self.head(h, logits)

@@ -1,0 +1,91 @@
+"""Shared test helpers: tiny configurations that differ in every size and
+option, model folders in temporary places, and comparisons with the plain
+implementation."""
+
+from __future__ import annotations
+
+import json
+from pathlib import Path
+
+import torch
+
+import plain_llama
+
+# Two tiny Llama configurations that differ in every size and option: layers,
+# width, head counts and groups, head size, a feed-forward width and a
+# vocabulary that are no power of two, theta, scaling, eps, tied or not.
+TINY_A = dict(
+    architectures=["LlamaForCausalLM"], num_hidden_layers=2, hidden_size=64, num_attention_heads=4,
+    num_key_value_heads=2, head_dim=16, intermediate_size=176, vocab_size=256, rope_theta=10000.0,
+    rope_scaling=None, rms_norm_eps=1e-5, tie_word_embeddings=True, max_position_embeddings=512,
+    hidden_act="silu",
+)
+TINY_B = dict(
+    architectures=["LlamaForCausalLM"], num_hidden_layers=3, hidden_size=120, num_attention_heads=6,
+    num_key_value_heads=2, head_dim=32, intermediate_size=328, vocab_size=389, rope_theta=500000.0,
+    rope_scaling=dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                      original_max_position_embeddings=64),
+    rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=1024, hidden_act="silu",
+)
+# a third one for sizes the other two miss: one kv head (every query head in one group), head size 48
+TINY_C = dict(
+    architectures=["LlamaForCausalLM"], num_hidden_layers=1, hidden_size=96, num_attention_heads=3,
+    num_key_value_heads=1, head_dim=48, intermediate_size=200, vocab_size=301, rope_theta=20000.0,
+    rope_scaling=None, rms_norm_eps=1e-5, tie_word_embeddings=True, max_position_embeddings=512,
+    hidden_act="silu",
+)
+TINY = {"tiny_a": TINY_A, "tiny_b": TINY_B, "tiny_c": TINY_C}
+SEEDS = {"tiny_a": 0, "tiny_b": 1, "tiny_c": 2}
+
+
+def make_model_dir(tmp: Path, name: str, store_dtype: str = "bfloat16", std: float = 0.05) -> Path:
+    """Write a random model folder with the package's random-weights mode."""
+    from inf_engine_b200.config import parse_config_dict
+    from inf_engine_b200.weights import write_random_model
+
+    cfg = parse_config_dict(TINY[name])
+    out = Path(tmp) / f"{name}_{store_dtype}"
+    if not (out / "model.safetensors").is_file():
+        write_random_model(cfg, SEEDS[name], out, store_dtype=store_dtype, std=std)
+    return out
+
+
+def plain_inputs(model_dir: Path):
+    """(config dict, float32 weights) of a model folder for the plain implementation,
+    read with the ``safetensors`` package rather than with the product's reader."""
+    from safetensors import safe_open
+
+    config = json.loads((Path(model_dir) / "config.json").read_text())
+    weights = {}
+    with safe_open(str(Path(model_dir) / "model.safetensors"), framework="pt", device="cpu") as f:
+        for k in f.keys():
+            weights[k] = f.get_tensor(k).float()
+    return config, weights
+
+
+def random_tokens(vocab: int, n: int, seed: int) -> list[int]:
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, vocab, (n,), generator=g).tolist()
+
+
+def tolerance(dtype: str, ref: torch.Tensor) -> float:
+    """Largest absolute logit difference allowed against the plain implementation.
+
+    float32: summation order only.  bfloat16: activations and cache are rounded to
+    8 bits of mantissa at every stage; the bound is relative to the largest logit.
+    """
+    scale = float(ref.abs().max())
+    return (2e-5 if dtype == "float32" else 4e-2) * max(scale, 1.0)
+
+
+def assert_close(got: torch.Tensor, ref: torch.Tensor, dtype: str, what: str = "") -> None:
+    got = got.float().cpu()
+    ref = ref.float().cpu()
+    assert got.shape == ref.shape, f"{what}: shape {tuple(got.shape)} vs {tuple(ref.shape)}"
+    assert torch.isfinite(got).all(), f"{what}: non-finite logits"
+    diff = (got - ref).abs()
+    tol = tolerance(dtype, ref)
+    if float(diff.max()) > tol:
+        idx = int(diff.max(dim=-1).values.argmax()) if diff.dim() > 1 else 0
+        raise AssertionError(f"{what}: max |diff| {float(diff.max()):.3e} > {tol:.3e}; first worst row {idx}; "
+                             f"rows over tolerance: {(diff.max(dim=-1).values > tol).nonzero().flatten().tolist()[:20]}")
