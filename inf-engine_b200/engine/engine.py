@@ -1,0 +1,131 @@
+"""The engine: continuous batching over the step function, in the manner of the
+reference's ``LlamaPagedEngine`` (engine/llama_paged_engine.py:106-455):
+``submit`` / ``step`` / ``run_offline`` / ``has_work``, a page pool given as
+``n_total_blocks`` x ``block_size``, an ``eos_token`` and a default sampling.
+
+One ``step`` is one scheduler plan, one batch through the model (prompt
+portions beside decode tokens), one sampling launch and one read of the
+sampled ids.
+"""
+
+from __future__ import annotations
+
+import tempfile
+import time
+from pathlib import Path
+
+import torch
+
+from ..config.registry import detect_config, get_preset
+from ..sampling.sampler import Sampler, SamplingConfig, request_key
+from ..weights.random_init import write_random_model
+from .batch import StepEntry
+from .runner import ModelRunner
+from .scheduler import Request, Scheduler
+
+
+class Engine:
+    def __init__(self, runner: ModelRunner, eos_token=None, sampling: SamplingConfig | None = None,
+                 max_queue_depth: int = 4096, max_batch: int | None = None, max_tokens_per_step: int = 2048,
+                 chunk: int | None = None):
+        self.runner = runner
+        self.cfg = sampling or SamplingConfig()
+        if eos_token is None:
+            eos_token = getattr(runner.config, "eos_token_id", None)
+        self.eos = eos_token
+        self.scheduler = Scheduler(runner.cache, runner.spec.max_positions,
+                                   max_batch=max_batch or runner.cache.max_requests,
+                                   max_tokens_per_step=max_tokens_per_step, chunk=chunk,
+                                   max_queue_depth=max_queue_depth, eos_token=eos_token)
+        self.sampler = Sampler(runner.rt)
+        self.stats = {"steps": 0, "prefill_tokens": 0, "decode_tokens": 0, "preemptions": 0}
+
+    # ------------------------------------------------------------ construction
+    @classmethod
+    def from_dir(cls, model_dir: str | Path, dtype="bfloat16", device="cuda:0", n_total_blocks: int = 4096,
+                 block_size: int = 16, max_requests: int = 64, **kw) -> "Engine":
+        runner = ModelRunner.from_dir(model_dir, dtype=dtype, device=device, page_size=block_size,
+                                      n_pages=n_total_blocks, max_requests=max_requests)
+        return cls(runner, **kw)
+
+    @classmethod
+    def from_random(cls, config, seed: int = 0, dtype="bfloat16", store_dtype: str = "bfloat16", **kw) -> "Engine":
+        """An engine over random weights: the model folder is written to a temporary
+        place with the random-weights mode and loaded like any other."""
+        if isinstance(config, str):
+            config = get_preset(config)
+        with tempfile.TemporaryDirectory(prefix="inf_engine_random_") as tmp:
+            write_random_model(config, seed, tmp, store_dtype=store_dtype)
+            return cls.from_dir(tmp, dtype=dtype, **kw)
+
+    # ------------------------------------------------------------------ queue
+    def submit(self, req: Request) -> bool:
+        return self.scheduler.submit(req)
+
+    @property
+    def has_work(self) -> bool:
+        return self.scheduler.has_work
+
+    @property
+    def completed(self) -> list[Request]:
+        return self.scheduler.completed
+
+    # ------------------------------------------------------------------- step
+    @torch.no_grad()
+    def step(self, now: float = 0.0) -> list[Request]:
+        """Admit, run one mixed batch, sample, finish; returns the requests completed."""
+        plan = self.scheduler.plan()
+        self.stats["preemptions"] += len(plan.preempted)
+        if not plan.entries:
+            return []
+        entries = [StepEntry(e.request.req_id, e.tokens, [len(e.tokens) - 1] if e.wants_logits else [])
+                   for e in plan.entries]
+        logits = self.runner.step(entries)
+        sampled = {}
+        wanted = [e for e in plan.entries if e.wants_logits]
+        if wanted:
+            configs = [e.request.sampling or self.cfg for e in wanted]
+            keys = [request_key(e.request.req_id, len(e.request.generated)) for e in wanted]
+            contexts = None
+            if any(c.repetition_penalty != 1.0 for c in configs):
+                contexts = [e.request.generated for e in wanted]
+            ids = self.sampler.sample(logits, configs, keys, contexts).tolist()   # the step's one device-to-host read
+            sampled = {e.request.req_id: t for e, t in zip(wanted, ids)}
+        for e in plan.entries:
+            self.stats["decode_tokens" if len(e.tokens) == 1 and e.request.generated else "prefill_tokens"] += len(e.tokens)
+        self.stats["steps"] += 1
+        return self.scheduler.commit(plan, sampled, now)
+
+    def run_offline(self, requests: list[Request]) -> dict[int, list[int]]:
+        """Submit everything, run to completion; ``{req_id: generated}``
+        (engine/llama_paged_engine.py:445-455).  Requests refused at submit map to []."""
+        refused = [r for r in requests if not self.submit(r)]
+        while self.has_work:
+            self.step(time.perf_counter())
+        out = {r.req_id: r.generated for r in self.completed}
+        out.update({r.req_id: [] for r in refused})
+        return out
+
+    def generate(self, prompt_ids: list[int], max_new_tokens: int, sampling: SamplingConfig | None = None,
+                 req_id: int = 0) -> list[int]:
+        """Continuation of one prompt (the reference's ``generate_cached``, engine/llama_model.py:177-215)."""
+        if max_new_tokens <= 0:
+            return []
+        req = Request(req_id=req_id, prompt_ids=list(prompt_ids), max_new_tokens=max_new_tokens, sampling=sampling)
+        if not self.submit(req):
+            raise ValueError(f"request refused: {req.error}")
+        while req not in self.completed:
+            self.step(time.perf_counter())
+        self.completed.remove(req)
+        return req.generated
+
+
+def load_engine(model_dir_or_preset: str, dtype="bfloat16", random_weights: bool = False, seed: int = 0, **kw) -> Engine:
+    """An engine from a model folder, or from a preset name with random weights."""
+    p = Path(model_dir_or_preset)
+    if p.is_dir() and not random_weights:
+        return Engine.from_dir(p, dtype=dtype, **kw)
+    return Engine.from_random(get_preset(model_dir_or_preset), seed=seed, dtype=dtype, **kw)
+
+
+__all__ = ["Engine", "Request", "load_engine", "detect_config"]

@@ -89,3 +89,62 @@ def assert_close(got: torch.Tensor, ref: torch.Tensor, dtype: str, what: str = "
         idx = int(diff.max(dim=-1).values.argmax()) if diff.dim() > 1 else 0
         raise AssertionError(f"{what}: max |diff| {float(diff.max()):.3e} > {tol:.3e}; first worst row {idx}; "
                              f"rows over tolerance: {(diff.max(dim=-1).values > tol).nonzero().flatten().tolist()[:20]}")
+
+
+# --------------------------------------------------------------------- replay traces
+def round64(n: int) -> int:
+    return -(-n // 64) * 64
+
+
+class TraceBuilder:
+    """Builds steps for ``bin/trace_run`` and remembers which (request, position)
+    each output row is, and the most tokens (rounded per request to 64) live at once."""
+
+    def __init__(self):
+        self.steps: list[dict] = []
+        self.rows: dict[int, list[tuple[str, int]]] = {}
+        self.held: dict[str, int] = {}
+        self.max_tokens = 0
+
+    def step(self, entries: list[tuple[str, list[int], int]], end: list[str] = ()):
+        """entries: (request id, tokens, position of the first of them); every position is wanted."""
+        n = len(self.steps)
+        rec = {"step": n, "entries": [], "end": list(end)}
+        rows = []
+        for rid, toks, start in entries:
+            assert self.held.get(rid, 0) == start, (rid, self.held.get(rid, 0), start)
+            rec["entries"].append({"id": rid, "tokens": toks, "want": list(range(len(toks)))})
+            rows += [(rid, start + i) for i in range(len(toks))]
+            self.held[rid] = start + len(toks)
+        self.max_tokens = max(self.max_tokens, sum(round64(v) for v in self.held.values()))
+        for rid in end:
+            self.held.pop(rid)
+        self.steps.append(rec)
+        self.rows[n] = rows
+
+
+def run_trace(model_dir, dtype: str, trace: TraceBuilder, out_dir, vocab: int, page_size: int = 16) -> dict:
+    """Run ``bin/trace_run`` as a user would and return ``{(request, position): logits}``."""
+    import json as _json
+    import os
+    import subprocess
+    import sys
+
+    import numpy as np
+
+    root = Path(__file__).resolve().parent.parent
+    text = "".join(_json.dumps(s) + "\n" for s in trace.steps)
+    proc = subprocess.run(
+        [sys.executable, str(root / "bin" / "trace_run"), "--model", str(model_dir), "--dtype", dtype, "--out",
+         str(out_dir), "--max-tokens", str(trace.max_tokens), "--page-size", str(page_size)],
+        input=text, capture_output=True, text=True, timeout=600, env=dict(os.environ))
+    assert proc.returncode == 0, f"trace_run failed:\n{proc.stderr[-3000:]}"
+    done = [l for l in proc.stdout.splitlines() if l.startswith("done ")]
+    assert done == [f"done {i}" for i in range(len(trace.steps))], proc.stdout[-2000:]
+    out = {}
+    for n, rows in trace.rows.items():
+        data = np.fromfile(Path(out_dir) / f"{n}.f32", dtype="<f4").reshape(len(rows), vocab)
+        for i, key in enumerate(rows):
+            assert key not in out
+            out[key] = torch.from_numpy(data[i].copy())
+    return out

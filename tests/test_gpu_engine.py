@@ -1,0 +1,300 @@
+"""The step function, the cache and generation, in process: long decoding, the
+first tokens of a sequence, weights made so that a wrong page or a wrong key
+shows, reused pages that hold stale data, greedy and sampled generation through
+the Python entry point and the command line."""
+
+import dataclasses
+import json
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+import plain_llama
+from helpers import TINY, assert_close, make_model_dir, plain_inputs, random_tokens
+
+pytestmark = pytest.mark.gpu
+DTYPES = ["float32", "bfloat16"]
+
+
+def runner_for(model_dir, dtype, **kw):
+    from inf_engine_b200 import ModelRunner
+    return ModelRunner.from_dir(model_dir, dtype=dtype, **kw)
+
+
+def entry(rid, toks, want="all"):
+    from inf_engine_b200 import StepEntry
+    return StepEntry(rid, toks, list(range(len(toks))) if want == "all" else want)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
+def test_long_decoding(tmp_path, name, dtype):
+    d = make_model_dir(tmp_path, name)
+    config, weights = plain_inputs(d)
+    toks = random_tokens(config["vocab_size"], 330, 5)
+    ref = plain_llama.forward_logits(weights, config, toks)
+    r = runner_for(d, dtype, page_size=8, n_pages=48)
+    r.open("x")
+    rows = [r.step([entry("x", toks[:6])]).cpu().clone()]
+    for p in range(6, len(toks)):
+        rows.append(r.step([entry("x", toks[p:p + 1])]).cpu().clone())
+    assert_close(torch.cat(rows), ref, dtype, f"{name} {dtype} long decoding")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c"])
+def test_first_tokens_of_a_sequence(tmp_path, name, dtype):
+    d = make_model_dir(tmp_path, name)
+    config, weights = plain_inputs(d)
+    r = runner_for(d, dtype, page_size=16, n_pages=8)
+    for n in (1, 2, 3, 17):
+        toks = random_tokens(config["vocab_size"], n, 40 + n)
+        ref = plain_llama.forward_logits(weights, config, toks)
+        r.open("whole")
+        assert_close(r.step([entry("whole", toks)]).cpu(), ref, dtype, f"{name} first {n} tokens at once")
+        r.close("whole")
+        r.open("single")
+        rows = [r.step([entry("single", [t])]).cpu().clone() for t in toks]
+        assert_close(torch.cat(rows), ref, dtype, f"{name} first {n} tokens one by one")
+        r.close("single")
+
+
+def sharpened(tmp_path, name, factor=5.0):
+    """A copy of a tiny model whose q and k projections are scaled up: the softmax becomes
+    peaked, each query leans on a few keys far back, and a key read from a wrong page or a
+    wrong offset moves the logits far beyond rounding."""
+    from inf_engine_b200.weights import open_checkpoint, write_safetensors
+
+    src = make_model_dir(tmp_path, name)
+    dst = Path(tmp_path) / f"{name}_sharp"
+    dst.mkdir(exist_ok=True)
+    t = {k: v.read().clone() for k, v in open_checkpoint(src).items()}
+    for k in t:
+        if k.endswith("q_proj.weight") or k.endswith("k_proj.weight"):
+            t[k] = (t[k].float() * factor).to(t[k].dtype)
+    write_safetensors(dst / "model.safetensors", t)
+    (dst / "config.json").write_text((src / "config.json").read_text())
+    return dst
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
+def test_peaked_attention_over_reused_pages(tmp_path, name, dtype):
+    # bfloat16 rounds q and k to 8 bits, and a score of size s then carries an error of about
+    # s/256 into the exponent: the scores are made 25 times larger in 32-bit, 6 times in bfloat16
+    d = sharpened(tmp_path, name, factor=5.0 if dtype == "float32" else 2.5)
+    config, weights = plain_inputs(d)
+    vocab = config["vocab_size"]
+    a, b, c = (random_tokens(vocab, n, s) for n, s in ((300, 1), (170, 2), (260, 3)))
+    ref = {k: plain_llama.forward_logits(weights, config, v) for k, v in (("a", a), ("b", b), ("c", c))}
+    r = runner_for(d, dtype, page_size=8, n_pages=-(-300 // 8) + -(-170 // 8) + 2)
+    got = {"a": [], "b": [], "c": []}
+    r.open("a"); r.open("b")
+    pa = pb = 0
+    while pa < len(a) or pb < len(b):
+        es = []
+        if pa < len(a):
+            n = min(37, len(a) - pa); es.append(entry("a", a[pa:pa + n])); pa += n
+        if pb < len(b):
+            n = 1 if pb > 150 else min(29, len(b) - pb); es.append(entry("b", b[pb:pb + n])); pb += n
+        lg = r.step(es).cpu()
+        o = 0
+        for e in es:
+            got[e.rid].append(lg[o:o + len(e.tokens)].clone()); o += len(e.tokens)
+    r.close("a")                                   # c now takes pages that a held; they still hold a's keys
+    r.open("c")
+    pc = 0
+    while pc < len(c):
+        n = min(2 + pc % 23, len(c) - pc)
+        got["c"].append(r.step([entry("c", c[pc:pc + n])]).cpu().clone()); pc += n
+    for k in got:
+        assert_close(torch.cat(got[k]), ref[k], dtype, f"{name} {dtype} peaked request {k}")
+    r.cache.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_model_with_a_window_layer_a_shared_cache_and_a_layer_run_twice(tmp_path, dtype):
+    """The order of layers is data: layer 0 (full attention), then layer 1 (a window of 24)
+    run twice, each run with a cache of its own, then layer 2 reading layer 0's cache.
+    Checked against the plain functions put together the same way."""
+    from inf_engine_b200 import ModelRunner
+    from inf_engine_b200.config import ScheduleEntry, parse_config_dict
+    from inf_engine_b200.parts import expected_tensors
+    from inf_engine_b200.weights import load_weights
+
+    name = "tiny_b"
+    d = make_model_dir(tmp_path, name)
+    config, weights = plain_inputs(d)
+    cfg = parse_config_dict(TINY[name])
+    base = cfg.model_spec()
+    window = 24
+    layers = list(base.layers)
+    layers[1] = dataclasses.replace(layers[1], mixer=dataclasses.replace(layers[1].mixer, window=window))
+    schedule = (ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(1), ScheduleEntry(2, cache_from=0))
+    spec = dataclasses.replace(base, layers=tuple(layers), schedule=schedule)
+    run_dtype = torch.float32 if dtype == "float32" else torch.bfloat16
+    tensors = load_weights(d, expected_tensors(spec), run_dtype, "cuda:0")
+    r = ModelRunner(cfg, tensors, run_dtype, page_size=8, n_pages=40, spec=spec)
+    assert len(r.cache.kv_groups) == 2 and r.cache.kv_groups[1].window == window
+    assert len(r.cache.kv_groups[1].entries) == 2               # layer 1's two runs have a cache each
+
+    toks = random_tokens(config["vocab_size"], 150, 9)
+
+    def plain_forward(toks):
+        w = weights
+        T = len(toks)
+        x = w["model.embed_tokens.weight"][torch.tensor(toks)]
+        cos, sin = plain_llama.rope_tables(config, T)
+        eps = config["rms_norm_eps"]
+        kv0 = None
+        for run, (layer, win, shared) in enumerate([(0, None, False), (1, window, False), (1, window, False), (2, None, True)]):
+            p = f"model.layers.{layer}."
+            h = plain_llama.rms_norm(x, w[p + "input_layernorm.weight"], eps)
+            wk, wv = w[p + "self_attn.k_proj.weight"], w[p + "self_attn.v_proj.weight"]
+            if run == 0:
+                kv0 = h
+            if shared:
+                # keys and values come from the cache of run 0: layer 0's projections of layer 0's input
+                p0 = "model.layers.0."
+                att = _attention_with_foreign_kv(h, kv0, w[p + "self_attn.q_proj.weight"],
+                                                 w[p0 + "self_attn.k_proj.weight"], w[p0 + "self_attn.v_proj.weight"],
+                                                 w[p + "self_attn.o_proj.weight"], config, cos, sin)
+            else:
+                att = plain_llama.attention(h, w[p + "self_attn.q_proj.weight"], wk, wv,
+                                            w[p + "self_attn.o_proj.weight"], config, cos, sin, window=win)
+            x = x + att
+            h = plain_llama.rms_norm(x, w[p + "post_attention_layernorm.weight"], eps)
+            x = x + plain_llama.swiglu(h, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
+        x = plain_llama.rms_norm(x, w["model.norm.weight"], eps)
+        return x @ w["lm_head.weight"].T
+
+    ref = plain_forward(toks)
+    r.open("x")
+    rows, p = [], 0
+    for n in [31, 2, 40, 1, 1, 1, 17, 57]:
+        rows.append(r.step([entry("x", toks[p:p + n])]).cpu().clone()); p += n
+        r.cache.check()
+    assert p == len(toks)
+    assert_close(torch.cat(rows), ref, dtype, f"window/shared/twice {dtype}")
+    # the window group gave pages back as it moved; the full group kept all
+    assert r.cache.kv_groups[1].pool.n_held <= -(-window // 8) + 1
+    assert r.cache.kv_groups[0].pool.n_held == -(-150 // 8)
+
+
+def _attention_with_foreign_kv(h_q, h_kv, wq, wk, wv, wo, config, cos, sin):
+    """plain_llama.attention with keys and values projected from another run's input."""
+    T = h_q.shape[0]
+    H, Hk, hd = config["num_attention_heads"], config["num_key_value_heads"], config["head_dim"]
+    q = (h_q @ wq.T).view(T, H, hd).transpose(0, 1)
+    k = (h_kv @ wk.T).view(T, Hk, hd).transpose(0, 1)
+    v = (h_kv @ wv.T).view(T, Hk, hd).transpose(0, 1)
+    q, k = plain_llama.apply_rope(q, cos[:T], sin[:T]), plain_llama.apply_rope(k, cos[:T], sin[:T])
+    g = H // Hk
+    k = k[:, None].expand(Hk, g, T, hd).reshape(H, T, hd)
+    v = v[:, None].expand(Hk, g, T, hd).reshape(H, T, hd)
+    s = (q @ k.transpose(1, 2)) * hd ** -0.5
+    s = s.masked_fill(~(torch.arange(T)[None, :] <= torch.arange(T)[:, None])[None], float("-inf"))
+    return (torch.softmax(s, -1) @ v).transpose(0, 1).reshape(T, H * hd) @ wo.T
+
+
+def test_step_refuses_what_it_cannot_run(tmp_path):
+    from inf_engine_b200 import OutOfPages
+    d = make_model_dir(tmp_path, "tiny_a")
+    r = runner_for(d, "float32", page_size=16, n_pages=2)
+    r.open("x")
+    with pytest.raises(ValueError, match="vocabulary"):
+        r.step([entry("x", [1, 999])])
+    with pytest.raises(OutOfPages):
+        r.step([entry("x", list(range(40)))])
+    assert r.cache.n_free_pages() == 2 and r.length("x") == 0      # nothing taken
+    with pytest.raises(KeyError):
+        r.step([entry("nobody", [1])])
+    with pytest.raises(ValueError, match="twice"):
+        r.step([entry("x", [1]), entry("x", [2])])
+    assert r.step([entry("x", [1, 2, 3], want=[])]) is None           # nothing wanted: nothing returned
+
+
+# ------------------------------------------------------------------- generation
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
+def test_greedy_generation_through_the_entry_point(tmp_path, name, dtype):
+    from inf_engine_b200 import Engine, Request
+    d = make_model_dir(tmp_path, name)
+    config, weights = plain_inputs(d)
+    vocab = config["vocab_size"]
+    prompts = [random_tokens(vocab, n, 60 + n) for n in (5, 17, 33, 1)]
+    engine = Engine.from_dir(d, dtype=dtype, n_total_blocks=24, block_size=8, max_tokens_per_step=24, chunk=16)
+    out = engine.run_offline([Request(i, p, max_new_tokens=8) for i, p in enumerate(prompts)])
+    for i, p in enumerate(prompts):
+        got = out[i]
+        assert len(got) == 8
+        # every generated token is the plain implementation's choice given the same prefix
+        # (in bfloat16: a token whose plain logit is within rounding of the best)
+        logits = plain_llama.forward_logits(weights, config, p + got)
+        for j, tok in enumerate(got):
+            row = logits[len(p) + j - 1]
+            if dtype == "float32":
+                assert tok == int(row.argmax()), f"{name} request {i} token {j}"
+            else:
+                assert float(row.max() - row[tok]) <= 4e-2 * max(1.0, float(row.abs().max()))
+    assert engine.runner.cache.n_free_pages() == 24 and engine.stats["prefill_tokens"] >= 56
+    if dtype == "float32":
+        assert out[0] == plain_llama.greedy_generate(weights, config, prompts[0], 8)
+
+
+def test_generation_survives_a_pool_that_runs_out(tmp_path):
+    """Pages run out while decoding: the youngest request is preempted and recomputed;
+    every request still gets exactly the tokens it gets when it runs alone."""
+    from inf_engine_b200 import Engine, Request
+    d = make_model_dir(tmp_path, "tiny_a")
+    config, _ = plain_inputs(d)
+    prompts = [random_tokens(config["vocab_size"], n, 80 + n) for n in (30, 21, 26, 9)]
+    alone = Engine.from_dir(d, dtype="float32", n_total_blocks=64, block_size=4)
+    want = [alone.generate(p, 40) for p in prompts]
+    tight = Engine.from_dir(d, dtype="float32", n_total_blocks=40, block_size=4, max_tokens_per_step=32)
+    out = tight.run_offline([Request(i, p, max_new_tokens=40) for i, p in enumerate(prompts)])
+    assert tight.stats["preemptions"] >= 1
+    assert [out[i] for i in range(4)] == want
+    tight.runner.cache.check()
+    assert tight.runner.cache.n_free_pages() == 40
+
+
+def test_sampled_generation_is_seeded_and_independent_of_the_batch(tmp_path):
+    from inf_engine_b200 import Engine, Request, SamplingConfig
+    d = make_model_dir(tmp_path, "tiny_b")
+    config, weights = plain_inputs(d)
+    prompts = [random_tokens(config["vocab_size"], n, 90 + n) for n in (1, 9, 40, 70)]
+    s = SamplingConfig(mode="temperature", temperature=0.7, seed=1)
+    e1 = Engine.from_dir(d, dtype="float32", n_total_blocks=64, block_size=8, max_tokens_per_step=64, chunk=16)
+    batch = e1.run_offline([Request(i, p, 12, sampling=s) for i, p in enumerate(prompts)])
+    e2 = Engine.from_dir(d, dtype="float32", n_total_blocks=64, block_size=8)
+    for i, p in enumerate(prompts):
+        assert e2.generate(p, 12, sampling=s, req_id=i) == batch[i]
+    other = e2.generate(prompts[2], 12, sampling=SamplingConfig(mode="temperature", temperature=0.7, seed=2), req_id=2)
+    assert other != batch[2]
+    # with random weights the distribution is nearly flat: sampling does not repeat the greedy answer
+    assert batch[2] != e2.generate(prompts[2], 12, req_id=2)
+    # stop at EOS: the token is kept and the request ends (engine/llama_paged_engine.py:207-211)
+    eos = batch[3][4]
+    e3 = Engine.from_dir(d, dtype="float32", n_total_blocks=64, block_size=8, eos_token=eos)
+    got = e3.run_offline([Request(3, prompts[3], 12, sampling=s)])[3]
+    assert got == batch[3][:batch[3].index(eos) + 1]
+
+
+def test_command_line(tmp_path):
+    d = make_model_dir(tmp_path, "tiny_a")
+    config, weights = plain_inputs(d)
+    root = Path(__file__).resolve().parent.parent
+    stats = tmp_path / "stats.json"
+    p = subprocess.run([sys.executable, str(root / "bin" / "generate_llama"), "--model-dir", str(d), "--dtype", "float32",
+                        "--prompt-ids", "5,17,3;9,9,9,9", "--n", "6", "--stats-json", str(stats)],
+                       capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    lines = [l for l in p.stdout.splitlines() if ":" in l]
+    got = {int(l.split(":")[0]): [int(t) for t in l.split(":")[1].split(",")] for l in lines}
+    assert got[0] == plain_llama.greedy_generate(weights, config, [5, 17, 3], 6)
+    assert got[1] == plain_llama.greedy_generate(weights, config, [9, 9, 9, 9], 6)
+    assert json.loads(stats.read_text())["new_tokens"] == 12

@@ -1,0 +1,352 @@
+"""Each CUDA kernel alone against a plain float32 PyTorch reference of the same
+operation, at sizes other than the engine's."""
+
+import math
+
+import pytest
+import torch
+
+import plain_llama
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def k():
+    from inf_engine_b200 import kernels
+    return kernels
+
+
+def tol(dtype):
+    return dict(atol=2e-6, rtol=1e-5) if dtype is torch.float32 else dict(atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("table_dtype", DTYPES)
+def test_embed_gather(table_dtype):
+    torch.manual_seed(0)
+    table = torch.randn(301, 200, device=DEV).to(table_dtype)
+    ids = torch.randint(0, 301, (37,), device=DEV, dtype=torch.int32)
+    out = torch.empty(37, 200, device=DEV)
+    k().embed_gather(ids, table, out)
+    assert torch.equal(out, table.float()[ids.long()])
+
+
+@pytest.mark.parametrize("act", DTYPES)
+@pytest.mark.parametrize("gain_dtype", DTYPES)
+@pytest.mark.parametrize("d", [48, 300, 2050])
+def test_rmsnorm_with_residual_sum(act, gain_dtype, d):
+    torch.manual_seed(1)
+    n, eps = 19, 3e-6
+    res = torch.randn(n, d, device=DEV) * 3
+    delta = (torch.randn(n, d, device=DEV)).to(act)
+    gain = (1 + 0.1 * torch.randn(d, device=DEV)).to(gain_dtype)
+    ref_sum = res + delta.float()
+    ref = plain_llama.rms_norm(ref_sum.cpu(), gain.float().cpu(), eps)
+    out = torch.empty(n, d, device=DEV, dtype=act)
+    r = res.clone()
+    k().rmsnorm(r, delta, gain, out, eps)
+    assert torch.allclose(r, ref_sum, atol=0, rtol=0)                  # the residual took the sum, in float32
+    assert torch.allclose(out.float().cpu(), ref, **tol(act))
+    # without a delta, and on gathered rows (the residual is left alone)
+    r2 = res.clone()
+    rows = torch.tensor([5, 0, 18], device=DEV, dtype=torch.int32)
+    out2 = torch.empty(3, d, device=DEV, dtype=act)
+    k().rmsnorm(r2, delta, gain, out2, eps, row_index=rows)
+    assert torch.equal(r2, res)
+    assert torch.allclose(out2.float().cpu(), ref[rows.long().cpu()], **tol(act))
+    out3 = torch.empty(n, d, device=DEV, dtype=act)
+    k().rmsnorm(r2, None, gain, out3, eps)
+    assert torch.allclose(out3.float().cpu(), plain_llama.rms_norm(res.cpu(), gain.float().cpu(), eps), **tol(act))
+
+
+@pytest.mark.parametrize("act", DTYPES)
+def test_rope_and_cache_write(act):
+    torch.manual_seed(2)
+    n, H, Hk, hd, ps, n_pages = 23, 3, 1, 48, 8, 9
+    cfgd = dict(head_dim=hd, hidden_size=H * hd, num_attention_heads=H, rope_theta=20000.0)
+    cos_full, sin_full = plain_llama.rope_tables(cfgd, 500)
+    cos, sin = cos_full[:, :hd // 2].contiguous().to(DEV), sin_full[:, :hd // 2].contiguous().to(DEV)
+    qkv = torch.randn(n, (H + 2 * Hk) * hd, device=DEV).to(act)
+    positions = torch.randint(0, 500, (n,), device=DEV, dtype=torch.int32)
+    slots = torch.randperm(ps * n_pages, device=DEV)[:n].to(torch.int32)
+    slots[3] = -1                                                       # a padding token writes nothing
+    kpool = torch.full((n_pages, Hk, ps, hd), 7.0, device=DEV, dtype=act)
+    vpool = torch.full((n_pages, Hk, ps, hd), 7.0, device=DEV, dtype=act)
+    q0 = qkv[:, :H * hd].float().cpu().view(n, H, hd)
+    k0 = qkv[:, H * hd:(H + Hk) * hd].float().cpu().view(n, Hk, hd)
+    v0 = qkv[:, (H + Hk) * hd:].float().cpu().view(n, Hk, hd)
+    pos = positions.long().cpu()
+    q_ref = torch.stack([plain_llama.apply_rope(q0[i][:, None], cos_full[pos[i]][None], sin_full[pos[i]][None])[:, 0] for i in range(n)])
+    k_ref = torch.stack([plain_llama.apply_rope(k0[i][:, None], cos_full[pos[i]][None], sin_full[pos[i]][None])[:, 0] for i in range(n)])
+    q, kk, v = qkv[:, :H * hd], qkv[:, H * hd:(H + Hk) * hd], qkv[:, (H + Hk) * hd:]
+    k().rope_kv_write(q, kk, v, cos, sin, positions, slots, kpool, vpool, H, Hk, hd, ps)
+    assert torch.allclose(q.float().cpu().view(n, H, hd), q_ref, **tol(act))
+    written = torch.zeros(n_pages, ps, dtype=torch.bool)
+    for i in range(n):
+        s = int(slots[i])
+        if s < 0:
+            continue
+        page, off = divmod(s, ps)
+        written[page, off] = True
+        assert torch.allclose(kpool[page, :, off].float().cpu(), k_ref[i], **tol(act))
+        assert torch.equal(vpool[page, :, off].float().cpu(), v0[i])
+    untouched = kpool.float().cpu()[~written[:, None, :].expand(n_pages, Hk, ps)]
+    assert (untouched == 7.0).all()
+
+
+@pytest.mark.parametrize("act", DTYPES)
+def test_silu_mul(act):
+    torch.manual_seed(3)
+    n, inter = 13, 328
+    gu = (torch.randn(n, 2 * inter, device=DEV) * 3).to(act)
+    out = torch.empty(n, inter, device=DEV, dtype=act)
+    k().silu_mul(gu, out)
+    g, u = gu.float().cpu()[:, :inter], gu.float().cpu()[:, inter:]
+    assert torch.allclose(out.float().cpu(), plain_llama.silu(g) * u, **tol(act))
+
+
+@pytest.mark.parametrize("a_dt,w_dt,c_dt", [(torch.float32,) * 3, (torch.float32, torch.bfloat16, torch.float32),
+                                            (torch.bfloat16, torch.float32, torch.bfloat16),
+                                            (torch.bfloat16, torch.bfloat16, torch.float32),
+                                            (torch.bfloat16, torch.bfloat16, torch.bfloat16)])
+def test_gemm_simt_is_float32_and_batch_invariant(a_dt, w_dt, c_dt):
+    torch.manual_seed(4)
+    M, N, K = 37, 101, 77
+    a = torch.randn(M, K, device=DEV).to(a_dt)
+    w = torch.randn(N, K, device=DEV).to(w_dt)
+    out = torch.empty(M, N, device=DEV, dtype=c_dt)
+    k().gemm_simt(a, w, out)
+    ref = (a.double().cpu() @ w.double().cpu().T).float()
+    assert torch.allclose(out.float().cpu(), ref, **(dict(atol=1e-4, rtol=1e-5) if c_dt is torch.float32 else tol(c_dt)))
+    one = torch.empty(1, N, device=DEV, dtype=c_dt)
+    k().gemm_simt(a[5:6], w, one)
+    assert torch.equal(one[0], out[5])                                   # a row does not depend on its neighbours
+    # strided output (a column slice of a wider buffer)
+    wide = torch.zeros(M, N + 11, device=DEV, dtype=c_dt)
+    k().gemm_simt(a, w, wide[:, 11:])
+    assert torch.equal(wide[:, 11:], out) and float(wide[:, :11].abs().sum()) == 0
+
+
+def paged_reference(q, kd, vd, q_lens, ctx_before, H, Hk, hd, window):
+    """Dense float32 attention per request: q [N, H*hd]; kd/vd lists of [S_r, Hk, hd]."""
+    outs = []
+    g = H // Hk
+    n0 = 0
+    for r, ql in enumerate(q_lens):
+        S = ctx_before[r] + ql
+        kk = kd[r][:S].repeat_interleave(g, dim=1).transpose(0, 1)       # [H, S, hd]
+        vv = vd[r][:S].repeat_interleave(g, dim=1).transpose(0, 1)
+        qq = q[n0:n0 + ql].view(ql, H, hd).transpose(0, 1)               # [H, ql, hd]
+        s = (qq @ kk.transpose(1, 2)) * hd ** -0.5
+        i = torch.arange(ql)[:, None] + ctx_before[r]
+        j = torch.arange(S)[None, :]
+        ok = j <= i
+        if window:
+            ok &= j > i - window
+        s = s.masked_fill(~ok[None], float("-inf"))
+        outs.append((torch.softmax(s, -1) @ vv).transpose(0, 1).reshape(ql, H * hd))
+        n0 += ql
+    return torch.cat(outs)
+
+
+def paged_case(act, H, Hk, hd, ps, q_lens, ctx_before, seed, spike=False):
+    """Random requests laid out on shuffled pages; returns everything the kernels need."""
+    g = torch.Generator().manual_seed(seed)
+    R = len(q_lens)
+    lens = [c + q for c, q in zip(ctx_before, q_lens)]
+    n_pages_r = [-(-s // ps) for s in lens]
+    n_pages = sum(n_pages_r) + 3
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    width = max(n_pages_r) + 2
+    table = torch.full((R, width), -1, dtype=torch.int32)
+    kpool = torch.full((n_pages, Hk, ps, hd), float("nan"))
+    vpool = torch.full((n_pages, Hk, ps, hd), float("nan"))
+    kd, vd = [], []
+    for r in range(R):
+        kr = torch.randn(lens[r], Hk, hd, generator=g)
+        vr = torch.randn(lens[r], Hk, hd, generator=g)
+        pages = [perm.pop() for _ in range(n_pages_r[r])]
+        table[r, :len(pages)] = torch.tensor(pages, dtype=torch.int32)
+        kd.append(kr)
+        vd.append(vr)
+    N = sum(q_lens)
+    q = torch.randn(N, H * hd, generator=g)
+    if spike:
+        # one far key per request stands out for every query head: its score dominates the softmax
+        n0 = 0
+        for r in range(R):
+            far = max(0, ctx_before[r] // 3)
+            kd[r][far] = 0
+            kd[r][far, :, 0] = 30.0
+            q[n0:n0 + q_lens[r]].view(q_lens[r], H, hd)[:, :, 0] = 8.0
+            n0 += q_lens[r]
+    kd = [t.to(act).float() for t in kd]
+    vd = [t.to(act).float() for t in vd]
+    q = q.to(act).float()
+    for r in range(R):
+        for p, page in enumerate(table[r, :n_pages_r[r]].tolist()):
+            n = min(ps, lens[r] - p * ps)
+            kpool[page, :, :n] = kd[r][p * ps:p * ps + n].transpose(0, 1)
+            vpool[page, :, :n] = vd[r][p * ps:p * ps + n].transpose(0, 1)
+    # what lies beyond a request's length on its last page, and pages it does not own, is poison that must never be read
+    kpool = torch.nan_to_num(kpool, nan=1e4)
+    vpool = torch.nan_to_num(vpool, nan=1e4)
+    q_start = [0]
+    for ql in q_lens:
+        q_start.append(q_start[-1] + ql)
+    return dict(q=q, kd=kd, vd=vd, kpool=kpool, vpool=vpool, table=table, q_start=q_start, N=N, R=R)
+
+
+def work_list(q_lens, group, rows):
+    req, pair0 = [], []
+    for r, ql in enumerate(q_lens):
+        for p in range(0, ql * group, rows):
+            req.append(r)
+            pair0.append(p)
+    return req, pair0
+
+
+CASES = [
+    # H, Hk, hd, page, q_lens, ctx_before, window
+    (4, 2, 16, 16, [33], [0], None),
+    (6, 2, 32, 8, [1, 9, 1, 40], [70, 0, 129, 31], None),
+    (3, 1, 48, 8, [5, 1], [11, 200], None),
+    (8, 8, 64, 16, [17, 1, 1], [0, 300, 15], None),
+    (4, 1, 128, 16, [20, 1], [50, 333], None),
+    (2, 1, 256, 4, [3, 1], [9, 40], None),
+    (4, 2, 32, 8, [30, 1, 7], [0, 90, 41], 13),
+    (5, 5, 80, 16, [2, 64], [62, 0], 33),
+]
+
+
+@pytest.mark.parametrize("act", DTYPES)
+@pytest.mark.parametrize("case", CASES)
+def test_attention_general(act, case):
+    H, Hk, hd, ps, q_lens, ctx_before, window = case
+    c = paged_case(act, H, Hk, hd, ps, q_lens, ctx_before, seed=hd + len(q_lens))
+    ref = paged_reference(c["q"], c["kd"], c["vd"], q_lens, ctx_before, H, Hk, hd, window)
+    req, pair0 = work_list(q_lens, H // Hk, 32)
+    dev = lambda t, dt=torch.int32: torch.as_tensor(t, dtype=dt).to(DEV)
+    out = torch.full((c["N"], H * hd), float("nan"), device=DEV, dtype=act)
+    k().attention_general(c["q"].to(DEV, act), out, c["kpool"].to(DEV, act), c["vpool"].to(DEV, act),
+                          c["table"].to(DEV), dev(c["q_start"]), dev(ctx_before), dev(req), dev(pair0), len(req),
+                          H, Hk, hd, ps, window, hd ** -0.5)
+    assert torch.allclose(out.float().cpu(), ref, **(dict(atol=1e-5, rtol=1e-5) if act is torch.float32 else tol(act)))
+
+
+@pytest.mark.parametrize("act", DTYPES)
+def test_attention_finds_one_far_key_among_hundreds(act):
+    H, Hk, hd, ps = 4, 2, 32, 8
+    q_lens, ctx_before = [1, 6], [700, 420]
+    c = paged_case(act, H, Hk, hd, ps, q_lens, ctx_before, seed=11, spike=True)
+    ref = paged_reference(c["q"], c["kd"], c["vd"], q_lens, ctx_before, H, Hk, hd, None)
+    # the reference itself is, to rounding, the value stored at the far key
+    far0 = c["vd"][0][700 // 3].repeat_interleave(2, dim=0).reshape(-1)
+    assert torch.allclose(ref[0], far0, atol=1e-3)
+    req, pair0 = work_list(q_lens, 2, 32)
+    dev = lambda t: torch.as_tensor(t, dtype=torch.int32).to(DEV)
+    out = torch.empty((c["N"], H * hd), device=DEV, dtype=act)
+    k().attention_general(c["q"].to(DEV, act), out, c["kpool"].to(DEV, act), c["vpool"].to(DEV, act),
+                          c["table"].to(DEV), dev(c["q_start"]), dev(ctx_before), dev(req), dev(pair0), len(req),
+                          H, Hk, hd, ps, None, hd ** -0.5)
+    assert torch.allclose(out.float().cpu(), ref, **(dict(atol=1e-5, rtol=1e-5) if act is torch.float32 else tol(act)))
+
+
+def test_attention_refuses_head_sizes_it_cannot_take():
+    from inf_engine_b200.kernels import KernelError
+    z = torch.zeros(1, device=DEV)
+    zi = torch.zeros(2, device=DEV, dtype=torch.int32)
+    with pytest.raises(KernelError, match="size"):
+        k().attention_general(z.view(1, 1), z.view(1, 1), z, z, zi.view(1, 2), zi, zi, zi, zi, 1, 1, 1, 24, 8, None, 1.0)
+
+
+# ------------------------------------------------------------------------ sampling
+def test_argmax_takes_the_first_maximum():
+    torch.manual_seed(5)
+    logits = torch.randn(9, 3001, device=DEV)
+    logits[2, 77] = logits[2, 1500] = 50.0
+    out = torch.empty(9, device=DEV, dtype=torch.int32)
+    k().argmax(logits, out)
+    ref = logits.cpu().argmax(-1)
+    assert out.cpu().tolist() == ref.tolist() and out[2] == 77
+
+
+def test_repetition_penalty():
+    torch.manual_seed(6)
+    logits = torch.randn(3, 500, device=DEV)
+    ctx = torch.full((3, 256), -1, dtype=torch.int32)
+    seen = [[4, 9, 4, 499, 0], [], [7] * 40]
+    for i, s in enumerate(seen):
+        ctx[i, :len(s)] = torch.tensor(s, dtype=torch.int32)
+    pen = torch.tensor([1.3, 1.0, 2.0], device=DEV)
+    ref = torch.stack([plain_llama.apply_repetition_penalty(logits[i].cpu(), seen[i], float(pen[i])) for i in range(3)])
+    k().repetition_penalty(logits, ctx.to(DEV), pen)
+    assert torch.allclose(logits.cpu(), ref, atol=1e-6)
+
+
+def _rows(configs, keys, vocab):
+    import numpy as np
+    from inf_engine_b200.sampling import SamplingMode
+    rows = np.zeros((len(configs), 7), dtype=np.int32)
+    f, u = rows.view(np.float32), rows.view(np.uint32)
+    for i, c in enumerate(configs):
+        if c.mode is SamplingMode.GREEDY:
+            f[i, 0], f[i, 1] = 0.0, 1.0
+        else:
+            f[i, 0] = c.temperature
+            f[i, 1] = c.top_p if c.mode is SamplingMode.TOP_P else 1.0
+            rows[i, 2] = max(1, min(c.top_k, vocab)) if c.mode is SamplingMode.TOP_K else 0
+        u[i, 3], u[i, 4] = c.seed & 0xFFFFFFFF, c.seed >> 32
+        u[i, 5], u[i, 6] = keys[i] & 0xFFFFFFFF, keys[i] >> 32
+    return torch.from_numpy(rows).to(DEV)
+
+
+@pytest.mark.parametrize("vocab", [389, 5003])
+def test_sampling_follows_the_plain_distribution_and_the_hashed_uniform(vocab):
+    from inf_engine_b200.sampling import SamplingConfig, uniform_of
+    torch.manual_seed(7)
+    modes = [("greedy", {}), ("temperature", dict(temperature=0.7)), ("top_k", dict(top_k=5, temperature=1.3)),
+             ("top_p", dict(top_p=0.6, temperature=0.9)), ("top_p", dict(top_p=1.0)), ("top_k", dict(top_k=10 ** 6))]
+    n_draws = 40
+    configs, keys = [], []
+    for mode, kw in modes:
+        for d in range(n_draws):
+            configs.append(SamplingConfig(mode=mode, seed=1234 + len(mode), **kw))
+            keys.append((3 << 32) | d)
+    logits = (torch.randn(len(modes), vocab) * 2.5)
+    logits[2, 10] = logits[2, 20] = logits[2].topk(5).values[-1]        # a tie on the top-k edge: both stay
+    big = logits.repeat_interleave(n_draws, dim=0).contiguous().to(DEV)
+    out = torch.empty(big.shape[0], device=DEV, dtype=torch.int32)
+    k().sample(big, _rows(configs, keys, vocab), out)
+    out = out.cpu().tolist()
+    for i, c in enumerate(configs):
+        row = logits[i // n_draws]
+        probs = plain_llama.filtered_distribution(row, c.mode.value, c.temperature, c.top_k, c.top_p).double()
+        tok = out[i]
+        assert probs[tok] > 0, f"{c.mode} drew token {tok} that the filter removed"
+        if c.mode.value == "greedy":
+            assert tok == int(row.argmax())
+            continue
+        cdf = probs.cumsum(0)
+        u = uniform_of(c.seed, keys[i])
+        lo = float(cdf[tok - 1]) if tok > 0 else 0.0
+        assert lo - 1e-5 <= u <= float(cdf[tok]) + 1e-5, f"{c.mode}: u={u} outside [{lo}, {float(cdf[tok])}] of token {tok}"
+    # the draws of one row spread over several tokens (the hash differs with the key)
+    assert len(set(out[n_draws:2 * n_draws])) >= 2
+
+
+def test_sampling_is_reproducible_and_independent_of_the_batch():
+    from inf_engine_b200.sampling import SamplingConfig
+    torch.manual_seed(8)
+    logits = torch.randn(6, 1000, device=DEV)
+    cfgs = [SamplingConfig(mode="top_p", top_p=0.8, temperature=1.1, seed=5) for _ in range(6)]
+    keys = [(i << 32) | 4 for i in range(6)]
+    a = torch.empty(6, device=DEV, dtype=torch.int32)
+    b = torch.empty(6, device=DEV, dtype=torch.int32)
+    k().sample(logits, _rows(cfgs, keys, 1000), a)
+    k().sample(logits, _rows(cfgs, keys, 1000), b)
+    assert torch.equal(a, b)
+    one = torch.empty(1, device=DEV, dtype=torch.int32)
+    k().sample(logits[4:5], _rows(cfgs[4:5], keys[4:5], 1000), one)
+    assert int(one[0]) == int(a[4])

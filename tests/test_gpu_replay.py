@@ -1,0 +1,95 @@
+"""Trace replay through ``bin/trace_run`` as a user runs it, compared with the
+plain implementation: each request alone and whole; most of it in one step and
+the last 32 tokens one by one; in portions of changing size down to two tokens;
+and mixed, up to four live requests, portions of some beside decoded tokens of
+others, in a pool so small that pages are used again.  In 32-bit and bfloat16."""
+
+import random
+
+import pytest
+import torch
+
+import plain_llama
+from helpers import TINY, TraceBuilder, assert_close, make_model_dir, plain_inputs, random_tokens, run_trace
+
+pytestmark = pytest.mark.gpu
+
+LENGTHS = {"tiny_a": [70, 45, 130, 20, 97, 33, 150], "tiny_b": [64, 129, 40, 200, 31, 16, 77]}
+PAGE = {"tiny_a": 16, "tiny_b": 8}
+
+
+def schedules(name: str, requests: dict[str, list[int]], seed: int) -> TraceBuilder:
+    rng = random.Random(seed)
+    t = TraceBuilder()
+    ids = list(requests)
+    # (1) each request alone and whole
+    for rid in ids[:3]:
+        t.step([("w" + rid, requests[rid], 0)], end=["w" + rid])
+    # (2) most of it in one step, the last 32 tokens one by one
+    for rid in ids[:2]:
+        toks = requests[rid]
+        cut = len(toks) - 32
+        t.step([("d" + rid, toks[:cut], 0)])
+        for p in range(cut, len(toks)):
+            t.step([("d" + rid, toks[p:p + 1], p)], end=["d" + rid] if p == len(toks) - 1 else [])
+    # (3) portions of changing size, down to two tokens
+    for rid in ids[2:4]:
+        toks, p = requests[rid], 0
+        sizes = [7, 2, 16, 3, 2, 17, 2, 31, 1, 5]
+        i = 0
+        while p < len(toks):
+            n = min(sizes[i % len(sizes)], len(toks) - p)
+            t.step([("p" + rid, toks[p:p + n], p)], end=["p" + rid] if p + n == len(toks) else [])
+            p += n
+            i += 1
+    # (4) mixed: up to four live, portions beside decoded tokens, some left out of a step
+    waiting = [("m" + rid, requests[rid]) for rid in ids]
+    live: dict[str, list] = {}
+    while waiting or live:
+        while waiting and len(live) < 4:
+            rid, toks = waiting.pop(0)
+            live[rid] = [toks, 0, len(toks) - rng.choice([3, 9, 20])]       # tokens, done, where decoding starts
+        entries, ended = [], []
+        for rid, st in list(live.items()):
+            toks, done, decode_from = st
+            if rng.random() < 0.2 and len(live) > 1:
+                continue                                                      # left out of this step
+            n = 1 if done >= decode_from else min(rng.choice([2, 3, 5, 11, 17, 40]), decode_from - done)
+            entries.append((rid, toks[done:done + n], done))
+            st[1] = done + n
+            if st[1] == len(toks):
+                ended.append(rid)
+                del live[rid]
+        if entries:
+            t.step(entries, end=ended)
+    return t
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
+def test_replay_under_every_cut(tmp_path, name, dtype):
+    model_dir = make_model_dir(tmp_path, name)
+    config, weights = plain_inputs(model_dir)
+    vocab = config["vocab_size"]
+    requests = {str(i): random_tokens(vocab, n, 100 + i) for i, n in enumerate(LENGTHS[name])}
+    trace = schedules(name, requests, seed=len(name))
+    # the pool is exactly what the trace holds at its fullest, so pages of finished requests are used again
+    assert trace.max_tokens < sum(len(v) for v in requests.values())
+    got = run_trace(model_dir, dtype, trace, tmp_path / "out", vocab, page_size=PAGE[name])
+    plain = {rid: plain_llama.forward_logits(weights, config, toks) for rid, toks in requests.items()}
+    by_request: dict[str, list] = {}
+    for (rid, pos), row in got.items():
+        by_request.setdefault(rid, []).append((pos, row))
+    assert len(by_request) == 3 + 2 + 2 + len(requests)
+    for rid, rows in by_request.items():
+        rows.sort(key=lambda x: x[0])
+        ref = plain[rid[1:]]
+        assert [p for p, _ in rows] == list(range(ref.shape[0])), f"{rid}: positions missing"
+        assert_close(torch.stack([r for _, r in rows]), ref, dtype, what=f"{name} {dtype} request {rid}")
+    if dtype == "float32":
+        # in 32-bit the cuts agree with each other far below the tolerance against the plain implementation
+        for rid in list(requests)[:2]:
+            whole = torch.stack([got[("w" + rid, p)] for p in range(len(requests[rid]))])
+            cut = torch.stack([got[("d" + rid, p)] for p in range(len(requests[rid]))])
+            mixed = torch.stack([got[("m" + rid, p)] for p in range(len(requests[rid]))])
+            assert float((whole - cut).abs().max()) < 1e-6 and float((whole - mixed).abs().max()) < 1e-6
