@@ -1,0 +1,294 @@
+"""Benchmark of the engine on one B200: decode tokens per second at batch 8 (and 1
+and 64), prefill of one 2,048-token prompt, at Llama-3.2-1B size with random
+weights and uniform random prompt ids.
+
+    python bench.py --gpus 1 --steps K --warmup W      -> one JSON line
+    python bench.py --impl reference ...               -> the reference arm (or why it is unavailable)
+
+A "step" is one decode step of the whole batch.  ``value`` is device-timed
+(CUDA events around K steps fed from the device); ``e2e`` is the same through
+``Engine.step`` with host tokens in and out every step.  Weights (2.5 GB) are
+larger than L2, so every step streams them from HBM: no L2 flush is needed.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+PROMPT_LEN = 2048
+POOL_CONTEXT = 4096
+PAGE = 16
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            d = json.load(open(path))
+            out = dict(FALLBACK_PEAKS)
+            for k in out:
+                if isinstance(d.get(k), (int, float)):
+                    out[k] = float(d[k])
+            out["source"] = "measured"
+            return out
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region is timed."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.samples = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append((time.perf_counter(), line.strip()))
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+
+    def summary(self, t0, t1):
+        sm, mx, reasons = [], 0, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for t, line in self.samples:
+            if not (t0 - 0.05 <= t <= t1 + 0.15):
+                continue
+            parts = [p.strip() for p in line.split(",")]
+            try:
+                sm.append(int(parts[0]))
+                mx = max(mx, int(parts[1]))
+            except (ValueError, IndexError):
+                continue
+            for n, v in zip(names, parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx or None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def model_numbers(cfg):
+    d, L, H, Hk, hd, I, V = (cfg.hidden_size, cfg.num_hidden_layers, cfg.num_attention_heads,
+                             cfg.num_key_value_heads, cfg.head_dim, cfg.intermediate_size, cfg.vocab_size)
+    per_layer = (H * hd + 2 * Hk * hd) * d + d * H * hd + 3 * I * d
+    linear_params = L * per_layer
+    head_params = V * d
+    weight_bytes = 2 * (linear_params + head_params) + 2 * 2 * L * d + 2 * d       # bf16; norms are small
+    kv_bytes_per_token = 2 * L * Hk * hd * 2
+    return dict(linear_params=linear_params, head_params=head_params, weight_bytes=weight_bytes,
+                kv_bytes_per_token=kv_bytes_per_token)
+
+
+def prefill_flops(cfg, n):
+    m = model_numbers(cfg)
+    attn = cfg.num_hidden_layers * 4 * cfg.num_attention_heads * cfg.head_dim * (n * (n + 1) // 2)
+    return 2 * n * m["linear_params"] + attn + 2 * m["head_params"]
+
+
+def run_ours(args):
+    import numpy as np
+    import torch
+
+    from inf_engine_b200 import Engine, Request, SamplingConfig, StepEntry, kernels
+    from inf_engine_b200.config import get_preset
+    from inf_engine_b200.sampling import pack_rows, request_key
+    from inf_engine_b200.weights import write_random_model
+
+    cfg = get_preset(args.model)
+    n_layers_full = cfg.num_hidden_layers
+    if args.layers:
+        import dataclasses
+        cfg = dataclasses.replace(cfg, num_hidden_layers=args.layers)
+    pk = peaks()
+    torch.cuda.set_device(0)
+    t_build = time.perf_counter()
+    with tempfile.TemporaryDirectory(prefix="bench_model_") as tmp:
+        write_random_model(cfg, args.seed, tmp)
+        engine = Engine.from_dir(tmp, dtype="bfloat16", n_total_blocks=64 * POOL_CONTEXT // PAGE, block_size=PAGE,
+                                 max_requests=64, max_tokens_per_step=8192, chunk=2048)
+    t_build = time.perf_counter() - t_build
+    runner = engine.runner
+    V = cfg.vocab_size
+    rng = np.random.default_rng(args.seed)
+    nums = model_numbers(cfg)
+    clocks = ClockSampler()
+    clocks.start()
+
+    def prompt():
+        return rng.integers(0, V, PROMPT_LEN).tolist()
+
+    # ---------------------------------------------------------------- prefill
+    def prefill_once():
+        runner.open("p")
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        toks = prompt()
+        torch.cuda.synchronize()
+        e0.record()
+        runner.step([StepEntry("p", toks, [PROMPT_LEN - 1])])
+        e1.record()
+        torch.cuda.synchronize()
+        runner.close("p")
+        return e0.elapsed_time(e1)
+
+    for _ in range(3):
+        prefill_once()
+    pre_ms = sorted(prefill_once() for _ in range(args.prefill_reps))
+    pre = pre_ms[len(pre_ms) // 2]
+    prefill = {"value": PROMPT_LEN / pre * 1e3, "unit": "tok/s", "tokens": PROMPT_LEN, "ms": pre,
+               "frac": prefill_flops(cfg, PROMPT_LEN) / (pre * 1e-3) / (pk["bf16_tflops"] * 1e12),
+               "peak_tflops": pk["bf16_tflops"], "peak_source": pk["source"]}
+
+    # ----------------------------------------------------------------- decode
+    greedy = SamplingConfig()
+
+    def decode_device(batch, steps, warmup):
+        """Device-timed decode: K steps, each fed the ids the step before sampled, no host read inside."""
+        rids = [f"d{batch}_{i}" for i in range(batch)]
+        for rid in rids:
+            runner.open(rid)
+        for i in range(0, batch, 4):                      # prompts, four at a time
+            runner.step([StepEntry(r, prompt(), []) for r in rids[i:i + 4]])
+        rows = pack_rows([greedy] * batch, [request_key(i, 0) for i in range(batch)], V)
+        ids = torch.as_tensor(rng.integers(0, V, batch), dtype=torch.int32).cuda()
+        entries = [StepEntry(r, [0], [0]) for r in rids]
+        for _ in range(warmup):
+            _, ids = runner.step_and_sample(entries, rows, device_tokens=ids)
+        torch.cuda.synchronize()
+        ctx0 = runner.length(rids[0])
+        n0 = kernels.LAUNCHES
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        e0.record()
+        for _ in range(steps):
+            _, ids = runner.step_and_sample(entries, rows, device_tokens=ids)
+        e1.record()
+        torch.cuda.synchronize()
+        t1 = time.perf_counter()
+        ms = e0.elapsed_time(e1)
+        launches = kernels.LAUNCHES - n0
+        for rid in rids:
+            runner.close(rid)
+        mean_ctx = ctx0 + steps / 2
+        bytes_step = nums["weight_bytes"] + batch * mean_ctx * nums["kv_bytes_per_token"]
+        return dict(tok_s=batch * steps / ms * 1e3, ms_per_step=ms / steps, launches=launches, t0=t0, t1=t1,
+                    bytes_step=bytes_step, ctx=(ctx0, ctx0 + steps))
+
+    def decode_e2e(batch, steps, warmup):
+        """Through Engine.step: host tokens in (one pinned copy a step), sampled ids out (one read a step)."""
+        reqs = [Request(1000 + i, prompt(), max_new_tokens=warmup + steps + 8) for i in range(batch)]
+        for r in reqs:
+            assert engine.submit(r), r.error
+        while any(len(r.generated) < 1 for r in reqs):
+            engine.step()
+        for _ in range(warmup):
+            engine.step()
+        torch.cuda.synchronize()
+        n_before = sum(len(r.generated) for r in reqs)
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            engine.step()
+        torch.cuda.synchronize()
+        t1 = time.perf_counter()
+        n_tok = sum(len(r.generated) for r in reqs) - n_before
+        while engine.has_work:
+            engine.step()
+        engine.completed.clear()
+        b = next(iter(runner.graphs._buckets.values()))
+        key = [k for k in runner.graphs._buckets if k[0] >= batch]
+        h2d = min(runner.graphs._buckets[k].n for k in key) * 4 if key else 0
+        return dict(tok_s=n_tok / (t1 - t0), h2d=h2d, d2h=4 * batch)
+
+    main = decode_device(args.batch, args.steps, args.warmup)
+    e2e = decode_e2e(args.batch, args.steps, args.warmup)
+    points = {}
+    for b in (1, 64):
+        points[f"decode_b{b}"] = decode_device(b, args.steps, args.warmup)["tok_s"]
+    clocks.stop()
+    clk = clocks.summary(main["t0"], main["t1"])
+
+    achieved = main["bytes_step"] / (main["ms_per_step"] * 1e-3) / 1e9
+    out = {
+        "metric": "decode tok/s at batch 8 (Llama-3.2-1B size, random weights)",
+        "value": main["tok_s"], "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": main["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: seeded random weights, uniform random prompt ids", "impl": "ours",
+        "config": {
+            "model": args.model, "layers": cfg.num_hidden_layers, "layers_of_model": n_layers_full,
+            "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
+            "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
+            "global_batch": args.batch, "seq_len": PROMPT_LEN, "context_start": main["ctx"][0],
+            "context_end": main["ctx"][1], "pool_context": POOL_CONTEXT, "page_size": PAGE,
+            "parallelism": "single-gpu", "l2": "inputs larger than L2 (weights 2.5 GB per step)",
+            "decode": "cuda graph per batch bucket, sampling in graph",
+        },
+        "e2e": {"value": e2e["tok_s"], "unit": "tok/s", "h2d_bytes_per_step": e2e["h2d"],
+                "d2h_bytes_per_step": e2e["d2h"]},
+        "gpu_launches": main["launches"],
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": achieved / pk["hbm_gbs"], "peak_source": pk["source"]},
+        "points": points,
+        "clocks": clk,
+        "build_s": t_build,
+    }
+    print(json.dumps(out))
+    return 0
+
+
+def run_reference(args):
+    print(json.dumps({"impl": "reference", "unavailable":
+                      "the reference has no setup.py or pyproject.toml: pip install --no-index of it fails "
+                      "('not installable'), so no unmodified install exists under baseline/_ref"}))
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="llama-3.2-1b")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (0: all)")
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--prefill-reps", type=int, default=7)
+    args = ap.parse_args()
+    if args.gpus != 1:
+        print(f"bench.py measures a single-GPU engine; --gpus {args.gpus} is not supported (use --gpus 1)")
+        return 2
+    if args.impl == "reference":
+        return run_reference(args)
+    args.warmup = max(args.warmup, 3)
+    return run_ours(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

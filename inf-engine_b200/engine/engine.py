@@ -17,7 +17,7 @@ from pathlib import Path
 import torch
 
 from ..config.registry import detect_config, get_preset
-from ..sampling.sampler import Sampler, SamplingConfig, request_key
+from ..sampling.sampler import Sampler, SamplingConfig, pack_rows, request_key
 from ..weights.random_init import write_random_model
 from .batch import StepEntry
 from .runner import ModelRunner
@@ -80,16 +80,22 @@ class Engine:
             return []
         entries = [StepEntry(e.request.req_id, e.tokens, [len(e.tokens) - 1] if e.wants_logits else [])
                    for e in plan.entries]
-        logits = self.runner.step(entries)
         sampled = {}
         wanted = [e for e in plan.entries if e.wants_logits]
-        if wanted:
-            configs = [e.request.sampling or self.cfg for e in wanted]
-            keys = [request_key(e.request.req_id, len(e.request.generated)) for e in wanted]
-            contexts = None
-            if any(c.repetition_penalty != 1.0 for c in configs):
+        configs = [e.request.sampling or self.cfg for e in wanted]
+        keys = [request_key(e.request.req_id, len(e.request.generated)) for e in wanted]
+        if wanted and all(c.repetition_penalty == 1.0 for c in configs):
+            # sampling rides in the step (inside the CUDA graph of a decode step)
+            rows = pack_rows(configs, keys, self.runner.spec.vocab_size)
+            _, ids = self.runner.step_and_sample(entries, rows)
+        else:
+            logits = self.runner.step(entries)
+            ids = None
+            if wanted:
                 contexts = [e.request.generated for e in wanted]
-            ids = self.sampler.sample(logits, configs, keys, contexts).tolist()   # the step's one device-to-host read
+                ids = self.sampler.sample(logits, configs, keys, contexts)
+        if wanted:
+            ids = ids.tolist()                                   # the step's one device-to-host read
             sampled = {e.request.req_id: t for e, t in zip(wanted, ids)}
         for e in plan.entries:
             self.stats["decode_tokens" if len(e.tokens) == 1 and e.request.generated else "prefill_tokens"] += len(e.tokens)

@@ -20,6 +20,7 @@ from ..parts.registry import expected_tensors
 from ..parts.runtime import Runtime
 from ..weights.loader import load_weights
 from .batch import StepEntry, build_context
+from .graphs import DecodeGraphs
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
 
@@ -39,7 +40,7 @@ def parse_dtype(dtype) -> torch.dtype:
 
 class ModelRunner:
     def __init__(self, config, tensors: dict, dtype, device="cuda:0", page_size: int = 16, n_pages: int = 256,
-                 max_requests: int = 64, spec=None):
+                 max_requests: int = 64, spec=None, use_graphs: bool = True):
         self.config = config
         self.spec = spec if spec is not None else config.model_spec()
         self.dtype = parse_dtype(dtype)
@@ -54,6 +55,8 @@ class ModelRunner:
         self.model.bind_cache(self.cache)
         self.page_size = page_size
         self.steps = 0
+        self.use_graphs = use_graphs
+        self.graphs = DecodeGraphs(self)
 
     # ------------------------------------------------------------ construction
     @classmethod
@@ -81,8 +84,14 @@ class ModelRunner:
     def step(self, entries: list[StepEntry]) -> torch.Tensor | None:
         """Run one batch.  Returns float32 logits [n_wanted, vocab] on the device
         (a view of a buffer that the next step overwrites) or None."""
+        return self.step_and_sample(entries, None)[0]
+
+    def step_and_sample(self, entries: list[StepEntry], sample_rows=None, device_tokens=None):
+        """``step`` plus, when ``sample_rows`` (int32 numpy [n_wanted, 7] records of
+        ``sampling.Sampler.pack``) is given, the sampled token ids (int32, device).
+        Steps that are all single decode tokens replay a CUDA graph."""
         if not entries:
-            return None
+            return None, None
         cache = self.cache
         seen = set()
         for e in entries:
@@ -109,9 +118,20 @@ class ModelRunner:
         for e in entries:
             ok = cache.reserve(e.rid, cache.lengths[e.rid] + len(e.tokens))
             assert ok
-        ctx = build_context(self.rt, cache, entries)
-        logits = self.model.forward(ctx)
+        sampled = None
+        if self.use_graphs and self.graphs.usable(entries):
+            logits, sampled = self.graphs.step(entries, sample_rows, device_tokens)
+        else:
+            ctx = build_context(self.rt, cache, entries)
+            if device_tokens is not None:
+                ctx.token_ids.copy_(device_tokens)
+            logits = self.model.forward(ctx)
+            if sample_rows is not None and logits is not None:
+                from .. import kernels
+                rows = self.rt.staging.upload(sample_rows.reshape(-1)).view(-1, 7)
+                sampled = self.rt.ws.take("sampled", (logits.shape[0],), torch.int32)
+                kernels.sample(logits, rows, sampled)
         for e in entries:
             cache.advance(e.rid, cache.lengths[e.rid] + len(e.tokens))
         self.steps += 1
-        return logits
+        return logits, sampled

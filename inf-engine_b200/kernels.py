@@ -31,7 +31,12 @@ def dtype_code(dtype: torch.dtype) -> int:
         raise KernelError(f"kernels take float32 and bfloat16, not {dtype}") from None
 
 
+LAUNCHES = 0     # launchers called so far (graph replays add what their capture counted)
+
+
 def _check(status: int, what: str) -> None:
+    global LAUNCHES
+    LAUNCHES += 1
     if status == 0:
         return
     if status < 0:

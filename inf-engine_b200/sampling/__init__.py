@@ -3,6 +3,7 @@ from .sampler import (
     Sampler,
     SamplingConfig,
     SamplingMode,
+    pack_rows,
     request_key,
     splitmix64,
     uniform_of,

@@ -72,6 +72,27 @@ def request_key(request_id: int, position: int) -> int:
     return ((int(request_id) & 0xFFFFFFFF) << 32) | (int(position) & 0xFFFFFFFF)
 
 
+def pack_rows(configs: list[SamplingConfig], keys: list[int], vocab: int) -> np.ndarray:
+    """The sampling kernel's records, int32 [n, 7]: temperature (float bits; <= 0 is greedy),
+    top_p (float bits; >= 1 is off), top_k (<= 0 is off), seed low/high, key low/high."""
+    m = len(configs)
+    rows = np.zeros((m, 7), dtype=np.int32)
+    f = rows.view(np.float32)
+    u = rows.view(np.uint32)
+    for i, c in enumerate(configs):
+        c.validate()
+        if c.mode is SamplingMode.GREEDY:
+            f[i, 0], f[i, 1], rows[i, 2] = 0.0, 1.0, 0
+        else:
+            f[i, 0] = c.temperature
+            f[i, 1] = c.top_p if c.mode is SamplingMode.TOP_P else 1.0
+            rows[i, 2] = max(1, min(int(c.top_k), vocab)) if c.mode is SamplingMode.TOP_K else 0
+        seed, key = c.seed & _MASK64, keys[i] & _MASK64
+        u[i, 3], u[i, 4] = seed & 0xFFFFFFFF, seed >> 32
+        u[i, 5], u[i, 6] = key & 0xFFFFFFFF, key >> 32
+    return rows
+
+
 class Sampler:
     def __init__(self, rt):
         self.rt = rt
@@ -101,20 +122,7 @@ class Sampler:
         if all(c.mode is SamplingMode.GREEDY for c in configs):
             kernels.argmax(logits, out)
             return out
-        rows = np.zeros((m, 7), dtype=np.int32)
-        f = rows.view(np.float32)
-        u = rows.view(np.uint32)
-        for i, c in enumerate(configs):
-            c.validate()
-            if c.mode is SamplingMode.GREEDY:
-                f[i, 0], f[i, 1], rows[i, 2] = 0.0, 1.0, 0
-            else:
-                f[i, 0] = c.temperature
-                f[i, 1] = c.top_p if c.mode is SamplingMode.TOP_P else 1.0
-                rows[i, 2] = max(1, min(int(c.top_k), vocab)) if c.mode is SamplingMode.TOP_K else 0
-            seed, key = c.seed & _MASK64, keys[i] & _MASK64
-            u[i, 3], u[i, 4] = seed & 0xFFFFFFFF, seed >> 32
-            u[i, 5], u[i, 6] = key & 0xFFFFFFFF, key >> 32
+        rows = pack_rows(configs, keys, vocab)
         dev = self.rt.staging.upload(rows.reshape(-1)).view(m, 7)
         kernels.sample(logits, dev, out)
         return out
