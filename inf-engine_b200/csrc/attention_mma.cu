@@ -1,0 +1,500 @@
+// Paged attention on tensor cores for bfloat16, one head size per build
+// (-DIE_HD=64 or 128): a prefill kernel for prompt portions and mixed batches,
+// and a split-key decode kernel with its merge for steps of single tokens.
+//
+// Both walk a request's keys through its block table in tiles, keep scores,
+// running maximum, running sum and the output accumulators in float32
+// (online softmax), and pack the `group` query heads that share a kv head into
+// the rows of one tile, so every key and value that is loaded serves all of
+// them (engine/llama_attention.py:27-44 expands K and V in memory instead).
+// Products run as mma.sync m16n8k16 on bfloat16 fragments read from shared
+// memory with ldmatrix; tiles arrive with cp.async, double-buffered.
+//
+// Rows of a tile are (token, head-in-group) pairs p = token*group + j of one
+// (request, kv head); a row sees keys first(p) <= key <= ctx_before + token,
+// with first = limit - window + 1 when a window is set.
+#include "common.cuh"
+
+#ifndef IE_HD
+#define IE_HD 64
+#endif
+
+namespace {
+
+constexpr int HD = IE_HD;
+constexpr int CHUNKS = HD / 8;   // 16-byte chunks in a row of HD bfloat16
+constexpr int KSTEPS = HD / 16;  // k-steps of q k^T
+constexpr int NT_O = HD / 8;     // 8-wide output tiles
+constexpr float LOG2E = 1.4426950408889634f;
+
+struct MmaAttnParams {
+  const bf16* q;
+  bf16* out;
+  const bf16* kpool;
+  const bf16* vpool;
+  const int* block_table;
+  const int* q_start;
+  const int* ctx_before;
+  const int* work_req;
+  const int* work_pair0;
+  float* part_o;   // decode: [n_tokens*n_heads, n_splits, HD]
+  float* part_ml;  // decode: [n_tokens*n_heads, n_splits, 2]
+  int q_stride, out_stride, table_stride;
+  int n_heads, n_kv_heads, page_size, window;
+  int n_splits, split_keys;
+  float scale_log2;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+  const int sz = valid ? 16 : 0;  // 0 bytes read: the 16 bytes are filled with zeros
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(sz) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3,
+                                                  uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+// byte offset of 16-byte chunk `chunk` of row `row` in a tile of rows of HD bfloat16;
+// the XOR keeps the eight rows that one ldmatrix touches on different banks
+__device__ __forceinline__ uint32_t swz(int row, int chunk) {
+  return (uint32_t)(row * (HD * 2) + ((chunk ^ (row & 7)) << 4));
+}
+
+// Copy keys [k0, k0+KT) of kv head c (K and V) into shared memory, zero where a key
+// is outside [0, k_end) or its page is not held.
+template <int KT, int NTHREADS>
+__device__ __forceinline__ void load_kv_tile(const MmaAttnParams& p, const int* table, int c, int k0, int k_end,
+                                             uint32_t ks_addr, uint32_t vs_addr, int tid) {
+#pragma unroll
+  for (int idx = tid; idx < KT * CHUNKS; idx += NTHREADS) {
+    const int row = idx / CHUNKS, chunk = idx - row * CHUNKS;
+    const int kp = k0 + row;
+    bool valid = kp < k_end && kp >= 0;
+    int page = -1;
+    if (valid) page = table[kp / p.page_size];
+    valid = valid && page >= 0;
+    size_t off = 0;
+    if (valid) off = (((size_t)page * p.n_kv_heads + c) * p.page_size + (kp % p.page_size)) * HD + chunk * 8;
+    const uint32_t so = swz(row, chunk);
+    cp_async16(ks_addr + so, p.kpool + off, valid);
+    cp_async16(vs_addr + so, p.vpool + off, valid);
+  }
+}
+
+// One warp, 16 rows, one tile of KT keys that lies in shared memory: scores, online
+// softmax update, output accumulation.  lim0/lim1 and first0/first1 bound the visible
+// keys of the lane's two rows (row = lane/4 and lane/4 + 8).
+template <int KT>
+__device__ __forceinline__ void warp_tile(const uint32_t (&qf)[KSTEPS][4], float (&o)[NT_O][4], float (&m)[2],
+                                          float (&l)[2], uint32_t ks_addr, uint32_t vs_addr, int k0, int lim0,
+                                          int lim1, int first0, int first1, bool need_mask, float scale_log2,
+                                          int lane) {
+  constexpr int NT_S = KT / 8;
+  float s[NT_S][4];
+#pragma unroll
+  for (int i = 0; i < NT_S; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+#pragma unroll
+  for (int n2 = 0; n2 < KT / 16; ++n2) {
+#pragma unroll
+    for (int ks = 0; ks < KSTEPS; ++ks) {
+      uint32_t b0, b1, b2, b3;
+      const int key = n2 * 16 + (lane & 7) + ((lane >> 4) << 3);
+      const int chunk = ks * 2 + ((lane >> 3) & 1);
+      ldmatrix_x4(b0, b1, b2, b3, ks_addr + swz(key, chunk));
+      mma_bf16(s[2 * n2], qf[ks], b0, b1);
+      mma_bf16(s[2 * n2 + 1], qf[ks], b2, b3);
+    }
+  }
+  const int col = (lane & 3) * 2;
+  float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < NT_S; ++i) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) s[i][e] *= scale_log2;
+    if (need_mask) {
+      const int kp = k0 + i * 8 + col;
+      if (kp > lim0 || kp < first0) s[i][0] = -INFINITY;
+      if (kp + 1 > lim0 || kp + 1 < first0) s[i][1] = -INFINITY;
+      if (kp > lim1 || kp < first1) s[i][2] = -INFINITY;
+      if (kp + 1 > lim1 || kp + 1 < first1) s[i][3] = -INFINITY;
+    }
+    mx0 = fmaxf(mx0, fmaxf(s[i][0], s[i][1]));
+    mx1 = fmaxf(mx1, fmaxf(s[i][2], s[i][3]));
+  }
+  mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+  mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+  mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+  mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+  const float mn0 = fmaxf(m[0], mx0), mn1 = fmaxf(m[1], mx1);
+  const float ms0 = mn0 == -INFINITY ? 0.f : mn0, ms1 = mn1 == -INFINITY ? 0.f : mn1;
+  const float c0 = fast_exp2(m[0] - ms0), c1 = fast_exp2(m[1] - ms1);  // exp2(-inf) = 0
+  m[0] = mn0;
+  m[1] = mn1;
+  float sum0 = 0.f, sum1 = 0.f;
+  uint32_t pf[NT_S][2];
+#pragma unroll
+  for (int i = 0; i < NT_S; ++i) {
+    const float p0 = fast_exp2(s[i][0] - ms0), p1 = fast_exp2(s[i][1] - ms0);
+    const float p2 = fast_exp2(s[i][2] - ms1), p3 = fast_exp2(s[i][3] - ms1);
+    sum0 += p0 + p1;
+    sum1 += p2 + p3;
+    pf[i][0] = pack_bf16(p0, p1);
+    pf[i][1] = pack_bf16(p2, p3);
+  }
+  l[0] = l[0] * c0 + sum0;
+  l[1] = l[1] * c1 + sum1;
+#pragma unroll
+  for (int i = 0; i < NT_O; ++i) {
+    o[i][0] *= c0;
+    o[i][1] *= c0;
+    o[i][2] *= c1;
+    o[i][3] *= c1;
+  }
+#pragma unroll
+  for (int kk = 0; kk < KT / 16; ++kk) {
+    const uint32_t a[4] = {pf[2 * kk][0], pf[2 * kk][1], pf[2 * kk + 1][0], pf[2 * kk + 1][1]};
+#pragma unroll
+    for (int d2 = 0; d2 < HD / 16; ++d2) {
+      uint32_t v0, v1, v2, v3;
+      const int key = kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+      const int chunk = d2 * 2 + (lane >> 4);
+      ldmatrix_x4_trans(v0, v1, v2, v3, vs_addr + swz(key, chunk));
+      mma_bf16(o[2 * d2], a, v0, v1);
+      mma_bf16(o[2 * d2 + 1], a, v2, v3);
+    }
+  }
+}
+
+// q fragments of the lane's two rows straight from global memory (zeros for rows past the end)
+__device__ __forceinline__ void load_q_frags(uint32_t (&qf)[KSTEPS][4], const bf16* row0, const bf16* row1,
+                                             int lane) {
+  const int col = (lane & 3) * 2;
+#pragma unroll
+  for (int ks = 0; ks < KSTEPS; ++ks) {
+    qf[ks][0] = row0 ? *reinterpret_cast<const uint32_t*>(row0 + ks * 16 + col) : 0u;
+    qf[ks][1] = row1 ? *reinterpret_cast<const uint32_t*>(row1 + ks * 16 + col) : 0u;
+    qf[ks][2] = row0 ? *reinterpret_cast<const uint32_t*>(row0 + ks * 16 + 8 + col) : 0u;
+    qf[ks][3] = row1 ? *reinterpret_cast<const uint32_t*>(row1 + ks * 16 + 8 + col) : 0u;
+  }
+}
+
+// ------------------------------------------------------------------- prefill
+constexpr int PF_WARPS = 4;
+constexpr int PF_THREADS = PF_WARPS * 32;
+constexpr int PF_ROWS = PF_WARPS * 16;
+constexpr int PF_KT = 64;
+constexpr int PF_STAGE_BYTES = 2 * PF_KT * HD * 2;  // K and V of one stage
+
+__global__ void __launch_bounds__(PF_THREADS) attention_prefill_kernel(MmaAttnParams p) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int c = blockIdx.y;
+  const int r_id = p.work_req[blockIdx.x];
+  const int pair0 = p.work_pair0[blockIdx.x];
+  const int group = p.n_heads / p.n_kv_heads;
+  const int q0 = p.q_start[r_id];
+  const int q_len = p.q_start[r_id + 1] - q0;
+  const int ctx = p.ctx_before[r_id];
+  const int n_pairs = q_len * group;
+  const int* table = p.block_table + (size_t)r_id * p.table_stride;
+
+  // the lane's two rows
+  const int pr0 = pair0 + warp * 16 + (lane >> 2), pr1 = pr0 + 8;
+  const bool v0 = pr0 < n_pairs, v1 = pr1 < n_pairs;
+  const int t0 = v0 ? pr0 / group : 0, t1 = v1 ? pr1 / group : 0;
+  const int lim0 = v0 ? ctx + t0 : -1, lim1 = v1 ? ctx + t1 : -1;
+  const int first0 = p.window > 0 ? max(0, lim0 - p.window + 1) : 0;
+  const int first1 = p.window > 0 ? max(0, lim1 - p.window + 1) : 0;
+  const bf16* qr0 = v0 ? p.q + (size_t)(q0 + t0) * p.q_stride + (c * group + (pr0 - t0 * group)) * HD : nullptr;
+  const bf16* qr1 = v1 ? p.q + (size_t)(q0 + t1) * p.q_stride + (c * group + (pr1 - t1 * group)) * HD : nullptr;
+  uint32_t qf[KSTEPS][4];
+  load_q_frags(qf, qr0, qr1, lane);
+
+  // keys that matter to the block and to this warp
+  const int last_pair = min(pair0 + PF_ROWS, n_pairs) - 1;
+  const int k_end = ctx + last_pair / group + 1;
+  int k_begin = 0;
+  if (p.window > 0) k_begin = (max(0, ctx + pair0 / group - p.window + 1) / PF_KT) * PF_KT;
+  const int w_first_pair = pair0 + warp * 16;
+  const int w_last_pair = min(w_first_pair + 16, n_pairs) - 1;
+  const bool warp_has_rows = w_first_pair < n_pairs;
+  const int w_max_lim = warp_has_rows ? ctx + w_last_pair / group : -1;
+  const int w_min_lim = warp_has_rows ? ctx + w_first_pair / group : -1;
+  const int w_min_first = p.window > 0 ? max(0, w_min_lim - p.window + 1) : 0;
+  const int w_max_first = p.window > 0 ? max(0, w_max_lim - p.window + 1) : 0;
+
+  float o[NT_O][4];
+#pragma unroll
+  for (int i = 0; i < NT_O; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+  const uint32_t base = smem_u32(smem);
+  const int n_tiles = (k_end - k_begin + PF_KT - 1) / PF_KT;
+  load_kv_tile<PF_KT, PF_THREADS>(p, table, c, k_begin, k_end, base, base + PF_KT * HD * 2, tid);
+  cp_async_commit();
+  for (int i = 0; i < n_tiles; ++i) {
+    const int k0 = k_begin + i * PF_KT;
+    if (i + 1 < n_tiles) {
+      const uint32_t nb = base + ((i + 1) & 1) * PF_STAGE_BYTES;
+      load_kv_tile<PF_KT, PF_THREADS>(p, table, c, k0 + PF_KT, k_end, nb, nb + PF_KT * HD * 2, tid);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    // skip tiles that no row of this warp can see
+    if (warp_has_rows && k0 <= w_max_lim && k0 + PF_KT > w_min_first) {
+      const uint32_t sb = base + (i & 1) * PF_STAGE_BYTES;
+      const bool need_mask = (k0 + PF_KT - 1 > w_min_lim) || (k0 < w_max_first);
+      warp_tile<PF_KT>(qf, o, m, l, sb, sb + PF_KT * HD * 2, k0, lim0, lim1, first0, first1, need_mask,
+                       p.scale_log2, lane);
+    }
+    __syncthreads();
+  }
+
+  // row sums across the quad, normalise, store
+  l[0] += __shfl_xor_sync(0xffffffffu, l[0], 1);
+  l[0] += __shfl_xor_sync(0xffffffffu, l[0], 2);
+  l[1] += __shfl_xor_sync(0xffffffffu, l[1], 1);
+  l[1] += __shfl_xor_sync(0xffffffffu, l[1], 2);
+  const int col = (lane & 3) * 2;
+  if (v0) {
+    const float inv = l[0] > 0.f ? 1.f / l[0] : 0.f;
+    bf16* dst = p.out + (size_t)(q0 + t0) * p.out_stride + (c * group + (pr0 - t0 * group)) * HD;
+#pragma unroll
+    for (int i = 0; i < NT_O; ++i)
+      *reinterpret_cast<uint32_t*>(dst + i * 8 + col) = pack_bf16(o[i][0] * inv, o[i][1] * inv);
+  }
+  if (v1) {
+    const float inv = l[1] > 0.f ? 1.f / l[1] : 0.f;
+    bf16* dst = p.out + (size_t)(q0 + t1) * p.out_stride + (c * group + (pr1 - t1 * group)) * HD;
+#pragma unroll
+    for (int i = 0; i < NT_O; ++i)
+      *reinterpret_cast<uint32_t*>(dst + i * 8 + col) = pack_bf16(o[i][2] * inv, o[i][3] * inv);
+  }
+}
+
+// -------------------------------------------------------------------- decode
+// One warp per split of the keys: block (x, kv head, request) holds splits
+// 4x .. 4x+3.  A request brings at most 16 rows (q_len * group <= 16).  Each warp
+// writes its unnormalised output, maximum and sum; the merge kernel combines the
+// splits in ascending order.
+constexpr int DC_WARPS = 4;
+constexpr int DC_THREADS = DC_WARPS * 32;
+constexpr int DC_KT = 32;
+constexpr int DC_STAGE_BYTES = 2 * DC_KT * HD * 2;
+constexpr int DC_WARP_BYTES = 2 * DC_STAGE_BYTES;
+
+__global__ void __launch_bounds__(DC_THREADS) attention_decode_kernel(MmaAttnParams p) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int split = blockIdx.x * DC_WARPS + warp;
+  const int c = blockIdx.y, r_id = blockIdx.z;
+  const int group = p.n_heads / p.n_kv_heads;
+  const int q0 = p.q_start[r_id];
+  const int q_len = p.q_start[r_id + 1] - q0;
+  const int ctx = p.ctx_before[r_id];
+  const int n_pairs = q_len * group;
+  const int* table = p.block_table + (size_t)r_id * p.table_stride;
+  if (split >= p.n_splits) return;
+
+  const int pr0 = lane >> 2, pr1 = pr0 + 8;
+  const bool v0 = pr0 < n_pairs, v1 = pr1 < n_pairs;
+  const int t0 = v0 ? pr0 / group : 0, t1 = v1 ? pr1 / group : 0;
+  const int lim0 = v0 ? ctx + t0 : -1, lim1 = v1 ? ctx + t1 : -1;
+  const int first0 = p.window > 0 ? max(0, lim0 - p.window + 1) : 0;
+  const int first1 = p.window > 0 ? max(0, lim1 - p.window + 1) : 0;
+  const int max_lim = ctx + q_len - 1;
+  const int min_first = p.window > 0 ? max(0, ctx - p.window + 1) : 0;
+
+  const int k_lo = max(split * p.split_keys, (min_first / DC_KT) * DC_KT);
+  const int k_hi = min((split + 1) * p.split_keys, max_lim + 1);
+
+  float o[NT_O][4];
+#pragma unroll
+  for (int i = 0; i < NT_O; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+  if (k_lo < k_hi && n_pairs > 0) {
+    const bf16* qr0 = v0 ? p.q + (size_t)(q0 + t0) * p.q_stride + (c * group + (pr0 - t0 * group)) * HD : nullptr;
+    const bf16* qr1 = v1 ? p.q + (size_t)(q0 + t1) * p.q_stride + (c * group + (pr1 - t1 * group)) * HD : nullptr;
+    uint32_t qf[KSTEPS][4];
+    load_q_frags(qf, qr0, qr1, lane);
+    const uint32_t base = smem_u32(smem) + warp * DC_WARP_BYTES;
+    const int n_tiles = (k_hi - k_lo + DC_KT - 1) / DC_KT;
+    load_kv_tile<DC_KT, 32>(p, table, c, k_lo, k_hi, base, base + DC_KT * HD * 2, lane);
+    cp_async_commit();
+    for (int i = 0; i < n_tiles; ++i) {
+      const int k0 = k_lo + i * DC_KT;
+      if (i + 1 < n_tiles) {
+        const uint32_t nb = base + ((i + 1) & 1) * DC_STAGE_BYTES;
+        load_kv_tile<DC_KT, 32>(p, table, c, k0 + DC_KT, k_hi, nb, nb + DC_KT * HD * 2, lane);
+        cp_async_commit();
+        cp_async_wait<1>();
+      } else {
+        cp_async_wait<0>();
+      }
+      __syncwarp();
+      const uint32_t sb = base + (i & 1) * DC_STAGE_BYTES;
+      const bool need_mask = (k0 + DC_KT - 1 > ctx) || (p.window > 0);
+      warp_tile<DC_KT>(qf, o, m, l, sb, sb + DC_KT * HD * 2, k0, lim0, lim1, first0, first1, need_mask,
+                       p.scale_log2, lane);
+      __syncwarp();
+    }
+  }
+  l[0] += __shfl_xor_sync(0xffffffffu, l[0], 1);
+  l[0] += __shfl_xor_sync(0xffffffffu, l[0], 2);
+  l[1] += __shfl_xor_sync(0xffffffffu, l[1], 1);
+  l[1] += __shfl_xor_sync(0xffffffffu, l[1], 2);
+  const int col = (lane & 3) * 2;
+  if (v0) {
+    const size_t row = (size_t)(q0 + t0) * p.n_heads + c * group + (pr0 - t0 * group);
+    float* po = p.part_o + (row * p.n_splits + split) * HD;
+#pragma unroll
+    for (int i = 0; i < NT_O; ++i) *reinterpret_cast<float2*>(po + i * 8 + col) = make_float2(o[i][0], o[i][1]);
+    if ((lane & 3) == 0) *reinterpret_cast<float2*>(p.part_ml + (row * p.n_splits + split) * 2) = make_float2(m[0], l[0]);
+  }
+  if (v1) {
+    const size_t row = (size_t)(q0 + t1) * p.n_heads + c * group + (pr1 - t1 * group);
+    float* po = p.part_o + (row * p.n_splits + split) * HD;
+#pragma unroll
+    for (int i = 0; i < NT_O; ++i) *reinterpret_cast<float2*>(po + i * 8 + col) = make_float2(o[i][2], o[i][3]);
+    if ((lane & 3) == 0) *reinterpret_cast<float2*>(p.part_ml + (row * p.n_splits + split) * 2) = make_float2(m[1], l[1]);
+  }
+}
+
+// out[row] = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M), splits in ascending order
+__global__ void __launch_bounds__(HD) attention_merge_kernel(const float* __restrict__ part_o,
+                                                             const float* __restrict__ part_ml, bf16* __restrict__ out,
+                                                             int n_heads, int n_splits, int out_stride) {
+  const int row = blockIdx.x;  // token * n_heads + head
+  const int d = threadIdx.x;
+  const float* ml = part_ml + (size_t)row * n_splits * 2;
+  float M = -INFINITY;
+  for (int s = 0; s < n_splits; ++s) M = fmaxf(M, ml[2 * s]);
+  float acc = 0.f, den = 0.f;
+  if (M > -INFINITY) {
+    for (int s = 0; s < n_splits; ++s) {
+      const float ms = ml[2 * s];
+      if (ms == -INFINITY) continue;
+      const float w = fast_exp2(ms - M);
+      acc += w * part_o[((size_t)row * n_splits + s) * HD + d];
+      den += w * ml[2 * s + 1];
+    }
+  }
+  const int token = row / n_heads, head = row - token * n_heads;
+  out[(size_t)token * out_stride + head * HD + d] = __float2bfloat16_rn(den > 0.f ? acc / den : 0.f);
+}
+
+static void fill(MmaAttnParams& p, const void* q, void* out, const void* kpool, const void* vpool,
+                 const int* block_table, const int* q_start, const int* ctx_before, int q_stride, int out_stride,
+                 int table_stride, int n_heads, int n_kv_heads, int page_size, int window, float scale) {
+  p.q = (const bf16*)q; p.out = (bf16*)out; p.kpool = (const bf16*)kpool; p.vpool = (const bf16*)vpool;
+  p.block_table = block_table; p.q_start = q_start; p.ctx_before = ctx_before;
+  p.work_req = nullptr; p.work_pair0 = nullptr; p.part_o = nullptr; p.part_ml = nullptr;
+  p.q_stride = q_stride; p.out_stride = out_stride; p.table_stride = table_stride;
+  p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.page_size = page_size; p.window = window;
+  p.n_splits = 0; p.split_keys = 0; p.scale_log2 = scale * LOG2E;
+}
+
+static int check_common(const void* q, const void* out, const void* kpool, const void* vpool, int q_stride,
+                        int out_stride, int n_heads, int n_kv_heads, int hd, int page_size) {
+  if (hd != HD) return IE_BAD_SIZE;
+  if (n_kv_heads <= 0 || n_heads % n_kv_heads || page_size <= 0) return IE_BAD_SIZE;
+  if (((uintptr_t)q | (uintptr_t)out) & 3) return IE_BAD_ALIGN;
+  if (((uintptr_t)kpool | (uintptr_t)vpool) & 15) return IE_BAD_ALIGN;
+  if ((q_stride | out_stride) & 1) return IE_BAD_ALIGN;
+  return IE_OK;
+}
+
+}  // namespace
+
+extern "C" int ie_attention_mma_head_dim() { return HD; }
+
+extern "C" int ie_attention_prefill(const void* q, void* out, const void* kpool, const void* vpool,
+                                    const int* block_table, const int* q_start, const int* ctx_before,
+                                    const int* work_req, const int* work_pair0, int q_stride, int out_stride,
+                                    int table_stride, int n_work, int n_heads, int n_kv_heads, int hd, int page_size,
+                                    int window, float scale, cudaStream_t stream) {
+  if (n_work <= 0) return IE_OK;
+  int rc = check_common(q, out, kpool, vpool, q_stride, out_stride, n_heads, n_kv_heads, hd, page_size);
+  if (rc) return rc;
+  MmaAttnParams p;
+  fill(p, q, out, kpool, vpool, block_table, q_start, ctx_before, q_stride, out_stride, table_stride, n_heads,
+       n_kv_heads, page_size, window, scale);
+  p.work_req = work_req;
+  p.work_pair0 = work_pair0;
+  const int smem = 2 * PF_STAGE_BYTES;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  attention_prefill_kernel<<<dim3(n_work, n_kv_heads), PF_THREADS, smem, stream>>>(p);
+  return launch_status();
+}
+
+// Scratch needed by the decode kernel, in floats: part_o then part_ml.
+extern "C" long long ie_attention_decode_scratch_floats(int n_tokens, int n_heads, int n_splits) {
+  return (long long)n_tokens * n_heads * n_splits * (HD + 2);
+}
+
+extern "C" int ie_attention_decode(const void* q, void* out, const void* kpool, const void* vpool,
+                                   const int* block_table, const int* q_start, const int* ctx_before, float* scratch,
+                                   int q_stride, int out_stride, int table_stride, int n_requests, int n_tokens,
+                                   int n_heads, int n_kv_heads, int hd, int page_size, int window, float scale,
+                                   int n_splits, int split_keys, cudaStream_t stream) {
+  if (n_requests <= 0) return IE_OK;
+  int rc = check_common(q, out, kpool, vpool, q_stride, out_stride, n_heads, n_kv_heads, hd, page_size);
+  if (rc) return rc;
+  if (n_splits <= 0 || split_keys <= 0 || split_keys % DC_KT) return IE_BAD_SIZE;
+  if ((uintptr_t)scratch & 15) return IE_BAD_ALIGN;
+  MmaAttnParams p;
+  fill(p, q, out, kpool, vpool, block_table, q_start, ctx_before, q_stride, out_stride, table_stride, n_heads,
+       n_kv_heads, page_size, window, scale);
+  p.n_splits = n_splits;
+  p.split_keys = split_keys;
+  p.part_o = scratch;
+  p.part_ml = scratch + (size_t)n_tokens * n_heads * n_splits * HD;
+  const int smem = DC_WARPS * DC_WARP_BYTES;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  dim3 grid((n_splits + DC_WARPS - 1) / DC_WARPS, n_kv_heads, n_requests);
+  attention_decode_kernel<<<grid, DC_THREADS, smem, stream>>>(p);
+  rc = launch_status();
+  if (rc) return rc;
+  attention_merge_kernel<<<n_tokens * n_heads, HD, 0, stream>>>(p.part_o, p.part_ml, p.out, n_heads, n_splits,
+                                                                out_stride);
+  return launch_status();
+}

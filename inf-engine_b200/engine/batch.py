@@ -53,6 +53,7 @@ class StepContext:
         self._work: dict = {}
         self.max_q_len = 0
         self.max_seq_len = 0
+        self.keys_cap = 0          # no request of the step holds more keys than this (sizes split-key grids)
 
     def attention_work(self, group: int, rows: int):
         """Work list for attention kernels that tile (token, head-in-group) pairs
@@ -131,4 +132,5 @@ def build_context(rt, manager, entries: list[StepEntry]) -> StepContext:
                 "slots": slots, "logit_rows": logit_rows, "q_lens": q_lens, "rids": [e.rid for e in entries]}
     ctx.max_q_len = max(q_lens)
     ctx.max_seq_len = max(b + q for b, q in zip(ctx_before, q_lens))
+    ctx.keys_cap = ctx.max_seq_len
     return ctx

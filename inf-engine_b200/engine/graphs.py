@@ -92,6 +92,7 @@ class DecodeGraphs:
                       for g, w in enumerate(widths)]
             ctx.n_tokens = ctx.n_requests = ctx.n_logits = B
             ctx.max_q_len = 1
+            ctx.keys_cap = min(widths) * self.runner.page_size if widths else 0
             ctx.host = {"q_lens": [1] * B, "q_start": list(range(B + 1)), "slots": [0] * B, "graph": True}
             b.ctx = ctx
             b.rows = view("sample_rows").view(B, 7)

@@ -180,3 +180,58 @@ def sample(logits: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> None:
     assert rows.is_contiguous() and out.dtype == torch.int32
     _check(core().ie_sample(_ptr(logits), _ptr(rows), _ptr(out), logits.shape[0], logits.shape[1],
                             logits.stride(0), _stream()), "sample")
+
+
+# ------------------------------------------------- tensor-core attention (bfloat16)
+MMA_HEAD_DIMS = (64, 128)
+_mma: dict[int, object] = {}
+
+
+def attention_mma_library(head_dim: int):
+    """The tensor-core attention kernels built for one head size; compiled when first asked for."""
+    if head_dim not in MMA_HEAD_DIMS:
+        raise KernelError(f"tensor-core attention is built for head sizes {MMA_HEAD_DIMS}, not {head_dim}")
+    lib = _mma.get(head_dim)
+    if lib is None:
+        lib = load_library(f"attn_mma_hd{head_dim}", ["attention_mma.cu"], {"IE_HD": head_dim})
+        P, I, F = c_void_p, c_int, c_float
+        lib.ie_attention_prefill.argtypes = [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P]
+        lib.ie_attention_prefill.restype = c_int
+        lib.ie_attention_decode.argtypes = [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, I, P]
+        lib.ie_attention_decode.restype = c_int
+        lib.ie_attention_decode_scratch_floats.argtypes = [I, I, I]
+        lib.ie_attention_decode_scratch_floats.restype = c_longlong
+        _mma[head_dim] = lib
+    return lib
+
+
+def attention_prefill_mma(q, out, kpool, vpool, block_table, q_start, ctx_before, work_req, work_pair0, n_work,
+                          n_heads, n_kv_heads, head_dim, page_size, window, scale) -> None:
+    """Causal paged attention for any mix of portions and single tokens; bfloat16; rows tiled by 64 pairs."""
+    assert q.dtype is torch.bfloat16 and q.stride(1) == 1 and out.stride(1) == 1
+    lib = attention_mma_library(head_dim)
+    _check(lib.ie_attention_prefill(_ptr(q), _ptr(out), _ptr(kpool), _ptr(vpool), _ptr(block_table), _ptr(q_start),
+                                    _ptr(ctx_before), _ptr(work_req), _ptr(work_pair0), q.stride(0), out.stride(0),
+                                    block_table.stride(0), n_work, n_heads, n_kv_heads, head_dim, page_size,
+                                    int(window or 0), float(scale), _stream()), "attention_prefill_mma")
+
+
+def attention_decode_scratch_floats(n_tokens, n_heads, n_splits, head_dim) -> int:
+    return int(attention_mma_library(head_dim).ie_attention_decode_scratch_floats(n_tokens, n_heads, n_splits))
+
+
+def attention_decode_mma(q, out, kpool, vpool, block_table, q_start, ctx_before, scratch, n_requests, n_tokens,
+                         n_heads, n_kv_heads, head_dim, page_size, window, scale, n_splits, split_keys) -> None:
+    """Split-key attention for steps where every request brings at most 16 (token, head-in-group) rows.
+
+    ``scratch`` is float32 device memory of ``attention_decode_scratch_floats`` elements that the kernel
+    fully overwrites (partial outputs, maxima and sums of every split) before its merge reads it."""
+    assert q.dtype is torch.bfloat16 and scratch.dtype is torch.float32
+    lib = attention_mma_library(head_dim)
+    _check(lib.ie_attention_decode(_ptr(q), _ptr(out), _ptr(kpool), _ptr(vpool), _ptr(block_table), _ptr(q_start),
+                                   _ptr(ctx_before), _ptr(scratch), q.stride(0), out.stride(0),
+                                   block_table.stride(0), n_requests, n_tokens, n_heads, n_kv_heads, head_dim,
+                                   page_size, int(window or 0), float(scale), n_splits, split_keys, _stream()),
+           "attention_decode_mma")
+    global LAUNCHES
+    LAUNCHES += 1        # the launcher runs two kernels: the split pass and its merge

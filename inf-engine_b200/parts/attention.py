@@ -95,7 +95,36 @@ class PagedAttention:
     def _attend(self, q, out, cache, ctx, kvctx) -> None:
         s = self.spec
         group = s.n_heads // s.n_kv_heads
+        if self.rt.act_dtype is torch.bfloat16 and s.head_dim in kernels.MMA_HEAD_DIMS:
+            # tensor-core kernels, built for this head size when first used
+            if ctx.max_q_len * group <= 16:
+                n_splits, split_keys = decode_splits(ctx.keys_cap, ctx.n_requests * s.n_kv_heads)
+                n = kernels.attention_decode_scratch_floats(ctx.n_tokens, s.n_heads, n_splits, s.head_dim)
+                scratch = self.rt.ws.take("attn_scratch", (n,), torch.float32)
+                kernels.attention_decode_mma(q, out, cache.k, cache.v, kvctx.block_table, ctx.q_start,
+                                             ctx.ctx_before, scratch, ctx.n_requests, ctx.n_tokens, s.n_heads,
+                                             s.n_kv_heads, s.head_dim, ctx.page_size, s.window, self.scale,
+                                             n_splits, split_keys)
+            else:
+                work_req, work_pair0, n_work = ctx.attention_work(group, 64)
+                kernels.attention_prefill_mma(q, out, cache.k, cache.v, kvctx.block_table, ctx.q_start,
+                                              ctx.ctx_before, work_req, work_pair0, n_work, s.n_heads,
+                                              s.n_kv_heads, s.head_dim, ctx.page_size, s.window, self.scale)
+            return
         work_req, work_pair0, n_work = ctx.attention_work(group, 32)
         kernels.attention_general(q, out, cache.k, cache.v, kvctx.block_table, ctx.q_start, ctx.ctx_before,
                                   work_req, work_pair0, n_work, s.n_heads, s.n_kv_heads, s.head_dim,
                                   ctx.page_size, s.window, self.scale)
+
+
+def decode_splits(keys_cap: int, n_streams: int, target_warps: int = 2048) -> tuple[int, int]:
+    """How the decode kernel cuts the keys: (number of splits, keys per split).
+
+    One warp works on one split of one (request, kv head); enough warps must be in
+    flight to keep HBM busy, so few requests mean short splits.  Splits are multiples
+    of 32 keys and cover ``keys_cap`` keys, the most any request of the step can hold.
+    """
+    keys_cap = max(int(keys_cap), 1)
+    per = -(-keys_cap * max(n_streams, 1) // target_warps)
+    split_keys = min(1024, max(32, -(-per // 32) * 32))
+    return -(-keys_cap // split_keys), split_keys

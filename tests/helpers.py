@@ -34,8 +34,22 @@ TINY_C = dict(
     rope_scaling=None, rms_norm_eps=1e-5, tie_word_embeddings=True, max_position_embeddings=512,
     hidden_act="silu",
 )
-TINY = {"tiny_a": TINY_A, "tiny_b": TINY_B, "tiny_c": TINY_C}
-SEEDS = {"tiny_a": 0, "tiny_b": 1, "tiny_c": 2}
+# head sizes 64 and 128 are the ones the tensor-core attention kernels are built for
+TINY_D = dict(
+    architectures=["LlamaForCausalLM"], num_hidden_layers=2, hidden_size=192, num_attention_heads=6,
+    num_key_value_heads=2, head_dim=64, intermediate_size=272, vocab_size=333, rope_theta=100000.0,
+    rope_scaling=dict(rope_type="llama3", factor=4.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                      original_max_position_embeddings=128),
+    rms_norm_eps=1e-5, tie_word_embeddings=True, max_position_embeddings=1024, hidden_act="silu",
+)
+TINY_E = dict(
+    architectures=["LlamaForCausalLM"], num_hidden_layers=2, hidden_size=136, num_attention_heads=2,
+    num_key_value_heads=1, head_dim=128, intermediate_size=144, vocab_size=270, rope_theta=50000.0,
+    rope_scaling=None, rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=1024,
+    hidden_act="silu",
+)
+TINY = {"tiny_a": TINY_A, "tiny_b": TINY_B, "tiny_c": TINY_C, "tiny_d": TINY_D, "tiny_e": TINY_E}
+SEEDS = {"tiny_a": 0, "tiny_b": 1, "tiny_c": 2, "tiny_d": 3, "tiny_e": 4}
 
 
 def make_model_dir(tmp: Path, name: str, store_dtype: str = "bfloat16", std: float = 0.05) -> Path:

@@ -30,7 +30,7 @@ def entry(rid, toks, want="all"):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_d", "tiny_e"])
 def test_long_decoding(tmp_path, name, dtype):
     d = make_model_dir(tmp_path, name)
     config, weights = plain_inputs(d)
@@ -45,7 +45,7 @@ def test_long_decoding(tmp_path, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c"])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c", "tiny_d", "tiny_e"])
 def test_first_tokens_of_a_sequence(tmp_path, name, dtype):
     d = make_model_dir(tmp_path, name)
     config, weights = plain_inputs(d)
@@ -81,7 +81,7 @@ def sharpened(tmp_path, name, factor=5.0):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_d", "tiny_e"])
 def test_peaked_attention_over_reused_pages(tmp_path, name, dtype):
     # bfloat16 rounds q and k to 8 bits, and a score of size s then carries an error of about
     # s/256 into the exponent: the scores are made 25 times larger in 32-bit, 6 times in bfloat16
@@ -219,7 +219,7 @@ def test_step_refuses_what_it_cannot_run(tmp_path):
 
 # ------------------------------------------------------------------- generation
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_d"])
 def test_greedy_generation_through_the_entry_point(tmp_path, name, dtype):
     from inf_engine_b200 import Engine, Request
     d = make_model_dir(tmp_path, name)

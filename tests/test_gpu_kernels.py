@@ -253,6 +253,88 @@ def test_attention_finds_one_far_key_among_hundreds(act):
     assert torch.allclose(out.float().cpu(), ref, **(dict(atol=1e-5, rtol=1e-5) if act is torch.float32 else tol(act)))
 
 
+MMA_CASES = [
+    # H, Hk, hd, page, q_lens, ctx_before, window
+    (8, 2, 64, 16, [200], [0], None),
+    (6, 2, 64, 8, [1, 9, 1, 70, 130], [70, 0, 129, 31, 515], None),
+    (4, 4, 64, 16, [17, 1, 64], [3, 300, 64], None),
+    (3, 1, 64, 4, [5, 66], [11, 200], None),
+    (4, 1, 128, 16, [20, 1, 100], [50, 333, 0], None),
+    (2, 2, 128, 32, [3, 150], [9, 40], None),
+    (8, 2, 64, 16, [30, 1, 7, 200], [0, 90, 41, 100], 37),
+    (2, 1, 128, 8, [2, 64, 1], [62, 0, 500], 70),
+]
+
+
+@pytest.mark.parametrize("case", MMA_CASES)
+def test_attention_prefill_tensor_cores(case):
+    H, Hk, hd, ps, q_lens, ctx_before, window = case
+    act = torch.bfloat16
+    c = paged_case(act, H, Hk, hd, ps, q_lens, ctx_before, seed=3 * hd + len(q_lens))
+    ref = paged_reference(c["q"], c["kd"], c["vd"], q_lens, ctx_before, H, Hk, hd, window)
+    req, pair0 = work_list(q_lens, H // Hk, 64)
+    dev = lambda t: torch.as_tensor(t, dtype=torch.int32).to(DEV)
+    out = torch.full((c["N"], H * hd), float("nan"), device=DEV, dtype=act)
+    k().attention_prefill_mma(c["q"].to(DEV, act), out, c["kpool"].to(DEV, act), c["vpool"].to(DEV, act),
+                              c["table"].to(DEV), dev(c["q_start"]), dev(ctx_before), dev(req), dev(pair0), len(req),
+                              H, Hk, hd, ps, window, hd ** -0.5)
+    assert torch.allclose(out.float().cpu(), ref, **tol(act))
+
+
+DECODE_CASES = [
+    # H, Hk, hd, page, q_lens, ctx_before, window, split_keys
+    (8, 2, 64, 16, [1, 1, 1], [0, 700, 33], None, 64),
+    (32, 8, 64, 16, [1] * 5, [2047, 1, 511, 512, 100], None, 128),
+    (6, 2, 64, 8, [2, 1, 5], [70, 0, 129], None, 32),
+    (4, 4, 64, 16, [1, 16], [300, 15], None, 256),
+    (4, 1, 128, 16, [1, 3], [333, 50], None, 96),
+    (16, 1, 128, 32, [1], [900], None, 128),
+    (8, 2, 64, 16, [1, 1, 2], [90, 41, 400], 37, 64),
+]
+
+
+@pytest.mark.parametrize("case", DECODE_CASES)
+def test_attention_decode_split_keys(case):
+    H, Hk, hd, ps, q_lens, ctx_before, window, split_keys = case
+    act = torch.bfloat16
+    assert max(q_lens) * (H // Hk) <= 16
+    c = paged_case(act, H, Hk, hd, ps, q_lens, ctx_before, seed=5 * hd + len(q_lens))
+    ref = paged_reference(c["q"], c["kd"], c["vd"], q_lens, ctx_before, H, Hk, hd, window)
+    dev = lambda t: torch.as_tensor(t, dtype=torch.int32).to(DEV)
+    cap = max(a + b for a, b in zip(q_lens, ctx_before)) + 77      # the cap may exceed every request's length
+    n_splits = -(-cap // split_keys)
+    n = k().attention_decode_scratch_floats(c["N"], H, n_splits, hd)
+    scratch = torch.full((n,), float("nan"), device=DEV)            # whatever an earlier call left must not matter
+    out = torch.full((c["N"], H * hd), float("nan"), device=DEV, dtype=act)
+    for _ in range(2):
+        k().attention_decode_mma(c["q"].to(DEV, act), out, c["kpool"].to(DEV, act), c["vpool"].to(DEV, act),
+                                 c["table"].to(DEV), dev(c["q_start"]), dev(ctx_before), scratch, len(q_lens),
+                                 c["N"], H, Hk, hd, ps, window, hd ** -0.5, n_splits, split_keys)
+        assert torch.allclose(out.float().cpu(), ref, **tol(act))
+
+
+@pytest.mark.parametrize("kind", ["prefill", "decode"])
+def test_tensor_core_attention_finds_one_far_key_among_hundreds(kind):
+    H, Hk, hd, ps, act = 4, 2, 64, 16, torch.bfloat16
+    q_lens, ctx_before = ([1, 6], [700, 420]) if kind == "prefill" else ([1, 1], [700, 420])
+    if kind == "prefill":
+        q_lens = [1, 40]
+    c = paged_case(act, H, Hk, hd, ps, q_lens, ctx_before, seed=12, spike=True)
+    ref = paged_reference(c["q"], c["kd"], c["vd"], q_lens, ctx_before, H, Hk, hd, None)
+    dev = lambda t: torch.as_tensor(t, dtype=torch.int32).to(DEV)
+    out = torch.empty((c["N"], H * hd), device=DEV, dtype=act)
+    args = (c["q"].to(DEV, act), out, c["kpool"].to(DEV, act), c["vpool"].to(DEV, act), c["table"].to(DEV),
+            dev(c["q_start"]), dev(ctx_before))
+    if kind == "prefill":
+        req, pair0 = work_list(q_lens, 2, 64)
+        k().attention_prefill_mma(*args, dev(req), dev(pair0), len(req), H, Hk, hd, ps, None, hd ** -0.5)
+    else:
+        n_splits = -(-701 // 64)
+        scratch = torch.empty(k().attention_decode_scratch_floats(c["N"], H, n_splits, hd), device=DEV)
+        k().attention_decode_mma(*args, scratch, 2, c["N"], H, Hk, hd, ps, None, hd ** -0.5, n_splits, 64)
+    assert torch.allclose(out.float().cpu(), ref, **tol(act))
+
+
 def test_attention_refuses_head_sizes_it_cannot_take():
     from inf_engine_b200.kernels import KernelError
     z = torch.zeros(1, device=DEV)
