@@ -179,30 +179,31 @@ extern "C" int ie_rope_kv_write(void* q, const void* k, const void* v, int q_str
 }
 
 // ---------------------------------------------------------------- SiLU(gate)*up
-// in is [n, 2*inter] with gate in columns [0, inter) and up in [inter, 2*inter);
+// in is [n, 2*inter]: gate in columns [0, inter) and up in [inter, 2*inter), or, when
+// `interleaved`, gate_j in column 2j and up_j in column 2j+1;
 // out[n, j] = gate*sigmoid(gate) * up          (engine/llama_mlp.py:32, engine/layers.py:28-30)
 template <typename TA>
 __global__ void silu_mul_kernel(const TA* __restrict__ in, TA* __restrict__ out, int inter, int in_stride,
-                                size_t total) {
+                                size_t total, int interleaved) {
   size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
   const size_t n = idx / inter;
   const int j = (int)(idx - n * inter);
-  const float g = to_f32(in[n * in_stride + j]);
-  const float u = to_f32(in[n * in_stride + inter + j]);
+  const float g = to_f32(in[n * in_stride + (interleaved ? 2 * j : j)]);
+  const float u = to_f32(in[n * in_stride + (interleaved ? 2 * j + 1 : inter + j)]);
   const float sg = 1.f / (1.f + expf(-g));
   out[idx] = from_f32<TA>((g * sg) * u);
 }
 
-extern "C" int ie_silu_mul(const void* in, void* out, int n_rows, int inter, int in_stride, int act_dtype,
-                           cudaStream_t stream) {
+extern "C" int ie_silu_mul(const void* in, void* out, int n_rows, int inter, int in_stride, int interleaved,
+                           int act_dtype, cudaStream_t stream) {
   const size_t total = (size_t)n_rows * inter;
   if (total == 0) return IE_OK;
   const unsigned blocks = (unsigned)((total + 255) / 256);
   if (act_dtype == IE_F32)
-    silu_mul_kernel<float><<<blocks, 256, 0, stream>>>((const float*)in, (float*)out, inter, in_stride, total);
+    silu_mul_kernel<float><<<blocks, 256, 0, stream>>>((const float*)in, (float*)out, inter, in_stride, total, interleaved);
   else if (act_dtype == IE_BF16)
-    silu_mul_kernel<bf16><<<blocks, 256, 0, stream>>>((const bf16*)in, (bf16*)out, inter, in_stride, total);
+    silu_mul_kernel<bf16><<<blocks, 256, 0, stream>>>((const bf16*)in, (bf16*)out, inter, in_stride, total, interleaved);
   else
     return IE_BAD_DTYPE;
   return launch_status();

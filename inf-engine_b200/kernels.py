@@ -68,7 +68,7 @@ def core():
         lib.ie_rmsnorm.argtypes = [P, P, P, I, P, I, P, I, I, F, P]
         lib.ie_residual_add.argtypes = [P, P, I, I, I, P]
         lib.ie_rope_kv_write.argtypes = [P, P, P, I, I, P, P, P, P, P, P, I, I, I, I, I, I, I, P]
-        lib.ie_silu_mul.argtypes = [P, P, I, I, I, I, P]
+        lib.ie_silu_mul.argtypes = [P, P, I, I, I, I, I, P]
         lib.ie_attention_general.argtypes = [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P]
         lib.ie_gemm_simt.argtypes = [P, I, P, I, P, I, I, I, I, I, I, I, P]
         lib.ie_argmax.argtypes = [P, P, I, I, L, P]
@@ -125,11 +125,12 @@ def rope_kv_write(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cos: torch.
                                    _stream()), "rope_kv_write")
 
 
-def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, interleaved: bool = False) -> None:
+    """out[n, j] = silu(gate_j) * up_j; gate and up are the two halves of a row, or alternate when ``interleaved``."""
     n, inter = out.shape
     assert gate_up.shape == (n, 2 * inter) and gate_up.stride(1) == 1 and out.is_contiguous()
-    _check(core().ie_silu_mul(_ptr(gate_up), _ptr(out), n, inter, gate_up.stride(0), dtype_code(out.dtype),
-                              _stream()), "silu_mul")
+    _check(core().ie_silu_mul(_ptr(gate_up), _ptr(out), n, inter, gate_up.stride(0), 1 if interleaved else 0,
+                              dtype_code(out.dtype), _stream()), "silu_mul")
 
 
 # --------------------------------------------------------------------- attention
@@ -235,3 +236,47 @@ def attention_decode_mma(q, out, kpool, vpool, block_table, q_start, ctx_before,
            "attention_decode_mma")
     global LAUNCHES
     LAUNCHES += 1        # the launcher runs two kernels: the split pass and its merge
+
+
+# ----------------------------------------------- weight-streaming product for few rows
+STREAM_MAX_ROWS = 64        # what the kernel takes
+STREAM_BEST_ROWS = 16       # beyond this the library product is faster (activations are re-read per block)
+_EPI = {"bf16": 0, "f32": 1, "residual": 2, "silu_mul": 3}
+_stream_lib = None
+
+
+def stream_library():
+    global _stream_lib
+    if _stream_lib is None:
+        lib = load_library("stream", ["gemm_stream.cu"])
+        P, I, F = c_void_p, c_int, c_float
+        lib.ie_gemm_stream.argtypes = [P, P, P, P, I, P, I, I, I, I, I, I, F, I, I, I, P]
+        lib.ie_gemm_stream.restype = c_int
+        _stream_lib = lib
+    return _stream_lib
+
+
+def gemm_stream(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, m: int, epi: str = "bf16",
+                gain: torch.Tensor | None = None, eps: float = 0.0, row_index: torch.Tensor | None = None,
+                nt: int | None = None) -> None:
+    """c = a @ w^T for m <= 64 rows, bfloat16 weights, reading w once at HBM speed.
+
+    With ``gain`` the input ``a`` is the float32 residual stream (rows gathered by ``row_index`` if given)
+    and RMSNorm with that gain and ``eps`` is applied inside the kernel.  ``epi``: "bf16" or "f32" store,
+    "residual" adds into the float32 ``c``, "silu_mul" takes w's rows as alternating gate/up and writes
+    silu(gate)*up, half as wide."""
+    n, k = w.shape
+    assert w.dtype is torch.bfloat16 and w.stride(1) == 1 and a.stride(-1) == 1 and c.stride(-1) == 1
+    if gain is None:
+        assert a.dtype is torch.bfloat16
+    else:
+        assert a.dtype is torch.float32 and gain.shape == (k,)
+    if nt is None:
+        nt = 4 if n >= 16384 else (2 if n >= 8192 else 1)
+        if m > 32:
+            nt = min(nt, 2)
+    _check(stream_library().ie_gemm_stream(_ptr(a), _ptr(w), _ptr(c), _ptr(gain),
+                                           dtype_code(gain.dtype) if gain is not None else 0, _ptr(row_index), m, n, k,
+                                           a.stride(0), w.stride(0), c.stride(0), float(eps),
+                                           0 if gain is None else 1, _EPI[epi], nt, _stream()),
+           f"gemm_stream(m={m}, n={n}, k={k}, {epi})")

@@ -73,10 +73,30 @@ class PagedAttention:
         return CacheRequirement(kind="kv", n_kv_heads=s.n_kv_heads, head_dim=s.head_dim, window=s.window,
                                 dtype=self.rt.act_dtype)
 
+    def can_fuse(self, n_tokens: int, norm) -> bool:
+        return hasattr(norm, "fusable_rms") and self.qkv.streams(n_tokens) and self.o.streams(n_tokens)
+
+    def forward_fused(self, residual: torch.Tensor, norm, ctx, cache: CacheView) -> None:
+        """residual += o(attention(qkv(norm(residual)))): the norm rides in the qkv product's prologue and the
+        residual sum in the output product's epilogue."""
+        rt = self.rt
+        n = residual.shape[0]
+        gain, eps = norm.fusable_rms()
+        qkv = rt.ws.take("attn_qkv", (n, self.q_width + 2 * self.kv_width), rt.act_dtype)
+        self.qkv.stream(residual, qkv, n, "bf16", gain, eps)
+        out = self._rotate_write_attend(qkv, ctx, cache)
+        self.o.stream(out, residual, n, "residual")
+
     def forward(self, x: torch.Tensor, ctx, cache: CacheView) -> torch.Tensor:
         s, rt = self.spec, self.rt
         n = x.shape[0]
         qkv = self.qkv(x, rt.ws.take("attn_qkv", (n, self.q_width + 2 * self.kv_width), rt.act_dtype))
+        out = self._rotate_write_attend(qkv, ctx, cache)
+        return self.o(out, rt.ws.take("mixer_out", (n, s.hidden), rt.act_dtype))
+
+    def _rotate_write_attend(self, qkv: torch.Tensor, ctx, cache: CacheView) -> torch.Tensor:
+        s, rt = self.spec, self.rt
+        n = qkv.shape[0]
         q = qkv[:, :self.q_width]
         k = qkv[:, self.q_width:self.q_width + self.kv_width]
         v = qkv[:, self.q_width + self.kv_width:]
@@ -90,7 +110,7 @@ class PagedAttention:
                               s.n_heads, s.n_kv_heads, s.head_dim, ctx.page_size)
         out = rt.ws.take("attn_out", (n, self.q_width), rt.act_dtype)
         self._attend(q, out, cache, ctx, kvctx)
-        return self.o(out, rt.ws.take("mixer_out", (n, s.hidden), rt.act_dtype))
+        return out
 
     def _attend(self, q, out, cache, ctx, kvctx) -> None:
         s = self.spec

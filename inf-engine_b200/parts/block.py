@@ -4,6 +4,7 @@ them: a block hands on the residual and a delta that is not added yet."""
 
 from __future__ import annotations
 
+from .. import kernels
 from .registry import (
     build_feedforward,
     build_mixer,
@@ -34,8 +35,27 @@ class PreNormBlock:
         self.feedforward = build_feedforward(spec.feedforward, tensors, rt)
 
     def forward(self, residual, pending, ctx, cache):
-        h = self.mixer_norm.add_norm(residual, pending)
-        a = self.mixer.forward(h, ctx, cache)
+        n = ctx.n_tokens
+        # a part may offer forward_fused(residual, norm, ...): it applies the norm and adds its own
+        # result into the residual inside its kernels (worth it for the few rows of a decode step)
+        if _fuses(self.mixer, n, self.mixer_norm):
+            if pending is not None:
+                kernels.residual_add(residual, pending)
+            self.mixer.forward_fused(residual, self.mixer_norm, ctx, cache)
+            a = None
+        else:
+            h = self.mixer_norm.add_norm(residual, pending)
+            a = self.mixer.forward(h, ctx, cache)
+        if _fuses(self.feedforward, n, self.ff_norm):
+            if a is not None:
+                kernels.residual_add(residual, a)
+            self.feedforward.forward_fused(residual, self.ff_norm, ctx)
+            return residual, None
         h = self.ff_norm.add_norm(residual, a)
         m = self.feedforward.forward(h, ctx)
         return residual, m
+
+
+def _fuses(part, n_tokens: int, norm) -> bool:
+    can = getattr(part, "can_fuse", None)
+    return bool(can and can(n_tokens, norm))

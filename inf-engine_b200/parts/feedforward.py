@@ -32,13 +32,28 @@ class GatedMLP:
         self.rt = rt
         gate, up = tensors[spec.gate_proj], tensors[spec.up_proj]
         dtype = torch.float32 if torch.float32 in (gate.dtype, up.dtype) else gate.dtype
-        self.gate_up = Linear(torch.cat([gate.to(dtype), up.to(dtype)], dim=0).contiguous(), rt, "gate_up")
+        # rows alternate gate_j, up_j: one thread of a product's epilogue then holds both halves of a pair
+        both = torch.stack([gate.to(dtype), up.to(dtype)], dim=1).reshape(2 * spec.intermediate, spec.hidden)
+        self.gate_up = Linear(both.contiguous(), rt, "gate_up")
         self.down = Linear(tensors[spec.down_proj], rt, "down")
+
+    def can_fuse(self, n_tokens: int, norm) -> bool:
+        return (hasattr(norm, "fusable_rms") and self.gate_up.streams(n_tokens) and self.down.streams(n_tokens))
+
+    def forward_fused(self, residual: torch.Tensor, norm, ctx) -> None:
+        """residual += down(silu(gate(n)) * up(n)) with n = norm(residual), in two launches: the norm rides in
+        the first product's prologue, the activation in its epilogue, the sum in the second's epilogue."""
+        n = residual.shape[0]
+        s, ws = self.spec, self.rt.ws
+        gain, eps = norm.fusable_rms()
+        h = ws.take("ff_hidden", (n, s.intermediate), torch.bfloat16)
+        self.gate_up.stream(residual, h, n, "silu_mul", gain, eps)
+        self.down.stream(h, residual, n, "residual")
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         n = x.shape[0]
         s, ws, dt = self.spec, self.rt.ws, self.rt.act_dtype
         gu = self.gate_up(x, ws.take("ff_gate_up", (n, 2 * s.intermediate), dt))
         h = ws.take("ff_hidden", (n, s.intermediate), dt)
-        kernels.silu_mul(gu, h)
+        kernels.silu_mul(gu, h, interleaved=True)
         return self.down(h, ws.take("ff_out", (n, s.hidden), dt))

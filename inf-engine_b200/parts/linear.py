@@ -25,6 +25,18 @@ class Linear:
         self.name = name
         self.out_features, self.in_features = weight.shape
 
+    def streams(self, n_rows: int) -> bool:
+        """True when the weight-streaming kernel of this package takes this product:
+        bfloat16 weight and activations, few rows, K a multiple of 8."""
+        return (self.weight.dtype is torch.bfloat16 and self.rt.act_dtype is torch.bfloat16
+                and 0 < n_rows <= kernels.STREAM_BEST_ROWS and self.in_features % 8 == 0)
+
+    def stream(self, x: torch.Tensor, out: torch.Tensor, n_rows: int, epi: str = "bf16", gain=None, eps: float = 0.0,
+               row_index=None) -> torch.Tensor:
+        """The product through the weight-streaming kernel, with its fused prologue and epilogue."""
+        kernels.gemm_stream(x, self.weight, out, n_rows, epi, gain, eps, row_index)
+        return out
+
     def __call__(self, x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         """Write ``x @ W^T`` into ``out`` ([M, out_features], may be a column slice)."""
         w = self.weight
@@ -35,6 +47,8 @@ class Linear:
             kernels.gemm_simt(x, w, out)
             return out
         # bfloat16 x bfloat16
+        if self.streams(x.shape[0]) and out.dtype in (torch.bfloat16, torch.float32):
+            return self.stream(x, out, x.shape[0], "bf16" if out.dtype is torch.bfloat16 else "f32")
         if out.dtype is torch.bfloat16 and out.is_contiguous():
             torch.mm(x, w.t(), out=out)
         elif out.dtype is torch.float32 and out.is_contiguous():

@@ -73,6 +73,12 @@ class DecoderModel:
         m = ctx.n_logits
         if m == 0:
             return None
-        h = self.final_norm.gather_norm(residual, pending, ctx.logit_rows, m)
         logits = rt.ws.take("logits", (m, spec.vocab_size), torch.float32)
+        if self.head.streams(m) and hasattr(self.final_norm, "fusable_rms"):
+            # final norm on the gathered rows inside the head product
+            if pending is not None:
+                kernels.residual_add(residual, pending)
+            gain, eps = self.final_norm.fusable_rms()
+            return self.head.stream(residual, logits, m, "f32", gain, eps, row_index=ctx.logit_rows)
+        h = self.final_norm.gather_norm(residual, pending, ctx.logit_rows, m)
         return self.head(h, logits)

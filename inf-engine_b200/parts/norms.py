@@ -24,6 +24,10 @@ class RMSNorm:
         self.eps = float(spec.eps)
         self.size = spec.size
 
+    def fusable_rms(self):
+        """(gain, eps) for kernels that apply this norm inside a matrix product's prologue."""
+        return self.gain, self.eps
+
     def add_norm(self, residual: torch.Tensor, delta: torch.Tensor | None, out_name: str = "normed") -> torch.Tensor:
         out = self.rt.ws.take(out_name, tuple(residual.shape), self.rt.act_dtype)
         kernels.rmsnorm(residual, delta, self.gain, out, self.eps)

@@ -104,6 +104,9 @@ def test_silu_mul(act):
     k().silu_mul(gu, out)
     g, u = gu.float().cpu()[:, :inter], gu.float().cpu()[:, inter:]
     assert torch.allclose(out.float().cpu(), plain_llama.silu(g) * u, **tol(act))
+    k().silu_mul(gu, out, interleaved=True)
+    g, u = gu.float().cpu()[:, 0::2], gu.float().cpu()[:, 1::2]
+    assert torch.allclose(out.float().cpu(), plain_llama.silu(g) * u, **tol(act))
 
 
 @pytest.mark.parametrize("a_dt,w_dt,c_dt", [(torch.float32,) * 3, (torch.float32, torch.bfloat16, torch.float32),
@@ -126,6 +129,58 @@ def test_gemm_simt_is_float32_and_batch_invariant(a_dt, w_dt, c_dt):
     wide = torch.zeros(M, N + 11, device=DEV, dtype=c_dt)
     k().gemm_simt(a, w, wide[:, 11:])
     assert torch.equal(wide[:, 11:], out) and float(wide[:, :11].abs().sum()) == 0
+
+
+@pytest.mark.parametrize("M", [1, 8, 13, 16, 17, 40, 64])
+@pytest.mark.parametrize("N,K", [(389, 120), (96, 328), (2056, 512)])
+def test_gemm_stream_plain_and_fused(M, N, K):
+    torch.manual_seed(M * 1000 + N)
+    bf = torch.bfloat16
+    a = torch.randn(M, K, device=DEV).to(bf)
+    w = (torch.randn(N, K, device=DEV) * 0.1).to(bf)
+    ref = a.float().cpu() @ w.float().cpu().T
+    scale = float(ref.abs().max())
+    for nt in (1, 2, 4):
+        if M > 32 and nt == 4:
+            continue
+        out = torch.full((M, N), float("nan"), device=DEV, dtype=bf)
+        k().gemm_stream(a, w, out, M, "bf16", nt=nt)
+        assert float((out.float().cpu() - ref).abs().max()) <= 1e-2 * scale
+        out32 = torch.full((M, N), float("nan"), device=DEV)
+        k().gemm_stream(a, w, out32, M, "f32", nt=nt)
+        assert float((out32.cpu() - ref).abs().max()) <= 1e-4 * scale + 1e-5
+    # residual epilogue: float32 accumulate in place
+    res = torch.randn(M, N, device=DEV)
+    want = res.cpu() + ref
+    k().gemm_stream(a, w, res, M, "residual")
+    assert float((res.cpu() - want).abs().max()) <= 1e-4 * scale + 1e-5
+    # fused RMSNorm prologue on the float32 residual stream, rows gathered
+    x = torch.randn(M + 5, K, device=DEV) * 2
+    rows = torch.randperm(M + 5)[:M].to(torch.int32).to(DEV)
+    for gain_dtype in (bf, torch.float32):
+        gain = (1 + 0.1 * torch.randn(K, device=DEV)).to(gain_dtype)
+        normed = plain_llama.rms_norm(x.cpu()[rows.long().cpu()], gain.float().cpu(), 1e-5)
+        want = normed @ w.float().cpu().T
+        out32 = torch.empty(M, N, device=DEV)
+        k().gemm_stream(x, w, out32, M, "f32", gain=gain, eps=1e-5, row_index=rows)
+        assert float((out32.cpu() - want).abs().max()) <= 1e-2 * float(want.abs().max())
+    # silu(gate)*up over interleaved rows
+    if N % 2 == 0:
+        out = torch.empty(M, N // 2, device=DEV, dtype=bf)
+        k().gemm_stream(a, w, out, M, "silu_mul")
+        want = plain_llama.silu(ref[:, 0::2]) * ref[:, 1::2]
+        assert float((out.float().cpu() - want).abs().max()) <= 1e-2 * max(1.0, float(want.abs().max()))
+
+
+def test_gemm_stream_refuses_what_it_cannot_take():
+    from inf_engine_b200.kernels import KernelError
+    bf = torch.bfloat16
+    a, w = torch.zeros(65, 64, device=DEV, dtype=bf), torch.zeros(8, 64, device=DEV, dtype=bf)
+    with pytest.raises(KernelError, match="size"):
+        k().gemm_stream(a, w, torch.zeros(65, 8, device=DEV, dtype=bf), 65)
+    a, w = torch.zeros(4, 12, device=DEV, dtype=bf), torch.zeros(8, 12, device=DEV, dtype=bf)
+    with pytest.raises(KernelError, match="size"):
+        k().gemm_stream(a, w, torch.zeros(4, 8, device=DEV, dtype=bf), 4)
 
 
 def paged_reference(q, kd, vd, q_lens, ctx_before, H, Hk, hd, window):
