@@ -10,5 +10,5 @@ def all_build_requests():
     reqs = [("core", LIBRARIES["core"], {}, [])]
     reqs.append(("stream", ["gemm_stream.cu"], {}, []))
     for hd in (64, 128):
-        reqs.append((f"attn_mma_hd{hd}", ["attention_mma.cu"], {"IE_HD": hd}, []))
+        reqs.append((f"attn_mma_hd{hd}", ["attention_mma.cu"], {"IE_HD": hd}, ["attention_noalloc.h"]))
     return reqs

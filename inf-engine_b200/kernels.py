@@ -194,7 +194,7 @@ def attention_mma_library(head_dim: int):
         raise KernelError(f"tensor-core attention is built for head sizes {MMA_HEAD_DIMS}, not {head_dim}")
     lib = _mma.get(head_dim)
     if lib is None:
-        lib = load_library(f"attn_mma_hd{head_dim}", ["attention_mma.cu"], {"IE_HD": head_dim})
+        lib = load_library(f"attn_mma_hd{head_dim}", ["attention_mma.cu"], {"IE_HD": head_dim}, ["attention_noalloc.h"])
         P, I, F = c_void_p, c_int, c_float
         lib.ie_attention_prefill.argtypes = [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P]
         lib.ie_attention_prefill.restype = c_int
