@@ -498,3 +498,45 @@ extern "C" int ie_attention_decode(const void* q, void* out, const void* kpool, 
                                                                 out_stride);
   return launch_status();
 }
+
+// ------------------------------------------------- decode without any allocation
+// See attention_noalloc.h.  The scratch of the split pass is this static array;
+// host code may not use its name as a pointer (on the host it is only a handle
+// for the runtime), so the device address is looked up once per device.
+#include "attention_noalloc.h"
+
+static __device__ __align__(256) float g_noalloc_scratch[IE_NOALLOC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int NOALLOC_MAX_DEVICES = 64;
+float* g_noalloc_ptr[NOALLOC_MAX_DEVICES] = {nullptr};
+}  // namespace
+
+extern "C" long long ie_attention_decode_noalloc_capacity(void) { return (long long)IE_NOALLOC_SCRATCH_FLOATS; }
+
+extern "C" int ie_attention_decode_noalloc(const void* q, void* out, const void* kpool, const void* vpool,
+                                           const int* block_table, const int* q_start, const int* ctx_before,
+                                           int q_stride, int out_stride, int table_stride, int n_requests,
+                                           int n_tokens, int n_heads, int n_kv_heads, int hd, int page_size,
+                                           int window, float scale, int n_splits, int split_keys,
+                                           cudaStream_t stream) {
+  if (n_requests <= 0) return IE_OK;
+  if (n_tokens <= 0 || n_heads <= 0 || n_splits <= 0) return IE_BAD_SIZE;
+  const long long need = (long long)n_tokens * n_heads * n_splits * (HD + 2);
+  if (need > (long long)IE_NOALLOC_SCRATCH_FLOATS) return IE_NOALLOC_TOO_LARGE;
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= NOALLOC_MAX_DEVICES) return IE_BAD_SIZE;
+  if (g_noalloc_ptr[dev] == nullptr) {
+    // first call on this device, with it current: the array's address in device memory
+    float* ptr = nullptr;
+    e = cudaGetSymbolAddress((void**)&ptr, g_noalloc_scratch);
+    if (e != cudaSuccess) return (int)e;
+    if (ptr == nullptr) return IE_BAD_ALIGN;
+    g_noalloc_ptr[dev] = ptr;
+  }
+  return ie_attention_decode(q, out, kpool, vpool, block_table, q_start, ctx_before, g_noalloc_ptr[dev], q_stride,
+                             out_stride, table_stride, n_requests, n_tokens, n_heads, n_kv_heads, hd, page_size,
+                             window, scale, n_splits, split_keys, stream);
+}
