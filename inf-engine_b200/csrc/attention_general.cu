@@ -42,6 +42,8 @@ struct AttnGeneralParams {
 template <typename T>
 __global__ void __launch_bounds__(AG_THREADS) attention_general_kernel(AttnGeneralParams p) {
   extern __shared__ float smem[];
+  pdl_trigger();
+  pdl_wait();
   const int hd = p.hd;
   const int ldq = hd + 1;
   float* Qs = smem;                      // [ROWS][hd+1]
@@ -201,13 +203,11 @@ extern "C" int ie_attention_general(const void* q, void* out, const void* kpool,
   if (act_dtype == IE_F32) {
     e = cudaFuncSetAttribute(attention_general_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    attention_general_kernel<float><<<grid, AG_THREADS, smem, stream>>>(p);
+    return launch_k(attention_general_kernel<float>, grid, AG_THREADS, smem, stream, p);
   } else if (act_dtype == IE_BF16) {
     e = cudaFuncSetAttribute(attention_general_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    attention_general_kernel<bf16><<<grid, AG_THREADS, smem, stream>>>(p);
-  } else {
-    return IE_BAD_DTYPE;
+    return launch_k(attention_general_kernel<bf16>, grid, AG_THREADS, smem, stream, p);
   }
-  return launch_status();
+  return IE_BAD_DTYPE;
 }

@@ -39,8 +39,10 @@ struct MmaAttnParams {
   const int* work_pair0;
   float* part_o;   // decode: [n_tokens*n_heads, n_splits, HD]
   float* part_ml;  // decode: [n_tokens*n_heads, n_splits, 2]
+  int* tickets;    // decode: [n_requests * n_kv_heads], zero between launches
   int q_stride, out_stride, table_stride;
   int n_heads, n_kv_heads, page_size, window;
+  int page_shift;  // log2(page_size) when it is a power of two, else -1
   int n_splits, split_keys;
   float scale_log2;
 };
@@ -87,22 +89,51 @@ __device__ __forceinline__ uint32_t swz(int row, int chunk) {
 
 // Copy keys [k0, k0+KT) of kv head c (K and V) into shared memory, zero where a key
 // is outside [0, k_end) or its page is not held.
+// Page and offset of key kp: shifts when the page size is a power of two (the usual case), a
+// division otherwise; the address arithmetic of a tile must stay far cheaper than its memory latency.
+__device__ __forceinline__ void page_of(const MmaAttnParams& p, int kp, int& page_index, int& offset) {
+  if (p.page_shift >= 0) {
+    page_index = kp >> p.page_shift;
+    offset = kp & (p.page_size - 1);
+  } else {
+    page_index = kp / p.page_size;
+    offset = kp - page_index * p.page_size;
+  }
+}
+
 template <int KT, int NTHREADS>
 __device__ __forceinline__ void load_kv_tile(const MmaAttnParams& p, const int* table, int c, int k0, int k_end,
                                              uint32_t ks_addr, uint32_t vs_addr, int tid) {
+  constexpr int ITERS = (KT * CHUNKS + NTHREADS - 1) / NTHREADS;
+  constexpr int ROWS_PER_ITER = NTHREADS / CHUNKS;
+  static_assert(NTHREADS % CHUNKS == 0, "a thread keeps its chunk column over the iterations");
+  // a thread copies chunk `chunk` of rows row0, row0 + ROWS_PER_ITER, ...; first every page lookup
+  // (independent loads that overlap), then the copies: a copy is a volatile statement, and a lookup
+  // placed after it would have to wait for it
+  const int row0 = tid / CHUNKS, chunk = tid - row0 * CHUNKS;
+  int src_row[ITERS];   // row of the pool ((page * kv_heads + c) * page_size + offset), or -1
 #pragma unroll
-  for (int idx = tid; idx < KT * CHUNKS; idx += NTHREADS) {
-    const int row = idx / CHUNKS, chunk = idx - row * CHUNKS;
+  for (int it = 0; it < ITERS; ++it) {
+    const int row = row0 + it * ROWS_PER_ITER;
     const int kp = k0 + row;
-    bool valid = kp < k_end && kp >= 0;
-    int page = -1;
-    if (valid) page = table[kp / p.page_size];
-    valid = valid && page >= 0;
-    size_t off = 0;
-    if (valid) off = (((size_t)page * p.n_kv_heads + c) * p.page_size + (kp % p.page_size)) * HD + chunk * 8;
-    const uint32_t so = swz(row, chunk);
-    cp_async16(ks_addr + so, p.kpool + off, valid);
-    cp_async16(vs_addr + so, p.vpool + off, valid);
+    src_row[it] = -1;
+    if (row < KT && kp < k_end && kp >= 0) {
+      int pi, po;
+      page_of(p, kp, pi, po);
+      const int page = __ldg(table + pi);
+      if (page >= 0) src_row[it] = (page * p.n_kv_heads + c) * p.page_size + po;
+    }
+  }
+#pragma unroll
+  for (int it = 0; it < ITERS; ++it) {
+    const int row = row0 + it * ROWS_PER_ITER;
+    if (row < KT) {
+      const bool valid = src_row[it] >= 0;
+      const size_t off = valid ? (size_t)src_row[it] * HD + chunk * 8 : 0;
+      const uint32_t so = swz(row, chunk);
+      cp_async16(ks_addr + so, p.kpool + off, valid);
+      cp_async16(vs_addr + so, p.vpool + off, valid);
+    }
   }
 }
 
@@ -212,6 +243,8 @@ constexpr int PF_STAGE_BYTES = 2 * PF_KT * HD * 2;  // K and V of one stage
 
 __global__ void __launch_bounds__(PF_THREADS) attention_prefill_kernel(MmaAttnParams p) {
   extern __shared__ __align__(128) unsigned char smem[];
+  pdl_trigger();
+  pdl_wait();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int c = blockIdx.y;
   const int r_id = p.work_req[blockIdx.x];
@@ -301,18 +334,32 @@ __global__ void __launch_bounds__(PF_THREADS) attention_prefill_kernel(MmaAttnPa
 }
 
 // -------------------------------------------------------------------- decode
-// One warp per split of the keys: block (x, kv head, request) holds splits
-// 4x .. 4x+3.  A request brings at most 16 rows (q_len * group <= 16).  Each warp
-// writes its unnormalised output, maximum and sum; the merge kernel combines the
-// splits in ascending order.
-constexpr int DC_WARPS = 4;
+// One warp per split of the keys: block (x, kv head, request) is one warp, so that a
+// whole step's blocks are resident at once and none waits for a slot.  A request brings at most 16 rows (q_len * group <= 16).
+// A warp keeps up to DC_STAGES key tiles in flight at once (a decode step is a
+// matter of latency: few bytes per warp, all of them wanted as early as
+// possible), writes its unnormalised output, maximum and sum, and takes a ticket
+// of its (request, kv head); the warp that takes the last ticket adds the splits
+// up in ascending order, so the result does not depend on which warp that is.
+constexpr int DC_WARPS = 1;
 constexpr int DC_THREADS = DC_WARPS * 32;
 constexpr int DC_KT = 32;
+constexpr int DC_STAGES = 4;
 constexpr int DC_STAGE_BYTES = 2 * DC_KT * HD * 2;
-constexpr int DC_WARP_BYTES = 2 * DC_STAGE_BYTES;
+constexpr int DC_WARP_BYTES = DC_STAGES * DC_STAGE_BYTES;
+
+__device__ __forceinline__ void cp_async_wait_pending(int pending) {
+  switch (pending) {
+    case 0: cp_async_wait<0>(); break;
+    case 1: cp_async_wait<1>(); break;
+    case 2: cp_async_wait<2>(); break;
+    default: cp_async_wait<3>(); break;
+  }
+}
 
 __global__ void __launch_bounds__(DC_THREADS) attention_decode_kernel(MmaAttnParams p) {
   extern __shared__ __align__(128) unsigned char smem[];
+  pdl_trigger();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int split = blockIdx.x * DC_WARPS + warp;
   const int c = blockIdx.y, r_id = blockIdx.z;
@@ -322,7 +369,6 @@ __global__ void __launch_bounds__(DC_THREADS) attention_decode_kernel(MmaAttnPar
   const int ctx = p.ctx_before[r_id];
   const int n_pairs = q_len * group;
   const int* table = p.block_table + (size_t)r_id * p.table_stride;
-  if (split >= p.n_splits) return;
 
   const int pr0 = lane >> 2, pr1 = pr0 + 8;
   const bool v0 = pr0 < n_pairs, v1 = pr1 < n_pairs;
@@ -332,40 +378,59 @@ __global__ void __launch_bounds__(DC_THREADS) attention_decode_kernel(MmaAttnPar
   const int first1 = p.window > 0 ? max(0, lim1 - p.window + 1) : 0;
   const int max_lim = ctx + q_len - 1;
   const int min_first = p.window > 0 ? max(0, ctx - p.window + 1) : 0;
+  const int lo_all = (min_first / DC_KT) * DC_KT;
 
-  const int k_lo = max(split * p.split_keys, (min_first / DC_KT) * DC_KT);
+  // splits that hold at least one key some row can see
+  const int s_first = lo_all / p.split_keys, s_last = max_lim / p.split_keys;
+  const int n_active = s_last - s_first + 1;
+  const int k_lo = max(split * p.split_keys, lo_all);
   const int k_hi = min((split + 1) * p.split_keys, max_lim + 1);
+  const bool has_work = split >= s_first && split <= s_last && split < p.n_splits && n_pairs > 0;
+  // A block without keys leaves at once and frees its slot.  It need not wait for the kernel ahead:
+  // split 0 of every (request, kv head) always has keys and waits, so this kernel still ends after it.
+  if (!has_work) return;
 
   float o[NT_O][4];
 #pragma unroll
   for (int i = 0; i < NT_O; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
-  if (k_lo < k_hi && n_pairs > 0) {
+  // Lengths, block tables and the keys of earlier steps are not written by this step's kernels:
+  // tiles of old keys only are fetched before the kernel ahead has finished.
+  const uint32_t base = smem_u32(smem) + warp * DC_WARP_BYTES;
+  const int n_tiles = (k_hi - k_lo + DC_KT - 1) / DC_KT;
+  const int n_first = min(n_tiles, DC_STAGES);
+  int issued = 0;
+  for (; issued < n_first && k_lo + (issued + 1) * DC_KT <= ctx; ++issued) {
+    const uint32_t sb = base + issued * DC_STAGE_BYTES;
+    load_kv_tile<DC_KT, 32>(p, table, c, k_lo + issued * DC_KT, k_hi, sb, sb + DC_KT * HD * 2, lane);
+    cp_async_commit();
+  }
+  pdl_wait();
+  for (; issued < n_first; ++issued) {
+    const uint32_t sb = base + issued * DC_STAGE_BYTES;
+    load_kv_tile<DC_KT, 32>(p, table, c, k_lo + issued * DC_KT, k_hi, sb, sb + DC_KT * HD * 2, lane);
+    cp_async_commit();
+  }
+  {
     const bf16* qr0 = v0 ? p.q + (size_t)(q0 + t0) * p.q_stride + (c * group + (pr0 - t0 * group)) * HD : nullptr;
     const bf16* qr1 = v1 ? p.q + (size_t)(q0 + t1) * p.q_stride + (c * group + (pr1 - t1 * group)) * HD : nullptr;
     uint32_t qf[KSTEPS][4];
     load_q_frags(qf, qr0, qr1, lane);
-    const uint32_t base = smem_u32(smem) + warp * DC_WARP_BYTES;
-    const int n_tiles = (k_hi - k_lo + DC_KT - 1) / DC_KT;
-    load_kv_tile<DC_KT, 32>(p, table, c, k_lo, k_hi, base, base + DC_KT * HD * 2, lane);
-    cp_async_commit();
     for (int i = 0; i < n_tiles; ++i) {
       const int k0 = k_lo + i * DC_KT;
-      if (i + 1 < n_tiles) {
-        const uint32_t nb = base + ((i + 1) & 1) * DC_STAGE_BYTES;
-        load_kv_tile<DC_KT, 32>(p, table, c, k0 + DC_KT, k_hi, nb, nb + DC_KT * HD * 2, lane);
-        cp_async_commit();
-        cp_async_wait<1>();
-      } else {
-        cp_async_wait<0>();
-      }
+      cp_async_wait_pending(issued - (i + 1));
       __syncwarp();
-      const uint32_t sb = base + (i & 1) * DC_STAGE_BYTES;
+      const uint32_t sb = base + (i % DC_STAGES) * DC_STAGE_BYTES;
       const bool need_mask = (k0 + DC_KT - 1 > ctx) || (p.window > 0);
       warp_tile<DC_KT>(qf, o, m, l, sb, sb + DC_KT * HD * 2, k0, lim0, lim1, first0, first1, need_mask,
                        p.scale_log2, lane);
       __syncwarp();
+      if (issued < n_tiles) {
+        load_kv_tile<DC_KT, 32>(p, table, c, k_lo + issued * DC_KT, k_hi, sb, sb + DC_KT * HD * 2, lane);
+        cp_async_commit();
+        ++issued;
+      }
     }
   }
   l[0] += __shfl_xor_sync(0xffffffffu, l[0], 1);
@@ -387,29 +452,87 @@ __global__ void __launch_bounds__(DC_THREADS) attention_decode_kernel(MmaAttnPar
     for (int i = 0; i < NT_O; ++i) *reinterpret_cast<float2*>(po + i * 8 + col) = make_float2(o[i][2], o[i][3]);
     if ((lane & 3) == 0) *reinterpret_cast<float2*>(p.part_ml + (row * p.n_splits + split) * 2) = make_float2(m[1], l[1]);
   }
-}
 
-// out[row] = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M), splits in ascending order
-__global__ void __launch_bounds__(HD) attention_merge_kernel(const float* __restrict__ part_o,
-                                                             const float* __restrict__ part_ml, bf16* __restrict__ out,
-                                                             int n_heads, int n_splits, int out_stride) {
-  const int row = blockIdx.x;  // token * n_heads + head
-  const int d = threadIdx.x;
-  const float* ml = part_ml + (size_t)row * n_splits * 2;
-  float M = -INFINITY;
-  for (int s = 0; s < n_splits; ++s) M = fmaxf(M, ml[2 * s]);
-  float acc = 0.f, den = 0.f;
-  if (M > -INFINITY) {
-    for (int s = 0; s < n_splits; ++s) {
-      const float ms = ml[2 * s];
-      if (ms == -INFINITY) continue;
-      const float w = fast_exp2(ms - M);
-      acc += w * part_o[((size_t)row * n_splits + s) * HD + d];
-      den += w * ml[2 * s + 1];
+  // ticket of this (request, kv head): the last warp to arrive merges
+  __threadfence();
+  __syncwarp();
+  int* ticket = p.tickets + r_id * p.n_kv_heads + c;
+  int mine = 0;
+  if (lane == 0) mine = atomicAdd(ticket, 1);
+  mine = __shfl_sync(0xffffffffu, mine, 0);
+  if (mine != n_active - 1) return;
+  __threadfence();
+  if (lane == 0) *ticket = 0;   // ready for the next launch
+
+  // out[row] = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M), splits in ascending order.
+  // Lane L owns dims [L*DPL, L*DPL+DPL) of a row.  The partials come from L2 (other SMs wrote them);
+  // four rows are merged side by side so that their loads are in flight together, eight splits at a time.
+  constexpr int DPL = HD / 32;
+  constexpr int RG = 4;   // rows merged together
+  for (int pg = 0; pg < n_pairs; pg += RG) {
+    const float2* ml[RG];
+    const float* po[RG];
+    bf16* dst[RG];
+    float M[RG], den[RG], acc[RG][DPL];
+#pragma unroll
+    for (int r = 0; r < RG; ++r) {
+      const int pr = min(pg + r, n_pairs - 1);   // rows past the end repeat the last one and are not stored
+      const int t = pr / group;
+      const size_t row = (size_t)(q0 + t) * p.n_heads + c * group + (pr - t * group);
+      ml[r] = reinterpret_cast<const float2*>(p.part_ml + (row * p.n_splits + s_first) * 2);
+      po[r] = p.part_o + (row * p.n_splits + s_first) * HD + lane * DPL;
+      dst[r] = p.out + (size_t)(q0 + t) * p.out_stride + (c * group + (pr - t * group)) * HD + lane * DPL;
+      M[r] = -INFINITY;
+      den[r] = 0.f;
+#pragma unroll
+      for (int d = 0; d < DPL; ++d) acc[r][d] = 0.f;
+    }
+    for (int j = lane; j < n_active; j += 32) {
+#pragma unroll
+      for (int r = 0; r < RG; ++r) M[r] = fmaxf(M[r], __ldcg(ml[r] + j).x);
+    }
+#pragma unroll
+    for (int r = 0; r < RG; ++r) M[r] = warp_max(M[r]);
+    for (int j0 = 0; j0 < n_active; j0 += 8) {
+      float2 mlv[RG][8];
+      float v[RG][8][DPL];
+#pragma unroll
+      for (int r = 0; r < RG; ++r) {
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int j = min(j0 + u, n_active - 1);   // the tail repeats the last split and gets weight 0
+          mlv[r][u] = __ldcg(ml[r] + j);
+          if (DPL == 2) {
+            const float2 x = __ldcg(reinterpret_cast<const float2*>(po[r] + (size_t)j * HD));
+            v[r][u][0] = x.x; v[r][u][1 % DPL] = x.y;
+          } else {
+            const float4 x = __ldcg(reinterpret_cast<const float4*>(po[r] + (size_t)j * HD));
+            v[r][u][0] = x.x; v[r][u][1 % DPL] = x.y; v[r][u][2 % DPL] = x.z; v[r][u][3 % DPL] = x.w;
+          }
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < RG; ++r) {
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const bool real = j0 + u < n_active && mlv[r][u].x > -INFINITY && M[r] > -INFINITY;
+          const float w = real ? fast_exp2(mlv[r][u].x - M[r]) : 0.f;
+          den[r] += w * mlv[r][u].y;
+#pragma unroll
+          for (int d = 0; d < DPL; ++d) acc[r][d] += w * v[r][u][d];
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < RG; ++r) {
+      if (pg + r < n_pairs) {
+        const float inv = den[r] > 0.f ? 1.f / den[r] : 0.f;
+#pragma unroll
+        for (int d = 0; d < DPL; d += 2)
+          *reinterpret_cast<uint32_t*>(dst[r] + d) = pack_bf16(acc[r][d] * inv, acc[r][d + 1] * inv);
+      }
     }
   }
-  const int token = row / n_heads, head = row - token * n_heads;
-  out[(size_t)token * out_stride + head * HD + d] = __float2bfloat16_rn(den > 0.f ? acc / den : 0.f);
 }
 
 static void fill(MmaAttnParams& p, const void* q, void* out, const void* kpool, const void* vpool,
@@ -417,14 +540,19 @@ static void fill(MmaAttnParams& p, const void* q, void* out, const void* kpool, 
                  int table_stride, int n_heads, int n_kv_heads, int page_size, int window, float scale) {
   p.q = (const bf16*)q; p.out = (bf16*)out; p.kpool = (const bf16*)kpool; p.vpool = (const bf16*)vpool;
   p.block_table = block_table; p.q_start = q_start; p.ctx_before = ctx_before;
-  p.work_req = nullptr; p.work_pair0 = nullptr; p.part_o = nullptr; p.part_ml = nullptr;
+  p.work_req = nullptr; p.work_pair0 = nullptr; p.part_o = nullptr; p.part_ml = nullptr; p.tickets = nullptr;
   p.q_stride = q_stride; p.out_stride = out_stride; p.table_stride = table_stride;
   p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.page_size = page_size; p.window = window;
   p.n_splits = 0; p.split_keys = 0; p.scale_log2 = scale * LOG2E;
+  p.page_shift = -1;
+  if ((page_size & (page_size - 1)) == 0)
+    for (int b = 0; b < 31; ++b)
+      if ((1 << b) == page_size) p.page_shift = b;
 }
 
 static int check_common(const void* q, const void* out, const void* kpool, const void* vpool, int q_stride,
                         int out_stride, int n_heads, int n_kv_heads, int hd, int page_size) {
+  // pool rows (page * kv_heads + head) * page_size + offset are 32-bit in the kernels: pools of up to 2^31 rows
   if (hd != HD) return IE_BAD_SIZE;
   if (n_kv_heads <= 0 || n_heads % n_kv_heads || page_size <= 0) return IE_BAD_SIZE;
   if (((uintptr_t)q | (uintptr_t)out) & 3) return IE_BAD_ALIGN;
@@ -457,14 +585,20 @@ extern "C" int ie_attention_prefill(const void* q, void* out, const void* kpool,
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
-  attention_prefill_kernel<<<dim3(n_work, n_kv_heads), PF_THREADS, smem, stream>>>(p);
-  return launch_status();
+  return launch_k(attention_prefill_kernel, dim3(n_work, n_kv_heads), PF_THREADS, smem, stream, p);
 }
 
-// Scratch needed by the decode kernel, in floats: part_o then part_ml.
+// Scratch needed by the decode kernel, in 4-byte words: IE_DECODE_TICKET_WORDS tickets (one per
+// request and kv head) at the start, then partial outputs, then maxima and sums.  The tickets
+// must be zero before the first launch on a piece of scratch; every launch leaves them zero
+// again, whatever the batch, because they always sit in the same place.  The rest may hold anything.
+#define IE_DECODE_TICKET_WORDS 4096
+#define IE_DECODE_MAX_ACTIVE_SPLITS 64
 extern "C" long long ie_attention_decode_scratch_floats(int n_tokens, int n_heads, int n_splits) {
-  return (long long)n_tokens * n_heads * n_splits * (HD + 2);
+  return IE_DECODE_TICKET_WORDS + (long long)n_tokens * n_heads * n_splits * (HD + 2);
 }
+// Words at the start of that scratch that must be zero before its first use.
+extern "C" long long ie_attention_decode_ticket_words() { return IE_DECODE_TICKET_WORDS; }
 
 extern "C" int ie_attention_decode(const void* q, void* out, const void* kpool, const void* vpool,
                                    const int* block_table, const int* q_start, const int* ctx_before, float* scratch,
@@ -481,8 +615,10 @@ extern "C" int ie_attention_decode(const void* q, void* out, const void* kpool, 
        n_kv_heads, page_size, window, scale);
   p.n_splits = n_splits;
   p.split_keys = split_keys;
-  p.part_o = scratch;
-  p.part_ml = scratch + (size_t)n_tokens * n_heads * n_splits * HD;
+  if ((long long)n_requests * n_kv_heads > IE_DECODE_TICKET_WORDS || n_splits > IE_DECODE_MAX_ACTIVE_SPLITS) return IE_BAD_SIZE;
+  p.tickets = reinterpret_cast<int*>(scratch);
+  p.part_o = scratch + IE_DECODE_TICKET_WORDS;
+  p.part_ml = p.part_o + (size_t)n_tokens * n_heads * n_splits * HD;
   const int smem = DC_WARPS * DC_WARP_BYTES;
   static bool attr_set = false;
   if (!attr_set) {
@@ -491,12 +627,7 @@ extern "C" int ie_attention_decode(const void* q, void* out, const void* kpool, 
     attr_set = true;
   }
   dim3 grid((n_splits + DC_WARPS - 1) / DC_WARPS, n_kv_heads, n_requests);
-  attention_decode_kernel<<<grid, DC_THREADS, smem, stream>>>(p);
-  rc = launch_status();
-  if (rc) return rc;
-  attention_merge_kernel<<<n_tokens * n_heads, HD, 0, stream>>>(p.part_o, p.part_ml, p.out, n_heads, n_splits,
-                                                                out_stride);
-  return launch_status();
+  return launch_k(attention_decode_kernel, grid, DC_THREADS, smem, stream, p);
 }
 
 // ------------------------------------------------- decode without any allocation
@@ -522,7 +653,7 @@ extern "C" int ie_attention_decode_noalloc(const void* q, void* out, const void*
                                            cudaStream_t stream) {
   if (n_requests <= 0) return IE_OK;
   if (n_tokens <= 0 || n_heads <= 0 || n_splits <= 0) return IE_BAD_SIZE;
-  const long long need = (long long)n_tokens * n_heads * n_splits * (HD + 2);
+  const long long need = ie_attention_decode_scratch_floats(n_tokens, n_heads, n_splits);
   if (need > (long long)IE_NOALLOC_SCRATCH_FLOATS) return IE_NOALLOC_TOO_LARGE;
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);

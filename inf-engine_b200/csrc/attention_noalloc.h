@@ -12,15 +12,18 @@
  *
  * - The array holds IE_NOALLOC_SCRATCH_FLOATS floats.  Every GPU that loads the
  *   library keeps that much memory until the process exits.
- * - A call needs n_tokens * n_heads * n_splits * (head_dim + 2) floats and is
+ * - A call needs 4096 + n_tokens * n_heads * n_splits * (head_dim + 2) words and is
  *   refused with IE_NOALLOC_TOO_LARGE when that exceeds the array.
  * - The first call on a device looks the array's device address up
  *   (cudaGetSymbolAddress) and remembers it; make that first call before any
  *   stream capture begins.  Later calls on the device only launch.
- * - All calls share the array and it keeps what the last call left.  Nothing in
- *   it has to start at zero: the first pass writes every element that the merge
- *   pass reads.  Two calls that overlap on the GPU (different streams) race on
- *   it; keep calls on one device in one stream or order them yourself.
+ * - All calls share the array and it keeps what the last call left.  Only the
+ *   tickets at its start (one per request and kv head, counting the splits that
+ *   have finished) have to be zero when a call starts: static device memory
+ *   starts as zeros and every call that completes puts its tickets back to zero.
+ *   Everything else is written before it is read.  Two calls that overlap on the
+ *   GPU (different streams) race on the array; keep calls on one device in one
+ *   stream or order them yourself.
  * - No cudaMalloc, cudaFree or allocating library routine is called.
  *
  * Arguments are those of ie_attention_decode without its scratch pointer; the

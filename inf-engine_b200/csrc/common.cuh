@@ -8,6 +8,9 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
+#include <tuple>
+#include <utility>
 
 #define IE_OK 0
 #define IE_BAD_DTYPE -1
@@ -72,3 +75,56 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 }
 
 static inline int launch_status() { return (int)cudaGetLastError(); }
+
+// ---------------------------------------------------- programmatic dependent launch
+// Every kernel of this package is launched so that it may start while the kernel
+// before it in the stream is still running (its blocks become resident once all
+// blocks of the predecessor have called pdl_trigger or exited).  A kernel may
+// read only data that no kernel writes (weights, tables, the step's metadata
+// copied in before the step) until it has called pdl_wait, which returns when the
+// predecessor has finished and its writes are visible; it writes nothing before
+// that.  This hides launch latency and lets weight-streaming kernels fetch their
+// first weights early.  Every block calls pdl_wait, so completion of a kernel
+// implies completion of everything before it.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+static inline bool pdl_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("IE_NO_PDL");
+    on = (e && e[0] == '1') ? 0 : 1;
+  }
+  return on == 1;
+}
+
+static inline int launch_raw(const void* kernel, dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                             void** args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return (int)cudaLaunchKernelExC(&cfg, kernel, args);
+}
+
+template <typename Tuple, size_t... I>
+static inline void tuple_pointers(Tuple& t, void** out, std::index_sequence<I...>) {
+  ((out[I] = (void*)&std::get<I>(t)), ...);
+}
+
+// launch_k(kernel, grid, block, smem, stream, args...): arguments are converted to the kernel's parameter types
+template <typename... KArgs, typename... Args>
+static inline int launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                           Args... args) {
+  static_assert(sizeof...(KArgs) == sizeof...(Args), "kernel argument count");
+  std::tuple<KArgs...> vals{static_cast<KArgs>(args)...};
+  void* ptrs[sizeof...(KArgs) ? sizeof...(KArgs) : 1];
+  tuple_pointers(vals, ptrs, std::index_sequence_for<KArgs...>{});
+  return launch_raw((const void*)kernel, grid, block, smem, stream, ptrs);
+}

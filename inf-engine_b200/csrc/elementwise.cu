@@ -10,6 +10,8 @@
 template <typename TW>
 __global__ void embed_gather_kernel(const int* __restrict__ ids, const TW* __restrict__ table,
                                     float* __restrict__ residual, int d, int vocab) {
+  pdl_trigger();
+  pdl_wait();
   const int n = blockIdx.x;
   int id = ids[n];
   const bool ok = id >= 0 && id < vocab;
@@ -23,12 +25,10 @@ extern "C" int ie_embed_gather(const int* ids, const void* table, int table_dtyp
   if (n_tokens <= 0) return IE_OK;
   const int threads = d >= 1024 ? 256 : 128;
   if (table_dtype == IE_F32)
-    embed_gather_kernel<float><<<n_tokens, threads, 0, stream>>>(ids, (const float*)table, residual, d, vocab);
-  else if (table_dtype == IE_BF16)
-    embed_gather_kernel<bf16><<<n_tokens, threads, 0, stream>>>(ids, (const bf16*)table, residual, d, vocab);
-  else
-    return IE_BAD_DTYPE;
-  return launch_status();
+    return launch_k(embed_gather_kernel<float>, n_tokens, threads, 0, stream, ids, (const float*)table, residual, d, vocab);
+  if (table_dtype == IE_BF16)
+    return launch_k(embed_gather_kernel<bf16>, n_tokens, threads, 0, stream, ids, (const bf16*)table, residual, d, vocab);
+  return IE_BAD_DTYPE;
 }
 
 // -------------------------------------------------------------------- RMSNorm
@@ -41,6 +41,8 @@ __global__ void rmsnorm_kernel(float* __restrict__ residual, const TA* __restric
                                const int* __restrict__ row_index, int d, float eps) {
   extern __shared__ float xs[];
   __shared__ float red[33];
+  pdl_trigger();
+  pdl_wait();
   const int m = blockIdx.x;
   const int row = row_index ? row_index[m] : m;
   float* res = residual + (size_t)row * d;
@@ -69,9 +71,8 @@ static int launch_rmsnorm(float* residual, const void* delta, const void* gain, 
     if (e != cudaSuccess) return (int)e;
   }
   const int threads = d >= 2048 ? 512 : (d >= 512 ? 256 : 128);
-  rmsnorm_kernel<TA, TW><<<n_rows, threads, smem, stream>>>(residual, (const TA*)delta, (const TW*)gain, (TA*)out,
-                                                             row_index, d, eps);
-  return launch_status();
+  return launch_k(rmsnorm_kernel<TA, TW>, n_rows, threads, smem, stream, residual, (const TA*)delta, (const TW*)gain,
+                  (TA*)out, row_index, d, eps);
 }
 
 extern "C" int ie_rmsnorm(float* residual, const void* delta, const void* gain, int gain_dtype, void* out,
@@ -91,6 +92,8 @@ extern "C" int ie_rmsnorm(float* residual, const void* delta, const void* gain, 
 // residual[n, :] += delta[n, :]   (for a block arrangement that has no norm to fuse the sum into)
 template <typename TA>
 __global__ void residual_add_kernel(float* __restrict__ residual, const TA* __restrict__ delta, size_t n) {
+  pdl_trigger();
+  pdl_wait();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) residual[i] += to_f32(delta[i]);
 }
@@ -99,13 +102,9 @@ extern "C" int ie_residual_add(float* residual, const void* delta, int act_dtype
   const size_t n = (size_t)n_rows * d;
   if (n == 0) return IE_OK;
   const unsigned blocks = (unsigned)((n + 255) / 256);
-  if (act_dtype == IE_F32)
-    residual_add_kernel<float><<<blocks, 256, 0, stream>>>(residual, (const float*)delta, n);
-  else if (act_dtype == IE_BF16)
-    residual_add_kernel<bf16><<<blocks, 256, 0, stream>>>(residual, (const bf16*)delta, n);
-  else
-    return IE_BAD_DTYPE;
-  return launch_status();
+  if (act_dtype == IE_F32) return launch_k(residual_add_kernel<float>, blocks, 256, 0, stream, residual, (const float*)delta, n);
+  if (act_dtype == IE_BF16) return launch_k(residual_add_kernel<bf16>, blocks, 256, 0, stream, residual, (const bf16*)delta, n);
+  return IE_BAD_DTYPE;
 }
 
 // ------------------------------------------------- rotary encoding + cache write
@@ -124,6 +123,8 @@ __global__ void rope_kv_write_kernel(TA* __restrict__ q, const TA* __restrict__ 
                                      const int* __restrict__ slot_mapping, TA* __restrict__ kpool,
                                      TA* __restrict__ vpool, int n_heads, int n_kv_heads, int hd, int page_size,
                                      int write_kv) {
+  pdl_trigger();
+  pdl_wait();
   const int n = blockIdx.x;
   const int half = hd >> 1;
   const int pos = positions[n];
@@ -166,16 +167,14 @@ extern "C" int ie_rope_kv_write(void* q, const void* k, const void* v, int q_str
   const int work = n_heads * hd / 2;
   const int threads = work >= 512 ? 256 : 128;
   if (act_dtype == IE_F32)
-    rope_kv_write_kernel<float><<<n_tokens, threads, 0, stream>>>(
-        (float*)q, (const float*)k, (const float*)v, q_stride, kv_stride, cos_t, sin_t, positions, slot_mapping,
-        (float*)kpool, (float*)vpool, n_heads, n_kv_heads, hd, page_size, write_kv);
-  else if (act_dtype == IE_BF16)
-    rope_kv_write_kernel<bf16><<<n_tokens, threads, 0, stream>>>(
-        (bf16*)q, (const bf16*)k, (const bf16*)v, q_stride, kv_stride, cos_t, sin_t, positions, slot_mapping,
-        (bf16*)kpool, (bf16*)vpool, n_heads, n_kv_heads, hd, page_size, write_kv);
-  else
-    return IE_BAD_DTYPE;
-  return launch_status();
+    return launch_k(rope_kv_write_kernel<float>, n_tokens, threads, 0, stream, (float*)q, (const float*)k,
+                    (const float*)v, q_stride, kv_stride, cos_t, sin_t, positions, slot_mapping, (float*)kpool,
+                    (float*)vpool, n_heads, n_kv_heads, hd, page_size, write_kv);
+  if (act_dtype == IE_BF16)
+    return launch_k(rope_kv_write_kernel<bf16>, n_tokens, threads, 0, stream, (bf16*)q, (const bf16*)k,
+                    (const bf16*)v, q_stride, kv_stride, cos_t, sin_t, positions, slot_mapping, (bf16*)kpool,
+                    (bf16*)vpool, n_heads, n_kv_heads, hd, page_size, write_kv);
+  return IE_BAD_DTYPE;
 }
 
 // ---------------------------------------------------------------- SiLU(gate)*up
@@ -185,6 +184,8 @@ extern "C" int ie_rope_kv_write(void* q, const void* k, const void* v, int q_str
 template <typename TA>
 __global__ void silu_mul_kernel(const TA* __restrict__ in, TA* __restrict__ out, int inter, int in_stride,
                                 size_t total, int interleaved) {
+  pdl_trigger();
+  pdl_wait();
   size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
   const size_t n = idx / inter;
@@ -201,10 +202,8 @@ extern "C" int ie_silu_mul(const void* in, void* out, int n_rows, int inter, int
   if (total == 0) return IE_OK;
   const unsigned blocks = (unsigned)((total + 255) / 256);
   if (act_dtype == IE_F32)
-    silu_mul_kernel<float><<<blocks, 256, 0, stream>>>((const float*)in, (float*)out, inter, in_stride, total, interleaved);
-  else if (act_dtype == IE_BF16)
-    silu_mul_kernel<bf16><<<blocks, 256, 0, stream>>>((const bf16*)in, (bf16*)out, inter, in_stride, total, interleaved);
-  else
-    return IE_BAD_DTYPE;
-  return launch_status();
+    return launch_k(silu_mul_kernel<float>, blocks, 256, 0, stream, (const float*)in, (float*)out, inter, in_stride, total, interleaved);
+  if (act_dtype == IE_BF16)
+    return launch_k(silu_mul_kernel<bf16>, blocks, 256, 0, stream, (const bf16*)in, (bf16*)out, inter, in_stride, total, interleaved);
+  return IE_BAD_DTYPE;
 }

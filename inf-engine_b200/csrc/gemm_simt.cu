@@ -17,6 +17,8 @@ template <typename TA, typename TW, typename TC>
 __global__ void __launch_bounds__(GS_THREADS) gemm_simt_kernel(const TA* __restrict__ A, const TW* __restrict__ W,
                                                                 TC* __restrict__ C, int M, int N, int K, int lda,
                                                                 int ldw, int ldc) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ float As[GS_BK][GS_BM + 4];
   __shared__ float Ws[GS_BK][GS_BN + 4];
   const int m0 = blockIdx.y * GS_BM, n0 = blockIdx.x * GS_BN;
@@ -68,9 +70,8 @@ template <typename TA, typename TW, typename TC>
 static int launch_gemm(const void* A, const void* W, void* C, int M, int N, int K, int lda, int ldw, int ldc,
                        cudaStream_t stream) {
   dim3 grid((N + GS_BN - 1) / GS_BN, (M + GS_BM - 1) / GS_BM);
-  gemm_simt_kernel<TA, TW, TC><<<grid, GS_THREADS, 0, stream>>>((const TA*)A, (const TW*)W, (TC*)C, M, N, K, lda,
-                                                                 ldw, ldc);
-  return launch_status();
+  return launch_k(gemm_simt_kernel<TA, TW, TC>, grid, GS_THREADS, 0, stream, (const TA*)A, (const TW*)W, (TC*)C, M, N,
+                  K, lda, ldw, ldc);
 }
 
 extern "C" int ie_gemm_simt(const void* A, int a_dtype, const void* W, int w_dtype, void* C, int c_dtype, int M,

@@ -59,10 +59,12 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 template <int PRO>
 __device__ __forceinline__ uint4 load_a8(const StreamParams& p, int m, int k, bool valid, float& ssq) {
   uint4 out = make_uint4(0u, 0u, 0u, 0u);
-  if (!valid) return out;
   if (PRO == PRO_PLAIN) {
-    return *reinterpret_cast<const uint4*>((const bf16*)p.A + (size_t)m * p.lda + k);
+    // an invalid lane reads element 0 of the buffer (always there) and discards it: no branch around the load
+    const uint4 v = *reinterpret_cast<const uint4*>((const bf16*)p.A + (valid ? (size_t)m * p.lda + k : 0));
+    return valid ? v : out;
   } else {
+    if (!valid) return out;
     const int row = p.row_index ? p.row_index[m] : m;
     const float* x = (const float*)p.A + (size_t)row * p.lda + k;
     const float4 x0 = *reinterpret_cast<const float4*>(x), x1 = *reinterpret_cast<const float4*>(x + 4);
@@ -94,6 +96,7 @@ template <int MB, int NT, int PRO, int EPI>
 __global__ void __launch_bounds__(GS_THREADS) gemm_stream_kernel(StreamParams p) {
   __shared__ float red[GS_WARPS][MB * NT * 4][32];
   __shared__ float red_ssq[GS_WARPS][MB * 2][8];
+  pdl_trigger();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int n_base = blockIdx.x * (8 * NT);
   const int n_chunks = (p.K + 31) >> 5;
@@ -116,23 +119,61 @@ __global__ void __launch_bounds__(GS_THREADS) gemm_stream_kernel(StreamParams p)
     wrow[nt] = p.W + (size_t)(wvalid[nt] ? n : 0) * p.ldw;
   }
 
-#pragma unroll 4
-  for (int c = c_lo; c < c_hi; ++c) {
+  // Weights do not depend on the kernel ahead: the first PREF chunks of every lane are on
+  // their way before this kernel waits for its activations.  The buffer then rolls: each
+  // chunk that is consumed is replaced by the chunk PREF further on, which keeps PREF
+  // 16-byte loads per weight row in flight per lane.
+  constexpr int PREF = NT == 4 ? 4 : 8;
+  uint4 wbuf[PREF][NT];
+#pragma unroll
+  for (int j = 0; j < PREF; ++j) {
+    const int c = c_lo + j;
     const int k = (c << 5) + t * 8;
-    const bool kvalid = k < p.K;
-    uint4 w[NT];
+    const bool ok = c < c_hi && k < p.K;
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt)
-      w[nt] = (kvalid && wvalid[nt]) ? ldg_stream(wrow[nt] + k) : make_uint4(0u, 0u, 0u, 0u);
+      wbuf[j][nt] = (ok && wvalid[nt]) ? ldg_stream(wrow[nt] + k) : make_uint4(0u, 0u, 0u, 0u);
+  }
+  pdl_wait();
+
+  // Activations of XG chunks are loaded together, without a branch between them, so that
+  // their latencies overlap instead of adding up; then the MMAs of those chunks run and
+  // the weight buffer is refilled for the chunks PREF further on.
+  constexpr int XG = MB == 1 ? PREF : (MB == 2 ? 4 : 2);
+  for (int base = c_lo; base < c_hi; base += PREF) {
 #pragma unroll
-    for (int mb = 0; mb < MB; ++mb) {
-      const int m0 = mb * 16 + g, m1 = m0 + 8;
-      const uint4 x0 = load_a8<PRO>(p, m0, k, kvalid && m0 < p.M, ssq[mb][0]);
-      const uint4 x1 = load_a8<PRO>(p, m1, k, kvalid && m1 < p.M, ssq[mb][1]);
+    for (int j0 = 0; j0 < PREF; j0 += XG) {
+      uint4 xa[XG][MB][2];
 #pragma unroll
-      for (int nt = 0; nt < NT; ++nt) {
-        mma16816(acc[mb][nt], x0.x, x1.x, x0.y, x1.y, w[nt].x, w[nt].y);
-        mma16816(acc[mb][nt], x0.z, x1.z, x0.w, x1.w, w[nt].z, w[nt].w);
+      for (int jj = 0; jj < XG; ++jj) {
+        const int c = base + j0 + jj;
+        const int k = (c << 5) + t * 8;
+        const bool kvalid = c < c_hi && k < p.K;
+#pragma unroll
+        for (int mb = 0; mb < MB; ++mb) {
+          const int m0 = mb * 16 + g, m1 = m0 + 8;
+          xa[jj][mb][0] = load_a8<PRO>(p, m0, k, kvalid && m0 < p.M, ssq[mb][0]);
+          xa[jj][mb][1] = load_a8<PRO>(p, m1, k, kvalid && m1 < p.M, ssq[mb][1]);
+        }
+      }
+#pragma unroll
+      for (int jj = 0; jj < XG; ++jj) {
+        const int j = j0 + jj;
+#pragma unroll
+        for (int mb = 0; mb < MB; ++mb) {
+          const uint4 x0 = xa[jj][mb][0], x1 = xa[jj][mb][1];
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) {
+            mma16816(acc[mb][nt], x0.x, x1.x, x0.y, x1.y, wbuf[j][nt].x, wbuf[j][nt].y);
+            mma16816(acc[mb][nt], x0.z, x1.z, x0.w, x1.w, wbuf[j][nt].z, wbuf[j][nt].w);
+          }
+        }
+        const int c2 = base + j + PREF;
+        const int k2 = (c2 << 5) + t * 8;
+        const bool ok = c2 < c_hi && k2 < p.K;
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+          wbuf[j][nt] = (ok && wvalid[nt]) ? ldg_stream(wrow[nt] + k2) : make_uint4(0u, 0u, 0u, 0u);
       }
     }
   }
@@ -202,8 +243,7 @@ __global__ void __launch_bounds__(GS_THREADS) gemm_stream_kernel(StreamParams p)
 template <int MB, int NT, int PRO, int EPI>
 int launch(const StreamParams& p, cudaStream_t stream) {
   const int grid = (p.N + 8 * NT - 1) / (8 * NT);
-  gemm_stream_kernel<MB, NT, PRO, EPI><<<grid, GS_THREADS, 0, stream>>>(p);
-  return launch_status();
+  return launch_k(gemm_stream_kernel<MB, NT, PRO, EPI>, grid, GS_THREADS, 0, stream, p);
 }
 
 template <int PRO, int EPI>

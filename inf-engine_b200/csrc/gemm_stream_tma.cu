@@ -1,0 +1,390 @@
+// Persistent weight-streaming product for decode steps on sm_100a:
+// C[M,N] = A[M,K] W[N,K]^T, M <= 16, bfloat16 weights read once from HBM by the
+// bulk-copy engine (cp.async.bulk, completion on mbarriers) into a ring of shared
+// memory stages, one block per SM that walks units of 8 weight rows.
+//
+// Why this shape: at M <= 16 the product is a read of W.  A block that owns little
+// data spends its life on latency (first bytes from HBM, activations from L2,
+// reduction, store); here a producer thread keeps the ring full across unit
+// boundaries, so HBM requests never stop while consumer warps multiply, reduce and
+// store.  Launched with programmatic dependent launch, the producer starts filling
+// the ring with this kernel's weights while the kernel ahead is still running; only
+// the consumers wait for its output.
+//
+//   producer  warp 4, one lane: for every (unit, k-stage) wait for the stage to be
+//             free, arm its mbarrier with the byte count, issue one bulk copy per
+//             weight row (rows are contiguous in global memory)
+//   consumers warps 0-7: stage the activations once per block in shared memory
+//             (bfloat16; with the RMSNorm prologue x*gain and 1/rms are computed here
+//             in float32, engine/layers.py:24-25), then per stage each warp takes a
+//             eighth of k, builds MMA fragments with 16-byte shared loads and runs
+//             mma.sync m16n8k16; at the end of a unit the eight partial sums are added
+//             in warp order and the epilogue of gemm_stream.cu is applied.
+//
+// Every wait on an mbarrier is bounded; on a timeout the block records an error
+// word that ie_gemm_stream_tma_error() reads, stops issuing copies and leaves.
+#include "common.cuh"
+
+namespace {
+
+enum { PRO_PLAIN = 0, PRO_NORM = 1 };
+enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_RESIDUAL = 2, EPI_SILU_MUL = 3 };
+
+constexpr int CONSUMER_WARPS = 8;
+constexpr int CONSUMER_THREADS = CONSUMER_WARPS * 32;
+constexpr int THREADS = CONSUMER_THREADS + 32;
+constexpr int ROW_PAD = 64;          // bytes added to a row's pitch: keeps 16-byte fragment loads off shared banks
+constexpr int MAX_STAGES = 12;
+constexpr unsigned SPIN_LIMIT = 1u << 20;   // polls of a wait that normally lasts microseconds
+
+__device__ int g_stream_error = 0;
+
+struct TmaParams {
+  const void* A;          // PLAIN: bf16 [M, lda];  NORM: float32 residual rows [*, lda]
+  const bf16* W;          // [N, ldw]
+  void* C;
+  const void* gain;
+  const int* row_index;
+  int M, N, K, lda, ldw, ldc;
+  int gain_is_f32;
+  float eps;
+  int ks;                 // k elements per stage (multiple of 128)
+  int n_stages;
+  int x_rows;             // 8 or 16 activation rows kept in shared memory
+};
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// false when the phase did not complete within SPIN_LIMIT polls
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  for (unsigned i = 0; i < SPIN_LIMIT; ++i) {
+    uint32_t ok;
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void bulk_copy(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_THREADS) : "memory"); }
+__device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// NT: 8*NT weight rows per unit (NT n-tiles of the MMA per warp)
+template <int NT, int PRO, int EPI>
+__global__ void __launch_bounds__(THREADS, 1) gemm_stream_tma_kernel(TmaParams p) {
+  constexpr int UNIT_ROWS = 8 * NT;
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ __align__(8) unsigned long long bars[2 * MAX_STAGES];   // full[], empty[]
+  __shared__ float red[2][CONSUMER_WARPS][4 * NT][32];
+  __shared__ float inv_rms[16];
+  __shared__ volatile int failed;
+
+  pdl_trigger();
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n_units = (p.N + UNIT_ROWS - 1) / UNIT_ROWS;
+  const int k_stages = p.K / p.ks;
+  const uint32_t w_pitch = (uint32_t)p.ks * 2 + ROW_PAD;
+  const uint32_t stage_bytes = UNIT_ROWS * w_pitch;
+  const uint32_t x_pitch = (uint32_t)p.K * 2 + ROW_PAD;
+  const uint32_t ring = smem_addr(smem);
+  const uint32_t xs = ring + p.n_stages * stage_bytes;
+  const uint32_t full0 = smem_addr(&bars[0]), empty0 = smem_addr(&bars[MAX_STAGES]);
+
+  if (tid == 0) {
+    failed = 0;
+    for (int s = 0; s < p.n_stages; ++s) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, CONSUMER_WARPS);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  if (warp == CONSUMER_WARPS) {
+    // ------------------------------------------------------------- producer
+    // lane 0 waits for the stage and arms its barrier; then lane r issues the copy of weight row r,
+    // so that the copies of a stage are issued side by side rather than one after the other
+    int s = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    const uint32_t row_bytes = (uint32_t)p.ks * 2;
+    for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
+      const int n0 = u * UNIT_ROWS;
+      const int rows = min(UNIT_ROWS, p.N - n0);
+      const bf16* src = p.W + (size_t)(n0 + (lane < rows ? lane : 0)) * p.ldw;
+      for (int ksi = 0; ksi < k_stages; ++ksi) {
+        const uint32_t bar = full0 + 8 * s;
+        if (lane == 0) {
+          ok = mbar_wait(empty0 + 8 * s, phase ^ 1);
+          if (ok) mbar_expect_tx(bar, row_bytes * rows);
+        }
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        if (!ok) break;
+        if (lane < rows) bulk_copy(ring + s * stage_bytes + lane * w_pitch, src + (size_t)ksi * p.ks, row_bytes, bar);
+        if (++s == p.n_stages) { s = 0; phase ^= 1; }
+      }
+    }
+    if (!ok && lane == 0) {
+      atomicExch(&g_stream_error, 1);
+      failed = 1;
+      // copies already issued land in this block's shared memory: stay a bounded while before leaving
+      for (int i = 0; i < 4096; ++i) __nanosleep(64);
+    }
+    pdl_wait();
+    return;
+  }
+
+  // --------------------------------------------------------------- consumers
+  pdl_wait();
+  const int g = lane >> 2, t = lane & 3;
+  // activations -> shared memory, once per block
+  {
+    unsigned char* xsm = smem + p.n_stages * stage_bytes;
+    for (int m = warp; m < p.x_rows; m += CONSUMER_WARPS) {
+      bf16* dst = reinterpret_cast<bf16*>(xsm + (size_t)m * x_pitch);
+      if (m >= p.M) {
+        for (int k = lane * 8; k < p.K; k += 256) *reinterpret_cast<uint4*>(dst + k) = make_uint4(0u, 0u, 0u, 0u);
+        continue;
+      }
+      if (PRO == PRO_PLAIN) {
+        const bf16* src = (const bf16*)p.A + (size_t)m * p.lda;
+        for (int k = lane * 8; k < p.K; k += 256)
+          *reinterpret_cast<uint4*>(dst + k) = *reinterpret_cast<const uint4*>(src + k);
+      } else {
+        const int row = p.row_index ? p.row_index[m] : m;
+        const float* src = (const float*)p.A + (size_t)row * p.lda;
+        float ssq = 0.f;
+        for (int k = lane * 8; k < p.K; k += 256) {
+          const float4 x0 = *reinterpret_cast<const float4*>(src + k), x1 = *reinterpret_cast<const float4*>(src + k + 4);
+          float gv[8];
+          if (p.gain_is_f32) {
+            const float4 g0 = *reinterpret_cast<const float4*>((const float*)p.gain + k);
+            const float4 g1 = *reinterpret_cast<const float4*>((const float*)p.gain + k + 4);
+            gv[0] = g0.x; gv[1] = g0.y; gv[2] = g0.z; gv[3] = g0.w; gv[4] = g1.x; gv[5] = g1.y; gv[6] = g1.z; gv[7] = g1.w;
+          } else {
+            const uint4 gr = *reinterpret_cast<const uint4*>((const bf16*)p.gain + k);
+            const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&gr);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float2 f = __bfloat1622float2(gp[i]);
+              gv[2 * i] = f.x;
+              gv[2 * i + 1] = f.y;
+            }
+          }
+          ssq += x0.x * x0.x + x0.y * x0.y + x0.z * x0.z + x0.w * x0.w + x1.x * x1.x + x1.y * x1.y + x1.z * x1.z + x1.w * x1.w;
+          uint4 o;
+          o.x = pack2(x0.x * gv[0], x0.y * gv[1]);
+          o.y = pack2(x0.z * gv[2], x0.w * gv[3]);
+          o.z = pack2(x1.x * gv[4], x1.y * gv[5]);
+          o.w = pack2(x1.z * gv[6], x1.w * gv[7]);
+          *reinterpret_cast<uint4*>(dst + k) = o;
+        }
+        ssq = warp_sum(ssq);
+        if (lane == 0) inv_rms[m] = 1.f / sqrtf(ssq / (float)p.K + p.eps);
+      }
+    }
+  }
+  consumer_sync();
+
+  const int kw = warp * (p.ks / CONSUMER_WARPS);        // this warp's k offset inside a stage
+  const int chunks = p.ks / (CONSUMER_WARPS * 32);      // 32-wide chunks per warp per stage
+  const bool two = p.x_rows > 8;
+  int s = 0;
+  uint32_t phase = 0;
+  int parity = 0;
+  bool dead = false;   // after a timed-out wait a warp stops waiting and computing but still meets every barrier
+  for (int u = blockIdx.x; u < n_units; u += gridDim.x) {
+    // two accumulators per n-tile: the two MMAs of a chunk do not wait for each other
+    float acc[NT][2][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[nt][0][e] = acc[nt][1][e] = 0.f;
+    for (int ksi = 0; ksi < k_stages; ++ksi) {
+      if (!dead && (failed || !mbar_wait(full0 + 8 * s, phase))) {
+        dead = true;
+        if (lane == 0) { atomicExch(&g_stream_error, 2); failed = 1; }
+      }
+      if (dead) continue;
+      const uint32_t wbase = ring + s * stage_bytes + g * w_pitch + (kw + t * 8) * 2;
+      const uint32_t xbase = xs + g * x_pitch + (ksi * p.ks + kw + t * 8) * 2;
+#pragma unroll 4
+      for (int c = 0; c < chunks; ++c) {
+        const uint4 x0 = lds128(xbase + c * 64);
+        uint4 x1 = make_uint4(0u, 0u, 0u, 0u);
+        if (two) x1 = lds128(xbase + 8 * x_pitch + c * 64);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          const uint4 w = lds128(wbase + nt * 8 * w_pitch + c * 64);
+          mma16816(acc[nt][0], x0.x, x1.x, x0.y, x1.y, w.x, w.y);
+          mma16816(acc[nt][1], x0.z, x1.z, x0.w, x1.w, w.z, w.w);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(empty0 + 8 * s);
+      if (++s == p.n_stages) { s = 0; phase ^= 1; }
+    }
+    // partial sums of the four warps, added in warp order
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) red[parity][warp][nt * 4 + e][lane] = acc[nt][0][e] + acc[nt][1][e];
+    consumer_sync();
+    if (tid < 64 * NT && !failed) {
+      const int ln = tid & 31, h = (tid >> 5) & 1, nt = tid >> 6;
+      const int gg = ln >> 2, tt = ln & 3;
+      const int m = gg + h * 8;
+      const int n = u * UNIT_ROWS + nt * 8 + tt * 2;
+      if (m < p.M && n < p.N) {
+        float v0 = 0.f, v1 = 0.f;
+#pragma unroll
+        for (int w4 = 0; w4 < CONSUMER_WARPS; ++w4) {
+          v0 += red[parity][w4][nt * 4 + h * 2][ln];
+          v1 += red[parity][w4][nt * 4 + h * 2 + 1][ln];
+        }
+        if (PRO == PRO_NORM) {
+          v0 *= inv_rms[m];
+          v1 *= inv_rms[m];
+        }
+        const bool has1 = n + 1 < p.N;
+        if (EPI == EPI_BF16) {
+          bf16* c = (bf16*)p.C + (size_t)m * p.ldc + n;
+          if (has1 && ((((uintptr_t)c) & 3) == 0)) *reinterpret_cast<uint32_t*>(c) = pack2(v0, v1);
+          else { c[0] = __float2bfloat16_rn(v0); if (has1) c[1] = __float2bfloat16_rn(v1); }
+        } else if (EPI == EPI_F32) {
+          float* c = (float*)p.C + (size_t)m * p.ldc + n;
+          c[0] = v0;
+          if (has1) c[1] = v1;
+        } else if (EPI == EPI_RESIDUAL) {
+          float* c = (float*)p.C + (size_t)m * p.ldc + n;
+          c[0] += v0;
+          if (has1) c[1] += v1;
+        } else {
+          const float sg = 1.f / (1.f + expf(-v0));
+          ((bf16*)p.C)[(size_t)m * p.ldc + (n >> 1)] = __float2bfloat16_rn((v0 * sg) * v1);
+        }
+      }
+    }
+    parity ^= 1;
+  }
+}
+
+template <int NT, int PRO, int EPI>
+int launch_one(const TmaParams& p, int n_sms, size_t smem, cudaStream_t stream) {
+  static bool attr = false;
+  if (!attr) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_stream_tma_kernel<NT, PRO, EPI>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, 204 * 1024);
+    if (e != cudaSuccess) return (int)e;
+    attr = true;
+  }
+  const int n_units = (p.N + 8 * NT - 1) / (8 * NT);
+  const int grid = n_units < n_sms ? n_units : n_sms;
+  return launch_k(gemm_stream_tma_kernel<NT, PRO, EPI>, grid, THREADS, smem, stream, p);
+}
+
+template <int PRO, int EPI>
+int launch_tma(const TmaParams& p, int nt, int n_sms, size_t smem, cudaStream_t stream) {
+  if (nt == 2) return launch_one<2, PRO, EPI>(p, n_sms, smem, stream);
+  return launch_one<1, PRO, EPI>(p, n_sms, smem, stream);
+}
+
+}  // namespace
+
+// 1 if the kernel takes this product (M <= 16, K a multiple of 256, activations fit in shared memory)
+extern "C" int ie_gemm_stream_tma_supports(int M, int N, int K) {
+  if (M <= 0 || M > 16 || N <= 0 || K <= 0 || (K % 256)) return 0;
+  const size_t x_bytes = (size_t)(M > 8 ? 16 : 8) * ((size_t)K * 2 + ROW_PAD);
+  return x_bytes <= 132 * 1024 ? 1 : 0;
+}
+
+// Reads and clears the error word that a timed-out mbarrier wait leaves (0: none).
+extern "C" int ie_gemm_stream_tma_error() {
+  int v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, g_stream_error, sizeof(int)) != cudaSuccess) return -1;
+  if (v) cudaMemcpyToSymbol(g_stream_error, &zero, sizeof(int));
+  return v;
+}
+
+extern "C" int ie_gemm_stream_tma(const void* A, const void* W, void* C, const void* gain, int gain_dtype,
+                                  const int* row_index, int M, int N, int K, int lda, int ldw, int ldc, float eps,
+                                  int pro, int epi, int n_sms, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return IE_OK;
+  if (!ie_gemm_stream_tma_supports(M, N, K) || (lda & 7) || (ldw & 7)) return IE_BAD_SIZE;
+  if (((uintptr_t)A | (uintptr_t)W) & 15) return IE_BAD_ALIGN;
+  if (epi == EPI_SILU_MUL && (N & 1)) return IE_BAD_SIZE;
+  if (n_sms <= 0) return IE_BAD_SIZE;
+  TmaParams p;
+  p.A = A; p.W = (const bf16*)W; p.C = C; p.gain = gain; p.row_index = row_index;
+  p.M = M; p.N = N; p.K = K; p.lda = lda; p.ldw = ldw; p.ldc = ldc;
+  p.gain_is_f32 = gain_dtype == IE_F32; p.eps = eps;
+  // units of 16 rows when that still gives every SM several units; a stage is 8 KB..16 KB per 8 rows
+  const int nt = (N >= 16 * 4 * n_sms) ? 2 : 1;
+  const int unit_rows = 8 * nt;
+  p.x_rows = M > 8 ? 16 : 8;
+  const size_t x_bytes = (size_t)p.x_rows * ((size_t)K * 2 + ROW_PAD);
+  const int ks_try[4] = {2048, 1024, 512, 256};
+  // A product that keeps an SM busy for long wants a deep ring (HBM answers after about 2 us, so about
+  // 100 KB per SM must be on its way).  A short one gains more from sharing the SM with the kernel behind
+  // it in the chain, which then prefetches its weights early: that needs dynamic + static shared memory
+  // of each to stay under 113 KB.
+  const bool deep = (size_t)N * K * 2 / (size_t)n_sms > 192 * 1024;
+  size_t budget = (size_t)((deep ? 212 : 113) - (nt == 2 ? 17 : 9)) * 1024;
+  int n_stages = 0;
+  size_t stage_bytes = 0;
+  for (int pass = 0; pass < 2 && n_stages < 3; ++pass) {
+    for (int i = 0; i < 4 && n_stages < 3; ++i) {
+      const int ks = ks_try[i];
+      if (K % ks || ks % (CONSUMER_WARPS * 32)) continue;
+      stage_bytes = (size_t)unit_rows * ((size_t)ks * 2 + ROW_PAD);
+      if (x_bytes + 3 * stage_bytes > budget) continue;
+      p.ks = ks;
+      n_stages = (int)((budget - x_bytes) / stage_bytes);
+    }
+    budget = (size_t)(212 - (nt == 2 ? 17 : 9)) * 1024;
+  }
+  if (n_stages < 3) return IE_BAD_SIZE;
+  if (n_stages > MAX_STAGES) n_stages = MAX_STAGES;
+  p.n_stages = n_stages;
+  const size_t smem = x_bytes + (size_t)n_stages * stage_bytes;
+  if (pro == PRO_NORM) {
+    if (!gain || ((uintptr_t)gain & 15)) return IE_BAD_ALIGN;
+    if (epi == EPI_BF16) return launch_tma<PRO_NORM, EPI_BF16>(p, nt, n_sms, smem, stream);
+    if (epi == EPI_F32) return launch_tma<PRO_NORM, EPI_F32>(p, nt, n_sms, smem, stream);
+    if (epi == EPI_SILU_MUL) return launch_tma<PRO_NORM, EPI_SILU_MUL>(p, nt, n_sms, smem, stream);
+    return IE_BAD_DTYPE;
+  }
+  if (pro == PRO_PLAIN) {
+    if (epi == EPI_BF16) return launch_tma<PRO_PLAIN, EPI_BF16>(p, nt, n_sms, smem, stream);
+    if (epi == EPI_F32) return launch_tma<PRO_PLAIN, EPI_F32>(p, nt, n_sms, smem, stream);
+    if (epi == EPI_RESIDUAL) return launch_tma<PRO_PLAIN, EPI_RESIDUAL>(p, nt, n_sms, smem, stream);
+    if (epi == EPI_SILU_MUL) return launch_tma<PRO_PLAIN, EPI_SILU_MUL>(p, nt, n_sms, smem, stream);
+    return IE_BAD_DTYPE;
+  }
+  return IE_BAD_DTYPE;
+}

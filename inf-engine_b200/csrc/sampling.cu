@@ -60,6 +60,8 @@ __global__ void __launch_bounds__(SM_THREADS) argmax_kernel(const float* __restr
                                                             int vocab, size_t row_stride) {
   __shared__ float sv[32];
   __shared__ int si[32];
+  pdl_trigger();
+  pdl_wait();
   const float* x = logits + (size_t)blockIdx.x * row_stride;
   float best = -INFINITY;
   int best_i = 0x7fffffff;
@@ -94,8 +96,7 @@ extern "C" int ie_argmax(const float* logits, int* out, int n_rows, int vocab, l
                          cudaStream_t stream) {
   if (n_rows <= 0) return IE_OK;
   if (vocab <= 0) return IE_BAD_SIZE;
-  argmax_kernel<<<n_rows, SM_THREADS, 0, stream>>>(logits, out, vocab, (size_t)row_stride);
-  return launch_status();
+  return launch_k(argmax_kernel, n_rows, SM_THREADS, 0, stream, logits, out, vocab, (size_t)row_stride);
 }
 
 // --------------------------------------------------------- repetition penalty
@@ -105,6 +106,8 @@ extern "C" int ie_argmax(const float* logits, int* out, int n_rows, int vocab, l
 __global__ void repetition_penalty_kernel(float* __restrict__ logits, const int* __restrict__ context,
                                           const float* __restrict__ penalty, int vocab, size_t row_stride,
                                           int ctx_len) {
+  pdl_trigger();
+  pdl_wait();
   const int row = blockIdx.x;
   const float pen = penalty[row];
   if (pen == 1.0f) return;
@@ -125,9 +128,8 @@ __global__ void repetition_penalty_kernel(float* __restrict__ logits, const int*
 extern "C" int ie_repetition_penalty(float* logits, const int* context, const float* penalty, int n_rows,
                                      int vocab, long long row_stride, int ctx_len, cudaStream_t stream) {
   if (n_rows <= 0 || ctx_len <= 0) return IE_OK;
-  repetition_penalty_kernel<<<n_rows, 256, 0, stream>>>(logits, context, penalty, vocab, (size_t)row_stride,
-                                                         ctx_len);
-  return launch_status();
+  return launch_k(repetition_penalty_kernel, n_rows, 256, 0, stream, logits, context, penalty, vocab,
+                  (size_t)row_stride, ctx_len);
 }
 
 // --------------------------------------------------------------------- sample
@@ -137,6 +139,8 @@ __global__ void __launch_bounds__(SM_THREADS) sample_kernel(const float* __restr
   __shared__ float red[33];
   __shared__ int redi[33];
   __shared__ float chunk_sum[SM_THREADS];
+  pdl_trigger();
+  pdl_wait();
   const float* x = logits + (size_t)blockIdx.x * row_stride;
   const SampleRow r = rows[blockIdx.x];
   const int tid = threadIdx.x;
@@ -256,6 +260,6 @@ extern "C" int ie_sample(const float* logits, const void* rows, int* out, int n_
                          long long row_stride, cudaStream_t stream) {
   if (n_rows <= 0) return IE_OK;
   if (vocab <= 0) return IE_BAD_SIZE;
-  sample_kernel<<<n_rows, SM_THREADS, 0, stream>>>(logits, (const SampleRow*)rows, out, vocab, (size_t)row_stride);
-  return launch_status();
+  return launch_k(sample_kernel, n_rows, SM_THREADS, 0, stream, logits, (const SampleRow*)rows, out, vocab,
+                  (size_t)row_stride);
 }

@@ -202,6 +202,7 @@ def attention_mma_library(head_dim: int):
         lib.ie_attention_decode.restype = c_int
         lib.ie_attention_decode_scratch_floats.argtypes = [I, I, I]
         lib.ie_attention_decode_scratch_floats.restype = c_longlong
+        lib.ie_attention_decode_ticket_words.restype = c_longlong
         _mma[head_dim] = lib
     return lib
 
@@ -221,12 +222,20 @@ def attention_decode_scratch_floats(n_tokens, n_heads, n_splits, head_dim) -> in
     return int(attention_mma_library(head_dim).ie_attention_decode_scratch_floats(n_tokens, n_heads, n_splits))
 
 
+def attention_decode_ticket_words(head_dim) -> int:
+    """How many words at the start of the decode scratch hold tickets; they must be zero before the
+    first launch on a piece of scratch (every launch leaves them zero)."""
+    return int(attention_mma_library(head_dim).ie_attention_decode_ticket_words())
+
+
 def attention_decode_mma(q, out, kpool, vpool, block_table, q_start, ctx_before, scratch, n_requests, n_tokens,
                          n_heads, n_kv_heads, head_dim, page_size, window, scale, n_splits, split_keys) -> None:
     """Split-key attention for steps where every request brings at most 16 (token, head-in-group) rows.
 
-    ``scratch`` is float32 device memory of ``attention_decode_scratch_floats`` elements that the kernel
-    fully overwrites (partial outputs, maxima and sums of every split) before its merge reads it."""
+    ``scratch`` is float32 device memory of ``attention_decode_scratch_floats`` elements: partial
+    tickets in its first ``attention_decode_ticket_words`` words, which must be zero when the first
+    launch starts and are zero again when a launch ends, then partial outputs, maxima and sums of
+    every split, which are written before they are read.  At most 64 splits."""
     assert q.dtype is torch.bfloat16 and scratch.dtype is torch.float32
     lib = attention_mma_library(head_dim)
     _check(lib.ie_attention_decode(_ptr(q), _ptr(out), _ptr(kpool), _ptr(vpool), _ptr(block_table), _ptr(q_start),
@@ -234,8 +243,6 @@ def attention_decode_mma(q, out, kpool, vpool, block_table, q_start, ctx_before,
                                    block_table.stride(0), n_requests, n_tokens, n_heads, n_kv_heads, head_dim,
                                    page_size, int(window or 0), float(scale), n_splits, split_keys, _stream()),
            "attention_decode_mma")
-    global LAUNCHES
-    LAUNCHES += 1        # the launcher runs two kernels: the split pass and its merge
 
 
 # ----------------------------------------------- weight-streaming product for few rows
@@ -248,12 +255,32 @@ _stream_lib = None
 def stream_library():
     global _stream_lib
     if _stream_lib is None:
-        lib = load_library("stream", ["gemm_stream.cu"])
+        lib = load_library("stream", ["gemm_stream.cu", "gemm_stream_tma.cu"])
         P, I, F = c_void_p, c_int, c_float
         lib.ie_gemm_stream.argtypes = [P, P, P, P, I, P, I, I, I, I, I, I, F, I, I, I, P]
         lib.ie_gemm_stream.restype = c_int
+        lib.ie_gemm_stream_tma.argtypes = [P, P, P, P, I, P, I, I, I, I, I, I, F, I, I, I, P]
+        lib.ie_gemm_stream_tma.restype = c_int
+        lib.ie_gemm_stream_tma_supports.argtypes = [I, I, I]
+        lib.ie_gemm_stream_tma_supports.restype = c_int
+        lib.ie_gemm_stream_tma_error.restype = c_int
         _stream_lib = lib
     return _stream_lib
+
+
+_n_sms: dict[int, int] = {}
+
+
+def sm_count() -> int:
+    dev = torch.cuda.current_device()
+    if dev not in _n_sms:
+        _n_sms[dev] = torch.cuda.get_device_properties(dev).multi_processor_count
+    return _n_sms[dev]
+
+
+def stream_error() -> int:
+    """Reads and clears the error word of the bulk-copy streaming kernel (0: no wait ever timed out)."""
+    return int(stream_library().ie_gemm_stream_tma_error())
 
 
 def gemm_stream(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, m: int, epi: str = "bf16",
@@ -271,11 +298,20 @@ def gemm_stream(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, m: int, epi: 
         assert a.dtype is torch.bfloat16
     else:
         assert a.dtype is torch.float32 and gain.shape == (k,)
+    lib = stream_library()
+    if nt is None and lib.ie_gemm_stream_tma_supports(m, n, k):
+        # persistent bulk-copy kernel: one block per SM, weights through a ring of shared memory
+        _check(lib.ie_gemm_stream_tma(_ptr(a), _ptr(w), _ptr(c), _ptr(gain),
+                                      dtype_code(gain.dtype) if gain is not None else 0, _ptr(row_index), m, n, k,
+                                      a.stride(0), w.stride(0), c.stride(0), float(eps),
+                                      0 if gain is None else 1, _EPI[epi], sm_count(), _stream()),
+               f"gemm_stream_tma(m={m}, n={n}, k={k}, {epi})")
+        return
     if nt is None:
         nt = 4 if n >= 16384 else (2 if n >= 8192 else 1)
         if m > 32:
             nt = min(nt, 2)
-    _check(stream_library().ie_gemm_stream(_ptr(a), _ptr(w), _ptr(c), _ptr(gain),
+    _check(lib.ie_gemm_stream(_ptr(a), _ptr(w), _ptr(c), _ptr(gain),
                                            dtype_code(gain.dtype) if gain is not None else 0, _ptr(row_index), m, n, k,
                                            a.stride(0), w.stride(0), c.stride(0), float(eps),
                                            0 if gain is None else 1, _EPI[epi], nt, _stream()),

@@ -120,7 +120,7 @@ class PagedAttention:
             if ctx.max_q_len * group <= 16:
                 n_splits, split_keys = decode_splits(ctx.keys_cap, ctx.n_requests * s.n_kv_heads)
                 n = kernels.attention_decode_scratch_floats(ctx.n_tokens, s.n_heads, n_splits, s.head_dim)
-                scratch = self.rt.ws.take("attn_scratch", (n,), torch.float32)
+                scratch = self.rt.ws.take("attn_scratch", (n,), torch.float32)   # zero when made; tickets stay zero
                 kernels.attention_decode_mma(q, out, cache.k, cache.v, kvctx.block_table, ctx.q_start,
                                              ctx.ctx_before, scratch, ctx.n_requests, ctx.n_tokens, s.n_heads,
                                              s.n_kv_heads, s.head_dim, ctx.page_size, s.window, self.scale,
@@ -137,14 +137,15 @@ class PagedAttention:
                                   ctx.page_size, s.window, self.scale)
 
 
-def decode_splits(keys_cap: int, n_streams: int, target_warps: int = 2048) -> tuple[int, int]:
+def decode_splits(keys_cap: int, n_streams: int, resident_warps: int = 888) -> tuple[int, int]:
     """How the decode kernel cuts the keys: (number of splits, keys per split).
 
-    One warp works on one split of one (request, kv head); enough warps must be in
-    flight to keep HBM busy, so few requests mean short splits.  Splits are multiples
-    of 32 keys and cover ``keys_cap`` keys, the most any request of the step can hold.
+    One warp works on one split of one (request, kv head) and keeps four tiles of 32 keys in
+    flight, so a split is at least 128 keys; with many streams the splits grow so that the
+    warps of a step (counted at half of ``keys_cap``, the usual fill) fit the GPU at once.
+    ``keys_cap`` is the most keys any request of the step can hold.  At most 64 splits.
     """
     keys_cap = max(int(keys_cap), 1)
-    per = -(-keys_cap * max(n_streams, 1) // target_warps)
-    split_keys = min(1024, max(32, -(-per // 32) * 32))
+    per = -(-keys_cap * max(n_streams, 1) // (2 * resident_warps))
+    split_keys = max(128, min(512, -(-per // 128) * 128), -(-keys_cap // (64 * 128)) * 128)   # at most 64 splits
     return -(-keys_cap // split_keys), split_keys

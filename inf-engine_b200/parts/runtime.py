@@ -34,7 +34,7 @@ class Workspace:
             # round up so that slowly growing steps do not reallocate every time
             cap = max(nbytes, 256)
             cap = 1 << (cap - 1).bit_length() if cap < (1 << 20) else -(-cap // (1 << 20)) * (1 << 20)
-            buf = torch.empty(cap, dtype=torch.uint8, device=self.device)
+            buf = torch.zeros(cap, dtype=torch.uint8, device=self.device)   # some kernels keep counters that start at zero
             self._buffers[name] = buf
         return buf[:nbytes].view(dtype).view(shape)
 

@@ -172,6 +172,52 @@ def test_gemm_stream_plain_and_fused(M, N, K):
         assert float((out.float().cpu() - want).abs().max()) <= 1e-2 * max(1.0, float(want.abs().max()))
 
 
+@pytest.mark.parametrize("M", [1, 5, 8, 9, 16])
+@pytest.mark.parametrize("N,K", [(389, 256), (1000, 768), (2050, 2048), (520, 8192)])
+def test_gemm_stream_bulk_copy_kernel(M, N, K):
+    """The persistent kernel (weights by cp.async.bulk through a shared-memory ring), default for K % 256 == 0."""
+    from inf_engine_b200 import kernels
+    lib = kernels.stream_library()
+    if not lib.ie_gemm_stream_tma_supports(M, N, K):
+        pytest.skip("activations of this shape do not fit the kernel's shared memory")
+    torch.manual_seed(M * 7 + N)
+    bf = torch.bfloat16
+    a = torch.randn(M, K, device=DEV).to(bf)
+    w = (torch.randn(N, K, device=DEV) * 0.05).to(bf)
+    ref = a.float().cpu() @ w.float().cpu().T
+    scale = float(ref.abs().max())
+    out32 = torch.full((M, N), float("nan"), device=DEV)
+    k().gemm_stream(a, w, out32, M, "f32")
+    assert float((out32.cpu() - ref).abs().max()) <= 2e-4 * scale + 1e-5
+    old = torch.empty(M, N, device=DEV)
+    k().gemm_stream(a, w, old, M, "f32", nt=1)                      # the register-streaming kernel agrees
+    assert float((out32 - old).abs().max()) <= 2e-4 * scale + 1e-5
+    out = torch.full((M, N), float("nan"), device=DEV, dtype=bf)
+    k().gemm_stream(a, w, out, M, "bf16")
+    assert float((out.float().cpu() - ref).abs().max()) <= 1e-2 * scale
+    res = torch.randn(M, N, device=DEV)
+    want = res.cpu() + ref
+    k().gemm_stream(a, w, res, M, "residual")
+    assert float((res.cpu() - want).abs().max()) <= 2e-4 * scale + 1e-5
+    if K <= 2048:
+        x = torch.randn(M + 3, K, device=DEV) * 2
+        rows = torch.randperm(M + 3)[:M].to(torch.int32).to(DEV)
+        for gain_dtype in (bf, torch.float32):
+            gain = (1 + 0.1 * torch.randn(K, device=DEV)).to(gain_dtype)
+            normed = plain_llama.rms_norm(x.cpu()[rows.long().cpu()], gain.float().cpu(), 1e-5)
+            want = normed @ w.float().cpu().T
+            got = torch.empty(M, N, device=DEV)
+            k().gemm_stream(x, w, got, M, "f32", gain=gain, eps=1e-5, row_index=rows)
+            assert float((got.cpu() - want).abs().max()) <= 1e-2 * float(want.abs().max())
+    if N % 2 == 0:
+        h = torch.empty(M, N // 2, device=DEV, dtype=bf)
+        k().gemm_stream(a, w, h, M, "silu_mul")
+        want = plain_llama.silu(ref[:, 0::2]) * ref[:, 1::2]
+        assert float((h.float().cpu() - want).abs().max()) <= 1e-2 * max(1.0, float(want.abs().max()))
+    torch.cuda.synchronize()
+    assert kernels.stream_error() == 0
+
+
 def test_gemm_stream_refuses_what_it_cannot_take():
     from inf_engine_b200.kernels import KernelError
     bf = torch.bfloat16
@@ -359,7 +405,8 @@ def test_attention_decode_split_keys(case):
     cap = max(a + b for a, b in zip(q_lens, ctx_before)) + 77      # the cap may exceed every request's length
     n_splits = -(-cap // split_keys)
     n = k().attention_decode_scratch_floats(c["N"], H, n_splits, hd)
-    scratch = torch.full((n,), float("nan"), device=DEV)            # whatever an earlier call left must not matter
+    scratch = torch.full((n,), float("nan"), device=DEV)            # whatever an earlier call left must not matter,
+    scratch[:k().attention_decode_ticket_words(hd)] = 0              # except the tickets, which start at zero
     out = torch.full((c["N"], H * hd), float("nan"), device=DEV, dtype=act)
     for _ in range(2):
         k().attention_decode_mma(c["q"].to(DEV, act), out, c["kpool"].to(DEV, act), c["vpool"].to(DEV, act),
@@ -385,7 +432,7 @@ def test_tensor_core_attention_finds_one_far_key_among_hundreds(kind):
         k().attention_prefill_mma(*args, dev(req), dev(pair0), len(req), H, Hk, hd, ps, None, hd ** -0.5)
     else:
         n_splits = -(-701 // 64)
-        scratch = torch.empty(k().attention_decode_scratch_floats(c["N"], H, n_splits, hd), device=DEV)
+        scratch = torch.zeros(k().attention_decode_scratch_floats(c["N"], H, n_splits, hd), device=DEV)
         k().attention_decode_mma(*args, scratch, 2, c["N"], H, Hk, hd, ps, None, hd ** -0.5, n_splits, 64)
     assert torch.allclose(out.float().cpu(), ref, **tol(act))
 

@@ -32,6 +32,8 @@ def _symbols(head_dim):
     lib.ie_attention_decode.argtypes = [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, I, P]
     lib.ie_attention_decode.restype = c_int
     lib.ie_attention_decode_noalloc_capacity.restype = c_longlong
+    lib.ie_attention_decode_scratch_floats.argtypes = [I, I, I]
+    lib.ie_attention_decode_scratch_floats.restype = c_longlong
     return lib
 
 
@@ -49,11 +51,11 @@ def test_no_alloc_entry_point_matches_the_ordinary_one(head_dim):
         q, kp, vp = c["q"].to(DEV, bf), c["kpool"].to(DEV, bf), c["vpool"].to(DEV, bf)
         table, q_start, ctx = c["table"].to(DEV), dev(c["q_start"]), dev(ctx_before)
         n_splits = -(-(max(a + b for a, b in zip(q_lens, ctx_before))) // split_keys)
-        need = c["N"] * H * n_splits * (head_dim + 2)
+        need = lib.ie_attention_decode_scratch_floats(c["N"], H, n_splits)
         assert need <= lib.ie_attention_decode_noalloc_capacity()
         out_a = torch.full((c["N"], H * head_dim), float("nan"), device=DEV, dtype=bf)
         out_b = torch.full_like(out_a, float("nan"))
-        scratch = torch.empty(need, device=DEV)
+        scratch = torch.zeros(need, device=DEV)      # the ordinary entry point wants its tickets zeroed by the caller
         common = (q.stride(0), out_a.stride(0), table.stride(0), len(q_lens), c["N"], H, Hk, head_dim, ps, 0,
                   head_dim ** -0.5, n_splits, split_keys, stream)
         rc = lib.ie_attention_decode(q.data_ptr(), out_a.data_ptr(), kp.data_ptr(), vp.data_ptr(), table.data_ptr(),
