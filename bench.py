@@ -131,7 +131,7 @@ def run_ours(args):
     t_build = time.perf_counter()
     with tempfile.TemporaryDirectory(prefix="bench_model_") as tmp:
         write_random_model(cfg, args.seed, tmp)
-        engine = Engine.from_dir(tmp, dtype="bfloat16", n_total_blocks=64 * POOL_CONTEXT // PAGE, block_size=PAGE,
+        engine = Engine.from_dir(tmp, dtype="bfloat16", n_total_blocks=args.pool_requests * POOL_CONTEXT // PAGE, block_size=PAGE,
                                  max_requests=64, max_tokens_per_step=8192, chunk=2048)
     t_build = time.perf_counter() - t_build
     runner = engine.runner
@@ -157,9 +157,12 @@ def run_ours(args):
         runner.close("p")
         return e0.elapsed_time(e1)
 
-    for _ in range(3):
-        prefill_once()
-    pre_ms = sorted(prefill_once() for _ in range(args.prefill_reps))
+    if args.only == "decode":
+        pre_ms = [float("nan")]
+    else:
+        for _ in range(3):
+            prefill_once()
+        pre_ms = sorted(prefill_once() for _ in range(args.prefill_reps))
     pre = pre_ms[len(pre_ms) // 2]
     prefill = {"value": PROMPT_LEN / pre * 1e3, "unit": "tok/s", "tokens": PROMPT_LEN, "ms": pre,
                "frac": prefill_flops(cfg, PROMPT_LEN) / (pre * 1e-3) / (pk["bf16_tflops"] * 1e12),
@@ -225,11 +228,21 @@ def run_ours(args):
         h2d = min(runner.graphs._buckets[k].n for k in key) * 4 if key else 0
         return dict(tok_s=n_tok / (t1 - t0), h2d=h2d, d2h=4 * batch)
 
+    if args.only == "prefill":
+        clocks.stop()
+        print(json.dumps({"impl": "ours", "only": "prefill", "prefill": prefill, "config": {"model": args.model, "layers": cfg.num_hidden_layers}}))
+        return 0
     main = decode_device(args.batch, args.steps, args.warmup)
+    if args.only == "decode":
+        clocks.stop()
+        print(json.dumps({"impl": "ours", "only": "decode", "value": main["tok_s"], "ms_per_step": main["ms_per_step"],
+                          "config": {"model": args.model, "layers": cfg.num_hidden_layers, "global_batch": args.batch}}))
+        return 0
     e2e = decode_e2e(args.batch, args.steps, args.warmup)
     points = {}
     for b in (1, 64):
-        points[f"decode_b{b}"] = decode_device(b, args.steps, args.warmup)["tok_s"]
+        if b <= args.pool_requests:
+            points[f"decode_b{b}"] = decode_device(b, args.steps, args.warmup)["tok_s"]
     clocks.stop()
     clk = clocks.summary(main["t0"], main["t1"])
 
@@ -280,6 +293,9 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (0: all)")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--prefill-reps", type=int, default=7)
+    ap.add_argument("--only", choices=["all", "decode", "prefill"], default="all",
+                    help="measure one part only (short runs for profiling); the JSON line then lacks the rest")
+    ap.add_argument("--pool-requests", type=int, default=64, help="requests of 4,096 tokens the cache pool is made for")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py measures a single-GPU engine; --gpus {args.gpus} is not supported (use --gpus 1)")
