@@ -140,7 +140,9 @@ __device__ __forceinline__ void load_kv_tile(const MmaAttnParams& p, const int* 
 // One warp, 16 rows, one tile of KT keys that lies in shared memory: scores, online
 // softmax update, output accumulation.  lim0/lim1 and first0/first1 bound the visible
 // keys of the lane's two rows (row = lane/4 and lane/4 + 8).
-template <int KT>
+// HALF: rows 8..15 of the tile do not exist (a decode step of a group of at most 8 heads): their share
+// of the softmax arithmetic is left out; the MMAs compute them anyway.
+template <int KT, bool HALF = false>
 __device__ __forceinline__ void warp_tile(const uint32_t (&qf)[KSTEPS][4], float (&o)[NT_O][4], float (&m)[2],
                                           float (&l)[2], uint32_t ks_addr, uint32_t vs_addr, int k0, int lim0,
                                           int lim1, int first0, int first1, bool need_mask, float scale_log2,
@@ -171,16 +173,20 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&qf)[KSTEPS][4], float
       const int kp = k0 + i * 8 + col;
       if (kp > lim0 || kp < first0) s[i][0] = -INFINITY;
       if (kp + 1 > lim0 || kp + 1 < first0) s[i][1] = -INFINITY;
-      if (kp > lim1 || kp < first1) s[i][2] = -INFINITY;
-      if (kp + 1 > lim1 || kp + 1 < first1) s[i][3] = -INFINITY;
+      if (!HALF) {
+        if (kp > lim1 || kp < first1) s[i][2] = -INFINITY;
+        if (kp + 1 > lim1 || kp + 1 < first1) s[i][3] = -INFINITY;
+      }
     }
     mx0 = fmaxf(mx0, fmaxf(s[i][0], s[i][1]));
-    mx1 = fmaxf(mx1, fmaxf(s[i][2], s[i][3]));
+    if (!HALF) mx1 = fmaxf(mx1, fmaxf(s[i][2], s[i][3]));
   }
   mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
   mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
-  mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
-  mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+  if (!HALF) {
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+  }
   const float mn0 = fmaxf(m[0], mx0), mn1 = fmaxf(m[1], mx1);
   const float ms0 = mn0 == -INFINITY ? 0.f : mn0, ms1 = mn1 == -INFINITY ? 0.f : mn1;
   const float c0 = fast_exp2(m[0] - ms0), c1 = fast_exp2(m[1] - ms1);  // exp2(-inf) = 0
@@ -191,11 +197,15 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&qf)[KSTEPS][4], float
 #pragma unroll
   for (int i = 0; i < NT_S; ++i) {
     const float p0 = fast_exp2(s[i][0] - ms0), p1 = fast_exp2(s[i][1] - ms0);
-    const float p2 = fast_exp2(s[i][2] - ms1), p3 = fast_exp2(s[i][3] - ms1);
     sum0 += p0 + p1;
-    sum1 += p2 + p3;
     pf[i][0] = pack_bf16(p0, p1);
-    pf[i][1] = pack_bf16(p2, p3);
+    if (!HALF) {
+      const float p2 = fast_exp2(s[i][2] - ms1), p3 = fast_exp2(s[i][3] - ms1);
+      sum1 += p2 + p3;
+      pf[i][1] = pack_bf16(p2, p3);
+    } else {
+      pf[i][1] = 0u;
+    }
   }
   l[0] = l[0] * c0 + sum0;
   l[1] = l[1] * c1 + sum1;
@@ -203,8 +213,10 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&qf)[KSTEPS][4], float
   for (int i = 0; i < NT_O; ++i) {
     o[i][0] *= c0;
     o[i][1] *= c0;
-    o[i][2] *= c1;
-    o[i][3] *= c1;
+    if (!HALF) {
+      o[i][2] *= c1;
+      o[i][3] *= c1;
+    }
   }
 #pragma unroll
   for (int kk = 0; kk < KT / 16; ++kk) {
@@ -423,8 +435,12 @@ __global__ void __launch_bounds__(DC_THREADS) attention_decode_kernel(MmaAttnPar
       __syncwarp();
       const uint32_t sb = base + (i % DC_STAGES) * DC_STAGE_BYTES;
       const bool need_mask = (k0 + DC_KT - 1 > ctx) || (p.window > 0);
-      warp_tile<DC_KT>(qf, o, m, l, sb, sb + DC_KT * HD * 2, k0, lim0, lim1, first0, first1, need_mask,
-                       p.scale_log2, lane);
+      if (n_pairs <= 8)
+        warp_tile<DC_KT, true>(qf, o, m, l, sb, sb + DC_KT * HD * 2, k0, lim0, lim1, first0, first1, need_mask,
+                               p.scale_log2, lane);
+      else
+        warp_tile<DC_KT, false>(qf, o, m, l, sb, sb + DC_KT * HD * 2, k0, lim0, lim1, first0, first1, need_mask,
+                                p.scale_log2, lane);
       __syncwarp();
       if (issued < n_tiles) {
         load_kv_tile<DC_KT, 32>(p, table, c, k_lo + issued * DC_KT, k_hi, sb, sb + DC_KT * HD * 2, lane);

@@ -50,7 +50,8 @@ struct TmaParams {
   float eps;
   int ks;                 // k elements per stage (multiple of 128)
   int n_stages;
-  int x_rows;             // 8 or 16 activation rows kept in shared memory
+  int x_rows;             // 8 or 16 activation rows (one MMA tile of tokens)
+  int x_in_smem;          // activations staged in shared memory once per block (else read from L2 per chunk)
 };
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -95,7 +96,8 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 }
 
 // NT: 8*NT weight rows per unit (NT n-tiles of the MMA per warp)
-template <int NT, int PRO, int EPI>
+// XS: activations staged in shared memory (true) or read from L2 per stage (false; plain prologue only)
+template <int NT, int PRO, int EPI, bool XS>
 __global__ void __launch_bounds__(THREADS, 1) gemm_stream_tma_kernel(TmaParams p) {
   constexpr int UNIT_ROWS = 8 * NT;
   extern __shared__ __align__(128) unsigned char smem[];
@@ -162,8 +164,9 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_stream_tma_kernel(TmaParams p
   // --------------------------------------------------------------- consumers
   pdl_wait();
   const int g = lane >> 2, t = lane & 3;
-  // activations -> shared memory, once per block
-  {
+  // activations -> shared memory, once per block (plain activations of a long K stay in L2 instead:
+  // they would crowd the ring out of shared memory)
+  if (XS) {
     unsigned char* xsm = smem + p.n_stages * stage_bytes;
     for (int m = warp; m < p.x_rows; m += CONSUMER_WARPS) {
       bf16* dst = reinterpret_cast<bf16*>(xsm + (size_t)m * x_pitch);
@@ -173,12 +176,14 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_stream_tma_kernel(TmaParams p
       }
       if (PRO == PRO_PLAIN) {
         const bf16* src = (const bf16*)p.A + (size_t)m * p.lda;
+#pragma unroll 4
         for (int k = lane * 8; k < p.K; k += 256)
           *reinterpret_cast<uint4*>(dst + k) = *reinterpret_cast<const uint4*>(src + k);
       } else {
         const int row = p.row_index ? p.row_index[m] : m;
         const float* src = (const float*)p.A + (size_t)row * p.lda;
         float ssq = 0.f;
+#pragma unroll 4
         for (int k = lane * 8; k < p.K; k += 256) {
           const float4 x0 = *reinterpret_cast<const float4*>(src + k), x1 = *reinterpret_cast<const float4*>(src + k + 4);
           float gv[8];
@@ -226,23 +231,53 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_stream_tma_kernel(TmaParams p
 #pragma unroll
       for (int e = 0; e < 4; ++e) acc[nt][0][e] = acc[nt][1][e] = 0.f;
     for (int ksi = 0; ksi < k_stages; ++ksi) {
+      // activations that stay in L2 (plain bfloat16, long K) are requested before the wait for the stage:
+      // they do not depend on it, and their latency then hides behind it
+      uint4 xg0[XS ? 1 : 8], xg1[XS ? 1 : 8];
+      if (!XS) {
+        const bf16* xa = (const bf16*)p.A + (size_t)(g < p.M ? g : 0) * p.lda + (ksi * p.ks + kw + t * 8);
+        const bf16* xb = (const bf16*)p.A + (size_t)(g + 8 < p.M ? g + 8 : 0) * p.lda + (ksi * p.ks + kw + t * 8);
+        const bool va = g < p.M, vb = g + 8 < p.M;
+#pragma unroll
+        for (int u = 0; u < (XS ? 1 : 8); ++u) {
+          const int c = min(u, chunks - 1);
+          xg0[u] = *reinterpret_cast<const uint4*>(xa + c * 32);
+          xg1[u] = two ? *reinterpret_cast<const uint4*>(xb + c * 32) : make_uint4(0u, 0u, 0u, 0u);
+          if (!va) xg0[u] = make_uint4(0u, 0u, 0u, 0u);
+          if (!vb) xg1[u] = make_uint4(0u, 0u, 0u, 0u);
+        }
+      }
       if (!dead && (failed || !mbar_wait(full0 + 8 * s, phase))) {
         dead = true;
         if (lane == 0) { atomicExch(&g_stream_error, 2); failed = 1; }
       }
       if (dead) continue;
       const uint32_t wbase = ring + s * stage_bytes + g * w_pitch + (kw + t * 8) * 2;
-      const uint32_t xbase = xs + g * x_pitch + (ksi * p.ks + kw + t * 8) * 2;
+      if (XS) {
+        const uint32_t xbase = xs + g * x_pitch + (ksi * p.ks + kw + t * 8) * 2;
 #pragma unroll 4
-      for (int c = 0; c < chunks; ++c) {
-        const uint4 x0 = lds128(xbase + c * 64);
-        uint4 x1 = make_uint4(0u, 0u, 0u, 0u);
-        if (two) x1 = lds128(xbase + 8 * x_pitch + c * 64);
+        for (int c = 0; c < chunks; ++c) {
+          const uint4 x0 = lds128(xbase + c * 64);
+          uint4 x1 = make_uint4(0u, 0u, 0u, 0u);
+          if (two) x1 = lds128(xbase + 8 * x_pitch + c * 64);
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-          const uint4 w = lds128(wbase + nt * 8 * w_pitch + c * 64);
-          mma16816(acc[nt][0], x0.x, x1.x, x0.y, x1.y, w.x, w.y);
-          mma16816(acc[nt][1], x0.z, x1.z, x0.w, x1.w, w.z, w.w);
+          for (int nt = 0; nt < NT; ++nt) {
+            const uint4 w = lds128(wbase + nt * 8 * w_pitch + c * 64);
+            mma16816(acc[nt][0], x0.x, x1.x, x0.y, x1.y, w.x, w.y);
+            mma16816(acc[nt][1], x0.z, x1.z, x0.w, x1.w, w.z, w.w);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int u = 0; u < (XS ? 1 : 8); ++u) {
+          if (u < chunks) {
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+              const uint4 w = lds128(wbase + nt * 8 * w_pitch + u * 64);
+              mma16816(acc[nt][0], xg0[u].x, xg1[u].x, xg0[u].y, xg1[u].y, w.x, w.y);
+              mma16816(acc[nt][1], xg0[u].z, xg1[u].z, xg0[u].w, xg1[u].w, w.z, w.w);
+            }
+          }
         }
       }
       __syncwarp();
@@ -294,18 +329,25 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_stream_tma_kernel(TmaParams p
   }
 }
 
-template <int NT, int PRO, int EPI>
-int launch_one(const TmaParams& p, int n_sms, size_t smem, cudaStream_t stream) {
+template <int NT, int PRO, int EPI, bool XS>
+int launch_xs(const TmaParams& p, int n_sms, size_t smem, cudaStream_t stream) {
   static bool attr = false;
   if (!attr) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_stream_tma_kernel<NT, PRO, EPI>,
+    cudaError_t e = cudaFuncSetAttribute(gemm_stream_tma_kernel<NT, PRO, EPI, XS>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, 204 * 1024);
     if (e != cudaSuccess) return (int)e;
     attr = true;
   }
   const int n_units = (p.N + 8 * NT - 1) / (8 * NT);
   const int grid = n_units < n_sms ? n_units : n_sms;
-  return launch_k(gemm_stream_tma_kernel<NT, PRO, EPI>, grid, THREADS, smem, stream, p);
+  return launch_k(gemm_stream_tma_kernel<NT, PRO, EPI, XS>, grid, THREADS, smem, stream, p);
+}
+
+template <int NT, int PRO, int EPI>
+int launch_one(const TmaParams& p, int n_sms, size_t smem, cudaStream_t stream) {
+  if (p.x_in_smem) return launch_xs<NT, PRO, EPI, true>(p, n_sms, smem, stream);
+  if (PRO == PRO_PLAIN) return launch_xs<NT, PRO_PLAIN, EPI, false>(p, n_sms, smem, stream);
+  return IE_BAD_SIZE;
 }
 
 template <int PRO, int EPI>
@@ -317,10 +359,15 @@ int launch_tma(const TmaParams& p, int nt, int n_sms, size_t smem, cudaStream_t 
 }  // namespace
 
 // 1 if the kernel takes this product (M <= 16, K a multiple of 256, activations fit in shared memory)
-extern "C" int ie_gemm_stream_tma_supports(int M, int N, int K) {
+// Activations are kept in shared memory when they take at most this much; beyond it the plain prologue
+// reads them from L2 and the RMSNorm prologue is not offered.
+constexpr size_t X_SMEM_LIMIT = 72 * 1024;
+
+extern "C" int ie_gemm_stream_tma_supports(int M, int N, int K, int pro) {
   if (M <= 0 || M > 16 || N <= 0 || K <= 0 || (K % 256)) return 0;
   const size_t x_bytes = (size_t)(M > 8 ? 16 : 8) * ((size_t)K * 2 + ROW_PAD);
-  return x_bytes <= 132 * 1024 ? 1 : 0;
+  if (pro == PRO_NORM) return x_bytes <= X_SMEM_LIMIT ? 1 : 0;
+  return 1;
 }
 
 // Reads and clears the error word that a timed-out mbarrier wait leaves (0: none).
@@ -335,7 +382,7 @@ extern "C" int ie_gemm_stream_tma(const void* A, const void* W, void* C, const v
                                   const int* row_index, int M, int N, int K, int lda, int ldw, int ldc, float eps,
                                   int pro, int epi, int n_sms, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return IE_OK;
-  if (!ie_gemm_stream_tma_supports(M, N, K) || (lda & 7) || (ldw & 7)) return IE_BAD_SIZE;
+  if (!ie_gemm_stream_tma_supports(M, N, K, pro) || (lda & 7) || (ldw & 7)) return IE_BAD_SIZE;
   if (((uintptr_t)A | (uintptr_t)W) & 15) return IE_BAD_ALIGN;
   if (epi == EPI_SILU_MUL && (N & 1)) return IE_BAD_SIZE;
   if (n_sms <= 0) return IE_BAD_SIZE;
@@ -347,7 +394,9 @@ extern "C" int ie_gemm_stream_tma(const void* A, const void* W, void* C, const v
   const int nt = (N >= 16 * 4 * n_sms) ? 2 : 1;
   const int unit_rows = 8 * nt;
   p.x_rows = M > 8 ? 16 : 8;
-  const size_t x_bytes = (size_t)p.x_rows * ((size_t)K * 2 + ROW_PAD);
+  size_t x_bytes = (size_t)p.x_rows * ((size_t)K * 2 + ROW_PAD);
+  p.x_in_smem = x_bytes <= X_SMEM_LIMIT ? 1 : 0;
+  if (!p.x_in_smem) x_bytes = 0;
   const int ks_try[4] = {2048, 1024, 512, 256};
   // A product that keeps an SM busy for long wants a deep ring (HBM answers after about 2 us, so about
   // 100 KB per SM must be on its way).  A short one gains more from sharing the SM with the kernel behind

@@ -135,7 +135,8 @@ extern "C" int ie_repetition_penalty(float* logits, const int* context, const fl
 // --------------------------------------------------------------------- sample
 __global__ void __launch_bounds__(SM_THREADS) sample_kernel(const float* __restrict__ logits,
                                                             const SampleRow* __restrict__ rows,
-                                                            int* __restrict__ out, int vocab, size_t row_stride) {
+                                                            int* __restrict__ out, int vocab, size_t row_stride,
+                                                            int skip_greedy) {
   __shared__ float red[33];
   __shared__ int redi[33];
   __shared__ float chunk_sum[SM_THREADS];
@@ -144,6 +145,7 @@ __global__ void __launch_bounds__(SM_THREADS) sample_kernel(const float* __restr
   const float* x = logits + (size_t)blockIdx.x * row_stride;
   const SampleRow r = rows[blockIdx.x];
   const int tid = threadIdx.x;
+  if (skip_greedy && r.temperature <= 0.f) return;    // greedy_split_kernel answers this row
 
   // the maximum (and its first index, which is the greedy answer)
   float best = -INFINITY;
@@ -256,10 +258,78 @@ __global__ void __launch_bounds__(SM_THREADS) sample_kernel(const float* __restr
   }
 }
 
+// Greedy rows of a large vocabulary, spread over SG_CHUNKS blocks per row: one block alone reads a row of
+// half a megabyte at the speed of one SM.  Each block finds the maximum of its slice and its first index,
+// takes a ticket of the row, and the block with the last ticket picks the best slice (ties: lowest index,
+// as argmax does).  Rows that are not greedy are left to sample_kernel, which then skips the greedy ones.
+#define SG_CHUNKS 16
+#define SG_MAX_ROWS 4096
+__device__ float g_sg_val[SG_MAX_ROWS * SG_CHUNKS];
+__device__ int g_sg_idx[SG_MAX_ROWS * SG_CHUNKS];
+__device__ unsigned int g_sg_ticket[SG_MAX_ROWS];   // zero between launches
+
+__global__ void __launch_bounds__(256) greedy_split_kernel(const float* __restrict__ logits,
+                                                           const SampleRow* __restrict__ rows, int* __restrict__ out,
+                                                           int vocab, size_t row_stride) {
+  __shared__ float sv[8];
+  __shared__ int si[8];
+  __shared__ unsigned int last;
+  pdl_trigger();
+  pdl_wait();
+  const int row = blockIdx.y, chunk = blockIdx.x;
+  if (rows[row].temperature > 0.f) return;            // not a greedy row
+  const int per = (vocab + SG_CHUNKS - 1) / SG_CHUNKS;
+  const int lo = chunk * per, hi = min(vocab, lo + per);
+  const float* x = logits + (size_t)row * row_stride;
+  float best = -INFINITY;
+  int best_i = 0x7fffffff;
+  for (int i = lo + threadIdx.x; i < hi; i += 256) {
+    const float v = x[i];
+    if (v > best || best_i == 0x7fffffff) { best = v; best_i = i; }   // i ascends: the first maximum stays
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+    if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) { sv[warp] = best; si[warp] = best_i; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < 8; ++w)
+      if (sv[w] > best || (sv[w] == best && si[w] < best_i)) { best = sv[w]; best_i = si[w]; }
+    g_sg_val[row * SG_CHUNKS + chunk] = best;
+    g_sg_idx[row * SG_CHUNKS + chunk] = best_i;
+    __threadfence();
+    last = atomicAdd(&g_sg_ticket[row], 1u);
+    if (last == SG_CHUNKS - 1) {
+      __threadfence();
+      float b = -INFINITY;
+      int bi = 0x7fffffff;
+      for (int c = 0; c < SG_CHUNKS; ++c) {
+        const float v = __ldcg(&g_sg_val[row * SG_CHUNKS + c]);
+        const int i = __ldcg(&g_sg_idx[row * SG_CHUNKS + c]);
+        if (i != 0x7fffffff && (v > b || bi == 0x7fffffff || (v == b && i < bi))) { b = v; bi = i; }
+      }
+      out[row] = bi == 0x7fffffff ? 0 : bi;
+      g_sg_ticket[row] = 0;
+    }
+  }
+}
+
 extern "C" int ie_sample(const float* logits, const void* rows, int* out, int n_rows, int vocab,
                          long long row_stride, cudaStream_t stream) {
   if (n_rows <= 0) return IE_OK;
   if (vocab <= 0) return IE_BAD_SIZE;
+  if (vocab >= 32768 && n_rows <= SG_MAX_ROWS) {
+    // greedy rows here, everything else (and nothing, when all rows are greedy) in sample_kernel
+    int rc = launch_k(greedy_split_kernel, dim3(SG_CHUNKS, n_rows), 256, 0, stream, logits, (const SampleRow*)rows, out,
+                      vocab, (size_t)row_stride);
+    if (rc) return rc;
+    return launch_k(sample_kernel, n_rows, SM_THREADS, 0, stream, logits, (const SampleRow*)rows, out, vocab,
+                    (size_t)row_stride, 1);
+  }
   return launch_k(sample_kernel, n_rows, SM_THREADS, 0, stream, logits, (const SampleRow*)rows, out, vocab,
-                  (size_t)row_stride);
+                  (size_t)row_stride, 0);
 }

@@ -261,7 +261,7 @@ def stream_library():
         lib.ie_gemm_stream.restype = c_int
         lib.ie_gemm_stream_tma.argtypes = [P, P, P, P, I, P, I, I, I, I, I, I, F, I, I, I, P]
         lib.ie_gemm_stream_tma.restype = c_int
-        lib.ie_gemm_stream_tma_supports.argtypes = [I, I, I]
+        lib.ie_gemm_stream_tma_supports.argtypes = [I, I, I, I]
         lib.ie_gemm_stream_tma_supports.restype = c_int
         lib.ie_gemm_stream_tma_error.restype = c_int
         _stream_lib = lib
@@ -299,7 +299,7 @@ def gemm_stream(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, m: int, epi: 
     else:
         assert a.dtype is torch.float32 and gain.shape == (k,)
     lib = stream_library()
-    if nt is None and lib.ie_gemm_stream_tma_supports(m, n, k):
+    if nt is None and lib.ie_gemm_stream_tma_supports(m, n, k, 0 if gain is None else 1):
         # persistent bulk-copy kernel: one block per SM, weights through a ring of shared memory
         _check(lib.ie_gemm_stream_tma(_ptr(a), _ptr(w), _ptr(c), _ptr(gain),
                                       dtype_code(gain.dtype) if gain is not None else 0, _ptr(row_index), m, n, k,

@@ -178,8 +178,7 @@ def test_gemm_stream_bulk_copy_kernel(M, N, K):
     """The persistent kernel (weights by cp.async.bulk through a shared-memory ring), default for K % 256 == 0."""
     from inf_engine_b200 import kernels
     lib = kernels.stream_library()
-    if not lib.ie_gemm_stream_tma_supports(M, N, K):
-        pytest.skip("activations of this shape do not fit the kernel's shared memory")
+    assert lib.ie_gemm_stream_tma_supports(M, N, K, 0)
     torch.manual_seed(M * 7 + N)
     bf = torch.bfloat16
     a = torch.randn(M, K, device=DEV).to(bf)
@@ -199,7 +198,7 @@ def test_gemm_stream_bulk_copy_kernel(M, N, K):
     want = res.cpu() + ref
     k().gemm_stream(a, w, res, M, "residual")
     assert float((res.cpu() - want).abs().max()) <= 2e-4 * scale + 1e-5
-    if K <= 2048:
+    if lib.ie_gemm_stream_tma_supports(M, N, K, 1):
         x = torch.randn(M + 3, K, device=DEV) * 2
         rows = torch.randperm(M + 3)[:M].to(torch.int32).to(DEV)
         for gain_dtype in (bf, torch.float32):
@@ -518,6 +517,32 @@ def test_sampling_follows_the_plain_distribution_and_the_hashed_uniform(vocab):
         assert lo - 1e-5 <= u <= float(cdf[tok]) + 1e-5, f"{c.mode}: u={u} outside [{lo}, {float(cdf[tok])}] of token {tok}"
     # the draws of one row spread over several tokens (the hash differs with the key)
     assert len(set(out[n_draws:2 * n_draws])) >= 2
+
+
+def test_greedy_rows_of_a_large_vocabulary_beside_sampled_rows():
+    """Above 32,768 entries greedy rows are answered by sixteen blocks a row; the other rows by the sampling kernel."""
+    from inf_engine_b200.sampling import SamplingConfig, uniform_of
+    torch.manual_seed(9)
+    vocab = 40003
+    logits = torch.randn(6, vocab) * 2
+    logits[1, 30000] = logits[1, 123] = 60.0                        # a tie across two slices: the lower index wins
+    logits[3, vocab - 1] = 70.0                                      # the very last entry
+    cfgs = [SamplingConfig(), SamplingConfig(), SamplingConfig(mode="temperature", temperature=0.8, seed=3),
+            SamplingConfig(), SamplingConfig(mode="top_k", top_k=4, seed=3), SamplingConfig()]
+    keys = [(i << 32) | 1 for i in range(6)]
+    out = torch.full((6,), -1, device=DEV, dtype=torch.int32)
+    for _ in range(2):                                               # the tickets go back to zero after a launch
+        k().sample(logits.to(DEV), _rows(cfgs, keys, vocab), out)
+        got = out.cpu().tolist()
+        for i in (0, 1, 3, 5):
+            assert got[i] == int(logits[i].argmax()), i
+        assert got[1] == 123 and got[3] == vocab - 1
+        for i in (2, 4):
+            probs = plain_llama.filtered_distribution(logits[i], cfgs[i].mode.value, cfgs[i].temperature, cfgs[i].top_k, 1.0).double()
+            cdf = probs.cumsum(0)
+            u = uniform_of(cfgs[i].seed, keys[i])
+            lo = float(cdf[got[i] - 1]) if got[i] > 0 else 0.0
+            assert probs[got[i]] > 0 and lo - 1e-5 <= u <= float(cdf[got[i]]) + 1e-5
 
 
 def test_sampling_is_reproducible_and_independent_of_the_batch():
