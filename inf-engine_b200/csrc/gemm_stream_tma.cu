@@ -402,7 +402,15 @@ extern "C" int ie_gemm_stream_tma(const void* A, const void* W, void* C, const v
   // 100 KB per SM must be on its way).  A short one gains more from sharing the SM with the kernel behind
   // it in the chain, which then prefetches its weights early: that needs dynamic + static shared memory
   // of each to stay under 113 KB.
-  const bool deep = (size_t)N * K * 2 / (size_t)n_sms > 192 * 1024;
+  bool deep = (size_t)N * K * 2 / (size_t)n_sms > 192 * 1024;
+  {
+    static int force = -2;   // IE_STREAM_RING=shallow|deep overrides the choice (for measurements)
+    if (force == -2) {
+      const char* e = getenv("IE_STREAM_RING");
+      force = !e ? -1 : (e[0] == 's' ? 0 : 1);
+    }
+    if (force >= 0) deep = force == 1;
+  }
   size_t budget = (size_t)((deep ? 212 : 113) - (nt == 2 ? 17 : 9)) * 1024;
   int n_stages = 0;
   size_t stage_bytes = 0;
