@@ -316,3 +316,45 @@ def gemm_stream(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, m: int, epi: 
                                            a.stride(0), w.stride(0), c.stride(0), float(eps),
                                            0 if gain is None else 1, _EPI[epi], nt, _stream()),
            f"gemm_stream(m={m}, n={n}, k={k}, {epi})")
+
+
+# ------------------------------------------------ tcgen05 product for many rows (prompt portions)
+_tc_lib = None
+
+
+def tcgen05_library():
+    global _tc_lib
+    if _tc_lib is None:
+        lib = load_library("tcgen05", ["gemm_tcgen05.cu"])
+        P, I = c_void_p, c_int
+        lib.ie_gemm_tcgen05.argtypes = [P, P, P, I, I, I, I, I, I, I, I, I, P]
+        lib.ie_gemm_tcgen05.restype = c_int
+        lib.ie_gemm_tcgen05_supports.argtypes = [I, I, I, I, I]
+        lib.ie_gemm_tcgen05_supports.restype = c_int
+        lib.ie_gemm_tcgen05_error.restype = c_int
+        _tc_lib = lib
+    return _tc_lib
+
+
+def gemm_tcgen05_supports(m: int, n: int, k: int, lda: int, ldw: int) -> bool:
+    return bool(tcgen05_library().ie_gemm_tcgen05_supports(m, n, k, lda, ldw))
+
+
+def gemm_tcgen05_error() -> int:
+    """Reads and clears the error word that a timed-out wait of the tcgen05 kernel leaves (0: none)."""
+    return int(tcgen05_library().ie_gemm_tcgen05_error())
+
+
+def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epi: str = "bf16", bn: int = 256) -> None:
+    """c = a @ w^T on the fifth-generation tensor cores (TMA operands, accumulator in tensor memory).
+
+    ``epi``: "bf16" store, "residual" adds into the float32 ``c``, "silu_mul" takes w's rows as alternating
+    gate/up and writes silu(gate)*up, half as wide."""
+    flush = globals().get("flush_stream_chain")
+    if flush:
+        flush()
+    m, k = a.shape
+    n = w.shape[0]
+    assert a.dtype is torch.bfloat16 and w.dtype is torch.bfloat16 and a.stride(1) == 1 and w.stride(1) == 1
+    _check(tcgen05_library().ie_gemm_tcgen05(_ptr(a), _ptr(w), _ptr(c), m, n, k, a.stride(0), w.stride(0), c.stride(0),
+                                             _EPI[epi], bn, sm_count(), _stream()), f"gemm_tcgen05(m={m}, n={n}, k={k}, {epi})")

@@ -50,10 +50,19 @@ class GatedMLP:
         self.gate_up.stream(residual, h, n, "silu_mul", gain, eps)
         self.down.stream(h, residual, n, "residual")
 
+    TCGEN05_MIN_ROWS = 128     # below one tile of rows the library product is the better choice
+
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         n = x.shape[0]
         s, ws, dt = self.spec, self.rt.ws, self.rt.act_dtype
-        gu = self.gate_up(x, ws.take("ff_gate_up", (n, 2 * s.intermediate), dt))
         h = ws.take("ff_hidden", (n, s.intermediate), dt)
-        kernels.silu_mul(gu, h, interleaved=True)
+        w = self.gate_up.weight
+        if (dt is torch.bfloat16 and w.dtype is torch.bfloat16 and n >= self.TCGEN05_MIN_ROWS
+                and kernels.gemm_tcgen05_supports(n, 2 * s.intermediate, s.hidden, x.stride(0), w.stride(0))):
+            # gate/up on the tcgen05 tensor cores with silu(gate)*up in the epilogue: the [n, 2*intermediate]
+            # matrix never goes to memory
+            kernels.gemm_tcgen05(x, w, h, "silu_mul")
+        else:
+            gu = self.gate_up(x, ws.take("ff_gate_up", (n, 2 * s.intermediate), dt))
+            kernels.silu_mul(gu, h, interleaved=True)
         return self.down(h, ws.take("ff_out", (n, s.hidden), dt))

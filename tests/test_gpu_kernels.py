@@ -217,6 +217,40 @@ def test_gemm_stream_bulk_copy_kernel(M, N, K):
     assert kernels.stream_error() == 0
 
 
+@pytest.mark.parametrize("M,N,K,bn", [(128, 256, 64, 256), (100, 200, 128, 128), (333, 1000, 512, 128),
+                                      (700, 1306, 192, 256), (2048, 3072, 2048, 256)])
+def test_gemm_tcgen05_against_float32(M, N, K, bn):
+    """TMA operands, tcgen05.mma with the accumulator in tensor memory, persistent over tiles, edge tiles included."""
+    torch.manual_seed(M + N)
+    bf = torch.bfloat16
+    a = torch.randn(M, K, device=DEV).to(bf)
+    w = (torch.randn(N, K, device=DEV) * 0.05).to(bf)
+    ref = a.float().cpu() @ w.float().cpu().T
+    scale = float(ref.abs().max())
+    out = torch.full((M, N), float("nan"), device=DEV, dtype=bf)
+    k().gemm_tcgen05(a, w, out, "bf16", bn)
+    assert float((out.float().cpu() - ref).abs().max()) <= 1e-2 * scale
+    res = torch.randn(M, N, device=DEV)
+    want = res.cpu() + ref
+    k().gemm_tcgen05(a, w, res, "residual", bn)
+    assert float((res.cpu() - want).abs().max()) <= 2e-4 * scale + 1e-5
+    h = torch.full((M, N // 2), float("nan"), device=DEV, dtype=bf)
+    k().gemm_tcgen05(a, w, h, "silu_mul", bn)
+    want = plain_llama.silu(ref[:, 0::2]) * ref[:, 1::2]
+    assert float((h.float().cpu() - want).abs().max()) <= 1e-2 * max(1.0, float(want.abs().max()))
+    torch.cuda.synchronize()
+    assert k().gemm_tcgen05_error() == 0
+
+
+def test_gemm_tcgen05_refuses_what_it_cannot_take():
+    from inf_engine_b200.kernels import KernelError
+    bf = torch.bfloat16
+    assert not k().gemm_tcgen05_supports(128, 256, 120, 120, 120)      # K is no multiple of 64
+    a, w = torch.zeros(4, 120, device=DEV, dtype=bf), torch.zeros(8, 120, device=DEV, dtype=bf)
+    with pytest.raises(KernelError, match="size"):
+        k().gemm_tcgen05(a, w, torch.zeros(4, 8, device=DEV, dtype=bf))
+
+
 def test_gemm_stream_refuses_what_it_cannot_take():
     from inf_engine_b200.kernels import KernelError
     bf = torch.bfloat16
