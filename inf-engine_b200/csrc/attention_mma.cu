@@ -355,8 +355,14 @@ __global__ void __launch_bounds__(PF_THREADS) attention_prefill_kernel(MmaAttnPa
 // up in ascending order, so the result does not depend on which warp that is.
 constexpr int DC_WARPS = 1;
 constexpr int DC_THREADS = DC_WARPS * 32;
-constexpr int DC_KT = 32;
-constexpr int DC_STAGES = 4;
+#ifndef IE_DC_KT
+#define IE_DC_KT 32
+#endif
+#ifndef IE_DC_STAGES
+#define IE_DC_STAGES 4
+#endif
+constexpr int DC_KT = IE_DC_KT;
+constexpr int DC_STAGES = IE_DC_STAGES;
 constexpr int DC_STAGE_BYTES = 2 * DC_KT * HD * 2;
 constexpr int DC_WARP_BYTES = DC_STAGES * DC_STAGE_BYTES;
 

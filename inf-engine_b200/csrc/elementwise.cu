@@ -31,6 +31,19 @@ extern "C" int ie_embed_gather(const int* ids, const void* table, int table_dtyp
   return IE_BAD_DTYPE;
 }
 
+// ids[i] = prev[src[i]] where src[i] >= 0: a token that the step before sampled and that the host has
+// not read yet is taken on the device (steps are enqueued one ahead of the host's read of their results)
+__global__ void patch_tokens_kernel(int* __restrict__ ids, const int* __restrict__ src, const int* __restrict__ prev, int n) {
+  pdl_trigger();
+  pdl_wait();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n && src[i] >= 0) ids[i] = prev[src[i]];
+}
+extern "C" int ie_patch_tokens(int* ids, const int* src, const int* prev, int n, cudaStream_t stream) {
+  if (n <= 0) return IE_OK;
+  return launch_k(patch_tokens_kernel, (n + 127) / 128, 128, 0, stream, ids, src, prev, n);
+}
+
 // -------------------------------------------------------------------- RMSNorm
 // x = residual[row] (+ delta[row]);  residual[row] = x (unless rows are gathered);
 // out[m] = x / sqrt(mean(x^2) + eps) * gain          (engine/layers.py:24-25)

@@ -21,13 +21,13 @@ from ..sampling.sampler import Sampler, SamplingConfig, pack_rows, request_key
 from ..weights.random_init import write_random_model
 from .batch import StepEntry
 from .runner import ModelRunner
-from .scheduler import Request, Scheduler
+from .scheduler import PLACEHOLDER, Request, Scheduler
 
 
 class Engine:
     def __init__(self, runner: ModelRunner, eos_token=None, sampling: SamplingConfig | None = None,
                  max_queue_depth: int = 4096, max_batch: int | None = None, max_tokens_per_step: int = 2048,
-                 chunk: int | None = None):
+                 chunk: int | None = None, pipeline: bool = True):
         self.runner = runner
         self.cfg = sampling or SamplingConfig()
         if eos_token is None:
@@ -39,6 +39,13 @@ class Engine:
                                    max_queue_depth=max_queue_depth, eos_token=eos_token)
         self.sampler = Sampler(runner.rt)
         self.stats = {"steps": 0, "prefill_tokens": 0, "decode_tokens": 0, "preemptions": 0}
+        # One step ahead: a step is enqueued before the host has read the tokens of the step before; it
+        # takes them on the device.  The host's work for a step then hides behind the GPU's work.
+        self.pipeline = pipeline
+        self._pending = None
+        self._host_ids = [torch.empty(max(1, runner.cache.max_requests), dtype=torch.int32, pin_memory=True)
+                          for _ in range(3)]
+        self._host_next = 0
 
     # ------------------------------------------------------------ construction
     @classmethod
@@ -64,7 +71,7 @@ class Engine:
 
     @property
     def has_work(self) -> bool:
-        return self.scheduler.has_work
+        return self.scheduler.has_work or self._pending is not None
 
     @property
     def completed(self) -> list[Request]:
@@ -73,7 +80,78 @@ class Engine:
     # ------------------------------------------------------------------- step
     @torch.no_grad()
     def step(self, now: float = 0.0) -> list[Request]:
-        """Admit, run one mixed batch, sample, finish; returns the requests completed."""
+        """Admit, run one mixed batch, sample, finish; returns the requests completed.
+
+        With ``pipeline`` the step is enqueued before the tokens of the step before are read (they are
+        taken on the device), and the requests returned are those that the step BEFORE completed."""
+        if self.pipeline and self._can_pipeline():
+            return self._step_ahead(now)
+        done = self._drain(now)
+        return done + self._step_now(now)
+
+    # a penalty over generated tokens needs them on the host; so does a plan that may have to preempt
+    def _can_pipeline(self) -> bool:
+        s = self.scheduler
+        if self.cfg.repetition_penalty != 1.0:
+            return False
+        for r in list(s.running) + s.queue[:4]:
+            if r.sampling is not None and r.sampling.repetition_penalty != 1.0:
+                return False
+        return s.cache.n_free_pages() >= len(s.running) + 1
+
+    def _drain(self, now: float) -> list[Request]:
+        if self._pending is None:
+            return []
+        pend, self._pending = self._pending, None
+        return self._resolve(pend, None, now)
+
+    def _resolve(self, pend, in_flight, now: float) -> list[Request]:
+        plan, wanted, host, event = pend["plan"], pend["wanted"], pend["host"], pend["event"]
+        event.synchronize()                                   # the step's one device-to-host read has landed
+        ids = host[:len(wanted)].tolist()
+        return self.scheduler.resolve(plan, {e.request.req_id: t for e, t in zip(wanted, ids)}, in_flight, now)
+
+    def _step_ahead(self, now: float) -> list[Request]:
+        prev = self._pending
+        plan = self.scheduler.plan()
+        self.stats["preemptions"] += len(plan.preempted)
+        if not plan.entries:
+            return self._drain(now)
+        prev_index = {e.request.req_id: i for i, e in enumerate(prev["wanted"])} if prev else {}
+        entries, token_src, any_src = [], [], False
+        for e in plan.entries:
+            toks = e.tokens
+            if toks[-1] == PLACEHOLDER:                       # the token the step before sampled for this request
+                assert len(toks) == 1 and e.request.req_id in prev_index
+                token_src.append(prev_index[e.request.req_id])
+                toks = [0]
+                any_src = True
+            else:
+                token_src.extend([-1] * len(toks))
+            entries.append(StepEntry(e.request.req_id, toks, [len(toks) - 1] if e.wants_logits else []))
+        wanted = [e for e in plan.entries if e.wants_logits]
+        configs = [e.request.sampling or self.cfg for e in wanted]
+        keys = [request_key(e.request.req_id, len(e.request.generated)) for e in wanted]
+        rows = pack_rows(configs, keys, self.runner.spec.vocab_size) if wanted else None
+        _, ids = self.runner.step_and_sample(entries, rows, device_tokens=prev["dev"] if any_src else None,
+                                             token_src=token_src if any_src else None)
+        for e in plan.entries:
+            self.stats["decode_tokens" if len(e.tokens) == 1 and e.request.generated else "prefill_tokens"] += len(e.tokens)
+        self.stats["steps"] += 1
+        self.scheduler.book(plan)
+        new = None
+        if wanted:
+            host = self._host_ids[self._host_next]
+            self._host_next = (self._host_next + 1) % len(self._host_ids)
+            host[:len(wanted)].copy_(ids[:len(wanted)], non_blocking=True)
+            event = torch.cuda.Event()
+            event.record()
+            new = {"plan": plan, "wanted": wanted, "host": host, "event": event, "dev": ids}
+        done = self._resolve(prev, plan, now) if prev else []      # read the step before while this one runs
+        self._pending = new
+        return done
+
+    def _step_now(self, now: float) -> list[Request]:
         plan = self.scheduler.plan()
         self.stats["preemptions"] += len(plan.preempted)
         if not plan.entries:

@@ -70,6 +70,8 @@ class DecodeGraphs:
             n += B * w
         off["sample_rows"] = (n, B * 7)
         n += B * 7
+        off["token_src"] = (n, B)
+        n += B
         return off, n
 
     def _get(self, B: int, widths: tuple[int, ...]):
@@ -96,13 +98,14 @@ class DecodeGraphs:
             ctx.host = {"q_lens": [1] * B, "q_start": list(range(B + 1)), "slots": [0] * B, "graph": True}
             b.ctx = ctx
             b.rows = view("sample_rows").view(B, 7)
+            b.token_src = view("token_src")
             b.sampled = torch.zeros(B, dtype=torch.int32, device=dev)
             b.logits = None
             self._buckets[key] = b
         return b
 
     # ------------------------------------------------------------------ steps
-    def _fill(self, b, entries, sample_rows: np.ndarray | None) -> None:
+    def _fill(self, b, entries, sample_rows: np.ndarray | None, token_src=None) -> None:
         cache = self.runner.cache
         ps = cache.page_size
         B, R = b.B, len(entries)
@@ -131,6 +134,10 @@ class DecodeGraphs:
             rows = h[r0:r0 + B * 7].reshape(B, 7)
             rows[:R] = sample_rows
             rows.view(np.float32)[R:, 1] = 1.0      # padding rows: greedy
+        t0 = o["token_src"][0]
+        h[t0:t0 + B] = -1
+        if token_src is not None:
+            h[t0:t0 + R] = token_src
         self.rt.staging.upload(h, into=b.dev)
 
     def _forward(self, b):
@@ -139,20 +146,26 @@ class DecodeGraphs:
         kernels.sample(logits, b.rows, b.sampled)
         return logits
 
-    def step(self, entries, sample_rows: np.ndarray | None, device_tokens: torch.Tensor | None = None):
+    def step(self, entries, sample_rows: np.ndarray | None, device_tokens: torch.Tensor | None = None,
+             token_src=None):
         """Run one decode step for ``entries`` (pages reserved by the caller).
         Returns (logits [R, V], sampled ids [R] or None), views of static buffers.
         ``device_tokens`` (int32 [R] on the device, e.g. the ids the last step sampled)
-        replaces the entries' token ids without a trip through the host."""
+        replaces the entries' token ids without a trip through the host: all of them, or, with
+        ``token_src`` (one index into ``device_tokens`` per entry, -1 to keep the host's id), some."""
         cache = self.runner.cache
         R = len(entries)
         B = _bucket(R, BATCH_BUCKETS)
         widths = tuple(_bucket(max(len(g.tables[e.rid]) for e in entries), [1 << i for i in range(3, 24)])
                        for g in cache.kv_groups)
         b = self._get(B, widths)
-        self._fill(b, entries, sample_rows)
+        self._fill(b, entries, sample_rows, token_src)
         if device_tokens is not None:
-            b.ctx.token_ids[:R].copy_(device_tokens[:R])
+            if token_src is None:
+                b.ctx.token_ids[:R].copy_(device_tokens[:R])
+            else:
+                from .. import kernels
+                kernels.patch_tokens(b.ctx.token_ids[:R], b.token_src, device_tokens)
         rt = self.rt
         saved = rt.ws
         rt.ws = self.ws

@@ -86,10 +86,12 @@ class ModelRunner:
         (a view of a buffer that the next step overwrites) or None."""
         return self.step_and_sample(entries, None)[0]
 
-    def step_and_sample(self, entries: list[StepEntry], sample_rows=None, device_tokens=None):
+    def step_and_sample(self, entries: list[StepEntry], sample_rows=None, device_tokens=None, token_src=None):
         """``step`` plus, when ``sample_rows`` (int32 numpy [n_wanted, 7] records of
         ``sampling.Sampler.pack``) is given, the sampled token ids (int32, device).
-        Steps that are all single decode tokens replay a CUDA graph."""
+        Steps that are all single decode tokens replay a CUDA graph.  ``device_tokens`` (int32 on the
+        device) with ``token_src`` (per token of the step an index into it, or -1) replaces token ids that
+        the host does not know yet; without ``token_src`` it replaces all of them in order."""
         if not entries:
             return None, None
         cache = self.cache
@@ -120,11 +122,17 @@ class ModelRunner:
             assert ok
         sampled = None
         if self.use_graphs and self.graphs.usable(entries):
-            logits, sampled = self.graphs.step(entries, sample_rows, device_tokens)
+            logits, sampled = self.graphs.step(entries, sample_rows, device_tokens, token_src)
         else:
             ctx = build_context(self.rt, cache, entries)
             if device_tokens is not None:
-                ctx.token_ids.copy_(device_tokens)
+                if token_src is None:
+                    ctx.token_ids.copy_(device_tokens)
+                else:
+                    import numpy as np
+                    from .. import kernels
+                    src = self.rt.staging.upload(np.asarray(token_src, dtype=np.int32))
+                    kernels.patch_tokens(ctx.token_ids, src, device_tokens)
             logits = self.model.forward(ctx)
             if sample_rows is not None and logits is not None:
                 from .. import kernels

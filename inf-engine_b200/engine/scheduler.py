@@ -59,11 +59,17 @@ class Request:
         return self.prompt_ids + self.generated
 
 
+PLACEHOLDER = -1    # stands in ``generated`` for a token that was sampled on the device and not read yet
+
+
 @dataclass
 class PlannedEntry:
     request: Request
     tokens: list[int]
     wants_logits: bool
+    slot: int = -1           # index in ``generated`` of the token this entry samples (booked steps)
+    last: bool = False       # the request ends with this token whatever it is (max_new_tokens)
+    cancelled: bool = False  # the request ended at an earlier token: this entry's result is dropped
 
 
 @dataclass
@@ -240,4 +246,50 @@ class Scheduler:
                 self.running.remove(req)
                 self.completed.append(req)
                 finished.append(req)
+        return finished
+
+    # ------------------------------------------------- steps booked before their tokens are read
+    def book(self, plan: StepPlan) -> None:
+        """Record a step that has been enqueued while its sampled tokens are still on the device: every
+        sampling entry gets a PLACEHOLDER in ``generated``; a request that reaches ``max_new_tokens`` ends
+        here and gives its pages back (later steps run after this one on the device, so the pages are not
+        rewritten before it has finished)."""
+        for e in plan.entries:
+            if not e.wants_logits:
+                continue
+            req = e.request
+            e.slot = len(req.generated)
+            req.generated.append(PLACEHOLDER)
+            if len(req.generated) >= req.max_new_tokens:
+                e.last = True
+                self.cache.close(req.req_id)
+                self.running.remove(req)
+
+    def resolve(self, plan: StepPlan, sampled: dict, in_flight: StepPlan | None = None, now: float = 0.0) -> list[Request]:
+        """The tokens of a booked step have arrived: put them in place of the placeholders, and end the
+        requests that end with them (EOS, stop_check, or booked as last).  A request that ends by its token
+        may have an entry in the step ``in_flight``; that entry is cancelled and its placeholder dropped."""
+        finished = []
+        for e in plan.entries:
+            if not e.wants_logits or e.cancelled:
+                continue
+            req = e.request
+            tok = int(sampled[req.req_id])
+            req.generated[e.slot] = tok
+            req.start_time = req.start_time or now
+            by_token = tok in self.eos or (req.stop_check is not None and req.stop_check(req.generated[:e.slot + 1]))
+            if not (e.last or by_token):
+                continue
+            if by_token:
+                del req.generated[e.slot + 1:]
+                if in_flight is not None:
+                    for f in in_flight.entries:
+                        if f.request is req:
+                            f.cancelled = True
+                if req in self.running:
+                    self.cache.close(req.req_id)
+                    self.running.remove(req)
+            req.finish_time = now
+            self.completed.append(req)
+            finished.append(req)
         return finished

@@ -65,6 +65,8 @@ def core():
         lib = load_library("core")
         P, I, F, L = c_void_p, c_int, c_float, c_longlong
         lib.ie_embed_gather.argtypes = [P, P, I, P, I, I, I, P]
+        lib.ie_patch_tokens.argtypes = [P, P, P, I, P]
+        lib.ie_patch_tokens.restype = c_int
         lib.ie_rmsnorm.argtypes = [P, P, P, I, P, I, P, I, I, F, P]
         lib.ie_residual_add.argtypes = [P, P, I, I, I, P]
         lib.ie_rope_kv_write.argtypes = [P, P, P, I, I, P, P, P, P, P, P, I, I, I, I, I, I, I, P]
@@ -88,6 +90,12 @@ def embed_gather(ids: torch.Tensor, table: torch.Tensor, residual: torch.Tensor)
     n, d = residual.shape
     _check(core().ie_embed_gather(_ptr(ids), _ptr(table), dtype_code(table.dtype), _ptr(residual), n, d,
                                   table.shape[0], _stream()), "embed_gather")
+
+
+def patch_tokens(ids: torch.Tensor, src: torch.Tensor, prev: torch.Tensor) -> None:
+    """ids[i] = prev[src[i]] where src[i] >= 0 (token ids that are still on the device)."""
+    assert ids.dtype == src.dtype == prev.dtype == torch.int32 and src.shape[0] >= ids.shape[0]
+    _check(core().ie_patch_tokens(_ptr(ids), _ptr(src), _ptr(prev), ids.shape[0], _stream()), "patch_tokens")
 
 
 def rmsnorm(residual: torch.Tensor, delta: torch.Tensor | None, gain: torch.Tensor, out: torch.Tensor,

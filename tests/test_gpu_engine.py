@@ -284,6 +284,35 @@ def test_sampled_generation_is_seeded_and_independent_of_the_batch(tmp_path):
     assert got == batch[3][:batch[3].index(eos) + 1]
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_steps_enqueued_one_ahead_give_the_same_tokens(tmp_path, dtype):
+    """With ``pipeline`` a step is enqueued before the tokens of the step before are read; requests that end
+    by their token (EOS, stop_check) are found out one step late and the extra step is dropped."""
+    from inf_engine_b200 import Engine, Request, SamplingConfig
+    d = make_model_dir(tmp_path, "tiny_b")
+    config, _ = plain_inputs(d)
+    prompts = [random_tokens(config["vocab_size"], n, 70 + n) for n in (3, 30, 11, 50, 7)]
+    s = SamplingConfig(mode="top_p", top_p=0.95, temperature=0.9, seed=11)
+
+    def run(pipeline, eos=None, stop=None):
+        e = Engine.from_dir(d, dtype=dtype, n_total_blocks=64, block_size=8, max_tokens_per_step=48, chunk=16,
+                            eos_token=eos, pipeline=pipeline)
+        reqs = [Request(i, p, 14 + i, sampling=s, stop_check=stop if i == 1 else None) for i, p in enumerate(prompts)]
+        out = e.run_offline(reqs)
+        e.runner.cache.check()
+        assert e.runner.cache.n_free_pages() == 64 and not e.has_work
+        return [out[i] for i in range(len(prompts))]
+
+    base = run(False)
+    assert run(True) == base
+    assert all(t >= 0 for g in base for t in g)
+    eos = base[3][5]                                           # a token that request 3 produces mid-way
+    stop = lambda g: len(g) >= 4
+    a, b = run(False, eos, stop), run(True, eos, stop)
+    assert a == b and len(a[1]) == 4
+    assert a[3] == base[3][:base[3].index(eos) + 1]
+
+
 def test_command_line(tmp_path):
     d = make_model_dir(tmp_path, "tiny_a")
     config, weights = plain_inputs(d)

@@ -148,3 +148,38 @@ def test_random_workloads_finish_with_every_page_back(seed):
     for r in reqs:
         assert r.generated == list(range(r.max_new_tokens))
     assert cache.n_free_pages() == cache.n_pages and cache.n_free_slots == 4
+
+
+def test_steps_booked_before_their_tokens_are_read():
+    """One step ahead: a step is booked with placeholders; its tokens arrive a step later.  A request that
+    ends by its token is found out late, its extra entry is cancelled and the placeholder dropped."""
+    from inf_engine_b200.engine.scheduler import PLACEHOLDER
+    cache, s = make(n_pages=64, eos_token=9)
+    a, b = Request(0, [1, 2, 3], 5), Request(1, [4, 5], 3)
+    s.submit(a)
+    s.submit(b)
+    script = {0: [5, 9, 7, 7, 7], 1: [6, 6, 6]}       # request 0 says EOS as its second token
+    pending = None
+    finished = []
+    steps = 0
+    while s.has_work or pending:
+        plan = s.plan()
+        for e in plan.entries:
+            base = cache.lengths[e.request.req_id]
+            assert all(t >= 0 for t in e.tokens[:-1])
+            cache.advance(e.request.req_id, base + len(e.tokens))
+        s.book(plan)
+        for e in plan.entries:
+            if e.wants_logits:
+                assert e.request.generated[e.slot] == PLACEHOLDER
+        if pending is not None:
+            toks = {e.request.req_id: script[e.request.req_id][e.slot] for e in pending.entries if e.wants_logits}
+            finished += s.resolve(pending, toks, plan)
+        pending = plan if plan.entries else None
+        cache.check()
+        steps += 1
+        assert steps < 50
+    assert a.generated == [5, 9]                         # nothing after the EOS, no placeholder left
+    assert b.generated == [6, 6, 6]                      # ended by max_new_tokens at booking time
+    assert sorted(r.req_id for r in finished) == [0, 1] and s.completed == finished
+    assert cache.n_free_pages() == 64 and cache.n_free_slots == 4
