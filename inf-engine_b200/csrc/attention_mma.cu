@@ -167,8 +167,6 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&qf)[KSTEPS][4], float
   float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
   for (int i = 0; i < NT_S; ++i) {
-#pragma unroll
-    for (int e = 0; e < 4; ++e) s[i][e] *= scale_log2;
     if (need_mask) {
       const int kp = k0 + i * 8 + col;
       if (kp > lim0 || kp < first0) s[i][0] = -INFINITY;
@@ -187,7 +185,9 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&qf)[KSTEPS][4], float
     mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
     mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
   }
-  const float mn0 = fmaxf(m[0], mx0), mn1 = fmaxf(m[1], mx1);
+  // maxima are kept in the exponent's units (score * scale * log2 e); the scale is positive, so it commutes
+  // with the maximum, and it enters each probability as one fused multiply-add: 2^(s*scale - m)
+  const float mn0 = fmaxf(m[0], mx0 * scale_log2), mn1 = fmaxf(m[1], mx1 * scale_log2);
   const float ms0 = mn0 == -INFINITY ? 0.f : mn0, ms1 = mn1 == -INFINITY ? 0.f : mn1;
   const float c0 = fast_exp2(m[0] - ms0), c1 = fast_exp2(m[1] - ms1);  // exp2(-inf) = 0
   m[0] = mn0;
@@ -196,11 +196,11 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&qf)[KSTEPS][4], float
   uint32_t pf[NT_S][2];
 #pragma unroll
   for (int i = 0; i < NT_S; ++i) {
-    const float p0 = fast_exp2(s[i][0] - ms0), p1 = fast_exp2(s[i][1] - ms0);
+    const float p0 = fast_exp2(fmaf(s[i][0], scale_log2, -ms0)), p1 = fast_exp2(fmaf(s[i][1], scale_log2, -ms0));
     sum0 += p0 + p1;
     pf[i][0] = pack_bf16(p0, p1);
     if (!HALF) {
-      const float p2 = fast_exp2(s[i][2] - ms1), p3 = fast_exp2(s[i][3] - ms1);
+      const float p2 = fast_exp2(fmaf(s[i][2], scale_log2, -ms1)), p3 = fast_exp2(fmaf(s[i][3], scale_log2, -ms1));
       sum1 += p2 + p3;
       pf[i][1] = pack_bf16(p2, p3);
     } else {
@@ -209,13 +209,15 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&qf)[KSTEPS][4], float
   }
   l[0] = l[0] * c0 + sum0;
   l[1] = l[1] * c1 + sum1;
+  if (__any_sync(0xffffffffu, c0 != 1.f || c1 != 1.f)) {   // once a row's maximum has settled there is nothing to rescale
 #pragma unroll
-  for (int i = 0; i < NT_O; ++i) {
-    o[i][0] *= c0;
-    o[i][1] *= c0;
-    if (!HALF) {
-      o[i][2] *= c1;
-      o[i][3] *= c1;
+    for (int i = 0; i < NT_O; ++i) {
+      o[i][0] *= c0;
+      o[i][1] *= c0;
+      if (!HALF) {
+        o[i][2] *= c1;
+        o[i][3] *= c1;
+      }
     }
   }
 #pragma unroll
@@ -247,13 +249,15 @@ __device__ __forceinline__ void load_q_frags(uint32_t (&qf)[KSTEPS][4], const bf
 }
 
 // ------------------------------------------------------------------- prefill
-constexpr int PF_WARPS = 4;
-constexpr int PF_THREADS = PF_WARPS * 32;
-constexpr int PF_ROWS = PF_WARPS * 16;
 constexpr int PF_KT = 64;
 constexpr int PF_STAGE_BYTES = 2 * PF_KT * HD * 2;  // K and V of one stage
 
-__global__ void __launch_bounds__(PF_THREADS) attention_prefill_kernel(MmaAttnParams p) {
+// PF_WARPS warps of 16 rows each: 4 (tiles of 64 rows) or 8 (tiles of 128 rows, for long portions: a key tile
+// that is loaded then serves twice as many rows)
+template <int PF_WARPS>
+__global__ void __launch_bounds__(PF_WARPS * 32) attention_prefill_kernel(MmaAttnParams p) {
+  constexpr int PF_THREADS = PF_WARPS * 32;
+  constexpr int PF_ROWS = PF_WARPS * 16;
   extern __shared__ __align__(128) unsigned char smem[];
   pdl_trigger();
   pdl_wait();
@@ -587,11 +591,13 @@ static int check_common(const void* q, const void* out, const void* kpool, const
 
 extern "C" int ie_attention_mma_head_dim() { return HD; }
 
+// rows: rows of a work item's tile, 64 or 128 (the work list must have been cut accordingly)
 extern "C" int ie_attention_prefill(const void* q, void* out, const void* kpool, const void* vpool,
                                     const int* block_table, const int* q_start, const int* ctx_before,
                                     const int* work_req, const int* work_pair0, int q_stride, int out_stride,
                                     int table_stride, int n_work, int n_heads, int n_kv_heads, int hd, int page_size,
-                                    int window, float scale, cudaStream_t stream) {
+                                    int window, float scale, int rows, cudaStream_t stream) {
+  if (rows != 64 && rows != 128) return IE_BAD_SIZE;
   if (n_work <= 0) return IE_OK;
   int rc = check_common(q, out, kpool, vpool, q_stride, out_stride, n_heads, n_kv_heads, hd, page_size);
   if (rc) return rc;
@@ -603,11 +609,14 @@ extern "C" int ie_attention_prefill(const void* q, void* out, const void* kpool,
   const int smem = 2 * PF_STAGE_BYTES;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attention_prefill_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
-  return launch_k(attention_prefill_kernel, dim3(n_work, n_kv_heads), PF_THREADS, smem, stream, p);
+  if (rows == 128) return launch_k(attention_prefill_kernel<8>, dim3(n_work, n_kv_heads), 256, smem, stream, p);
+  return launch_k(attention_prefill_kernel<4>, dim3(n_work, n_kv_heads), 128, smem, stream, p);
 }
 
 // Scratch needed by the decode kernel, in 4-byte words: IE_DECODE_TICKET_WORDS tickets (one per

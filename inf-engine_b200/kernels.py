@@ -204,7 +204,7 @@ def attention_mma_library(head_dim: int):
     if lib is None:
         lib = load_library(f"attn_mma_hd{head_dim}", ["attention_mma.cu"], {"IE_HD": head_dim}, ["attention_noalloc.h"])
         P, I, F = c_void_p, c_int, c_float
-        lib.ie_attention_prefill.argtypes = [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P]
+        lib.ie_attention_prefill.argtypes = [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P]
         lib.ie_attention_prefill.restype = c_int
         lib.ie_attention_decode.argtypes = [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, I, P]
         lib.ie_attention_decode.restype = c_int
@@ -216,14 +216,15 @@ def attention_mma_library(head_dim: int):
 
 
 def attention_prefill_mma(q, out, kpool, vpool, block_table, q_start, ctx_before, work_req, work_pair0, n_work,
-                          n_heads, n_kv_heads, head_dim, page_size, window, scale) -> None:
-    """Causal paged attention for any mix of portions and single tokens; bfloat16; rows tiled by 64 pairs."""
+                          n_heads, n_kv_heads, head_dim, page_size, window, scale, rows: int = 64) -> None:
+    """Causal paged attention for any mix of portions and single tokens; bfloat16; the work list cuts each
+    request's (token, head-in-group) pairs into tiles of ``rows`` (64 or 128)."""
     assert q.dtype is torch.bfloat16 and q.stride(1) == 1 and out.stride(1) == 1
     lib = attention_mma_library(head_dim)
     _check(lib.ie_attention_prefill(_ptr(q), _ptr(out), _ptr(kpool), _ptr(vpool), _ptr(block_table), _ptr(q_start),
                                     _ptr(ctx_before), _ptr(work_req), _ptr(work_pair0), q.stride(0), out.stride(0),
                                     block_table.stride(0), n_work, n_heads, n_kv_heads, head_dim, page_size,
-                                    int(window or 0), float(scale), _stream()), "attention_prefill_mma")
+                                    int(window or 0), float(scale), rows, _stream()), "attention_prefill_mma")
 
 
 def attention_decode_scratch_floats(n_tokens, n_heads, n_splits, head_dim) -> int:

@@ -126,10 +126,11 @@ class PagedAttention:
                                              s.n_kv_heads, s.head_dim, ctx.page_size, s.window, self.scale,
                                              n_splits, split_keys)
             else:
-                work_req, work_pair0, n_work = ctx.attention_work(group, 64)
+                rows = 64      # tiles of 128 rows (8 warps) leave one block per SM at this register count: slower
+                work_req, work_pair0, n_work = ctx.attention_work(group, rows)
                 kernels.attention_prefill_mma(q, out, cache.k, cache.v, kvctx.block_table, ctx.q_start,
                                               ctx.ctx_before, work_req, work_pair0, n_work, s.n_heads,
-                                              s.n_kv_heads, s.head_dim, ctx.page_size, s.window, self.scale)
+                                              s.n_kv_heads, s.head_dim, ctx.page_size, s.window, self.scale, rows)
             return
         work_req, work_pair0, n_work = ctx.attention_work(group, 32)
         kernels.attention_general(q, out, cache.k, cache.v, kvctx.block_table, ctx.q_start, ctx.ctx_before,

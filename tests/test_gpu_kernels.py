@@ -400,18 +400,19 @@ MMA_CASES = [
 ]
 
 
+@pytest.mark.parametrize("rows", [64, 128])
 @pytest.mark.parametrize("case", MMA_CASES)
-def test_attention_prefill_tensor_cores(case):
+def test_attention_prefill_tensor_cores(case, rows):
     H, Hk, hd, ps, q_lens, ctx_before, window = case
     act = torch.bfloat16
     c = paged_case(act, H, Hk, hd, ps, q_lens, ctx_before, seed=3 * hd + len(q_lens))
     ref = paged_reference(c["q"], c["kd"], c["vd"], q_lens, ctx_before, H, Hk, hd, window)
-    req, pair0 = work_list(q_lens, H // Hk, 64)
+    req, pair0 = work_list(q_lens, H // Hk, rows)
     dev = lambda t: torch.as_tensor(t, dtype=torch.int32).to(DEV)
     out = torch.full((c["N"], H * hd), float("nan"), device=DEV, dtype=act)
     k().attention_prefill_mma(c["q"].to(DEV, act), out, c["kpool"].to(DEV, act), c["vpool"].to(DEV, act),
                               c["table"].to(DEV), dev(c["q_start"]), dev(ctx_before), dev(req), dev(pair0), len(req),
-                              H, Hk, hd, ps, window, hd ** -0.5)
+                              H, Hk, hd, ps, window, hd ** -0.5, rows)
     assert torch.allclose(out.float().cpu(), ref, **tol(act))
 
 
