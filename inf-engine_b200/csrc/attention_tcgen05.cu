@@ -1,0 +1,483 @@
+// Causal paged attention for prompt portions on the fifth-generation tensor cores (sm_100a), head size 64,
+// bfloat16: S = Q K^T and O += P V are tcgen05.mma instructions with their accumulators in tensor memory;
+// keys and values arrive page by page through TMA (cp.async.bulk.tensor over the cache pool); the online
+// softmax runs one thread per row straight out of tensor memory (tcgen05.ld), with no shuffles.
+//
+// Same mathematics and same work split as attention_mma.cu (engine/llama_attention.py:106-137 of the
+// reference): a block takes one (request, kv head) and a tile of 128 (token, head-in-group) rows, so that the
+// query heads of a group share every key tile; keys are walked in tiles of 128 in ascending order.
+//
+//   warp 0      TMA producer: for each key tile looks the pages up in the block table and issues one tensor
+//               copy per page for K and for V into a two-stage ring (a page that is not held or lies past the
+//               end is replaced by page 0: its keys are masked and its values get weight zero)
+//   warp 1      allocates tensor memory, issues  S = Q K^T  (4 MMAs of K = 16), later  O += P V  (8 MMAs; V is
+//               the MN-major operand: its rows are keys, as the cache stores them)
+//   warps 2-5   thread r owns row r: reads S from tensor memory, masks, keeps the running maximum and sum in
+//               float32, rescales O in tensor memory when the maximum moved, writes P as bfloat16 into shared
+//               memory in the 128-byte swizzle that the MMA expects
+//
+// Every wait on an mbarrier is bounded; on a timeout the block records an error word, stops, frees its tensor
+// memory and leaves.
+#include "common.cuh"
+#include <cuda.h>
+
+namespace {
+
+constexpr int HD = 64;
+constexpr int ROWS = 128;            // rows of a block's tile
+constexpr int KT = 128;              // keys of a tile
+constexpr int FA_THREADS = 192;
+constexpr unsigned FA_SPIN_LIMIT = 1u << 20;
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr uint32_t TILE_BYTES = 128 * 64 * 2;   // 16 KB: Q, one K stage, one V stage, half of P
+
+__device__ int g_fa_error = 0;
+
+struct FaParams {
+  const bf16* q;
+  bf16* out;
+  const int* block_table;
+  const int* q_start;
+  const int* ctx_before;
+  const int* work_req;
+  const int* work_pair0;
+  int q_stride, out_stride, table_stride;
+  int n_heads, n_kv_heads, page_size, page_shift, n_work;
+  float scale_log2;
+};
+
+__device__ __forceinline__ uint32_t saddr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void fa_mbar_init(uint32_t bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void fa_mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void fa_mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool fa_mbar_wait(uint32_t bar, uint32_t parity) {
+  for (unsigned i = 0; i < FA_SPIN_LIMIT; ++i) {
+    uint32_t ok;
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void fa_tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+               ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+// K-major operand: rows of 128 bytes, 128-byte swizzle, 8-row groups 1024 bytes apart
+__device__ __forceinline__ uint64_t desc_k_major(uint32_t addr) {
+  return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// MN-major operand of 64 contiguous elements (one swizzle atom wide): K advances by rows of 128 bytes,
+// groups of 8 rows 1024 bytes apart (stride offset); the leading offset (between 64-element groups) is not used
+__device__ __forceinline__ uint64_t desc_mn_major(uint32_t addr) {
+  return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)(TILE_BYTES >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) |
+         ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+__device__ __forceinline__ uint32_t idesc_f32_bf16(int m, int n, int b_mn_major) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn_major << 16) | ((uint32_t)(n >> 3) << 17) |
+         ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void fa_umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+               ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void fa_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void fa_tmem_ld32(uint32_t taddr, float (&r)[32]) {
+  uint32_t u[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]), "=r"(u[7]), "=r"(u[8]),
+        "=r"(u[9]), "=r"(u[10]), "=r"(u[11]), "=r"(u[12]), "=r"(u[13]), "=r"(u[14]), "=r"(u[15]), "=r"(u[16]),
+        "=r"(u[17]), "=r"(u[18]), "=r"(u[19]), "=r"(u[20]), "=r"(u[21]), "=r"(u[22]), "=r"(u[23]), "=r"(u[24]),
+        "=r"(u[25]), "=r"(u[26]), "=r"(u[27]), "=r"(u[28]), "=r"(u[29]), "=r"(u[30]), "=r"(u[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) r[i] = __uint_as_float(u[i]);
+}
+__device__ __forceinline__ void fa_tmem_st32(uint32_t taddr, const float (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      ::"r"(taddr), "r"(__float_as_uint(r[0])), "r"(__float_as_uint(r[1])), "r"(__float_as_uint(r[2])),
+        "r"(__float_as_uint(r[3])), "r"(__float_as_uint(r[4])), "r"(__float_as_uint(r[5])), "r"(__float_as_uint(r[6])),
+        "r"(__float_as_uint(r[7])), "r"(__float_as_uint(r[8])), "r"(__float_as_uint(r[9])), "r"(__float_as_uint(r[10])),
+        "r"(__float_as_uint(r[11])), "r"(__float_as_uint(r[12])), "r"(__float_as_uint(r[13])), "r"(__float_as_uint(r[14])),
+        "r"(__float_as_uint(r[15])), "r"(__float_as_uint(r[16])), "r"(__float_as_uint(r[17])), "r"(__float_as_uint(r[18])),
+        "r"(__float_as_uint(r[19])), "r"(__float_as_uint(r[20])), "r"(__float_as_uint(r[21])), "r"(__float_as_uint(r[22])),
+        "r"(__float_as_uint(r[23])), "r"(__float_as_uint(r[24])), "r"(__float_as_uint(r[25])), "r"(__float_as_uint(r[26])),
+        "r"(__float_as_uint(r[27])), "r"(__float_as_uint(r[28])), "r"(__float_as_uint(r[29])), "r"(__float_as_uint(r[30])),
+        "r"(__float_as_uint(r[31]))
+      : "memory");
+}
+__device__ __forceinline__ float fa_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t fa_pack(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+// byte offset of 16-byte chunk `chunk` (0..7) of row `row` in a tile of 128-byte rows under the 128-byte swizzle
+__device__ __forceinline__ uint32_t sw128(int row, int chunk) { return (uint32_t)(row * 128 + ((chunk ^ (row & 7)) << 4)); }
+
+__global__ void __launch_bounds__(FA_THREADS, 2) attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
+                                                                          const __grid_constant__ CUtensorMap map_v,
+                                                                          FaParams p) {
+  // seven tiles of 16 KB (Q, two stages of K, two of V, two halves of P), then the barriers
+  // (kv_full[2], kv_empty[2], s_full, p_ready, pv_done), the tensor-memory slot and the failure flag.
+  // No static shared memory and no padding: two blocks have to fit one SM.
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem_raw + 7 * TILE_BYTES);
+  uint32_t* tmem_slot_p = reinterpret_cast<uint32_t*>(smem_raw + 7 * TILE_BYTES + 64);
+  volatile int* failed_p = reinterpret_cast<volatile int*>(smem_raw + 7 * TILE_BYTES + 72);
+#define tmem_slot (*tmem_slot_p)
+#define failed (*failed_p)
+
+  pdl_trigger();
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t base = saddr(smem_raw);
+  if (base & 1023u) {              // the swizzled tiles need 1024-byte alignment: refuse rather than compute nonsense
+    if (tid == 0) atomicExch(&g_fa_error, 8);
+    return;
+  }
+  const uint32_t q_sm = base, k_sm = base + TILE_BYTES, v_sm = base + 3 * TILE_BYTES, p_sm = base + 5 * TILE_BYTES;
+  unsigned char* gen_base = smem_raw;
+  const uint32_t kv_full0 = saddr(&bars[0]), kv_empty0 = saddr(&bars[2]);
+  const uint32_t s_full = saddr(&bars[4]), p_ready = saddr(&bars[5]), pv_done = saddr(&bars[6]);
+
+  // heads are the fast index and the work list is walked from its end: in a long prompt the tiles with the
+  // most keys start first, and the short ones fill the tail of the launch
+  const int c = blockIdx.x % p.n_kv_heads;
+  const int w_id = p.n_work - 1 - blockIdx.x / p.n_kv_heads;
+  const int r_id = p.work_req[w_id];
+  const int pair0 = p.work_pair0[w_id];
+  const int group = p.n_heads / p.n_kv_heads;
+  const int q0 = p.q_start[r_id];
+  const int q_len = p.q_start[r_id + 1] - q0;
+  const int ctx = p.ctx_before[r_id];
+  const int n_pairs = q_len * group;
+  const int* table = p.block_table + (size_t)r_id * p.table_stride;
+  const int last_pair = min(pair0 + ROWS, n_pairs) - 1;
+  const int k_end = ctx + last_pair / group + 1;           // keys [0, k_end) matter to the block
+  const int n_tiles = (k_end + KT - 1) / KT;
+
+  if (tid == 0) {
+    failed = 0;
+    for (int s = 0; s < 2; ++s) {
+      fa_mbar_init(kv_full0 + 8 * s, 1);
+      fa_mbar_init(kv_empty0 + 8 * s, 1);
+    }
+    fa_mbar_init(s_full, 1);
+    fa_mbar_init(p_ready, 4);
+    fa_mbar_init(pv_done, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    // 256 columns: S in [0, 128), O in [128, 192)
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 256;" ::"r"(saddr(tmem_slot_p)) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = tmem_slot;
+  const uint32_t tmem_s = tmem, tmem_o = tmem + 128;
+
+  pdl_wait();
+
+  if (warp == 0) {
+    // ------------------------------------------------------------- producer
+    // lane i takes page i of a tile: the lookups of a tile run side by side (one after the other they cost
+    // a trip to L2 each), and every lane issues its own two copies
+    const int ps = p.page_size;
+    const int pages_per_tile = KT / ps;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int j = 0; j < n_tiles; ++j) {
+      const int s = j & 1;
+      int row = c * ps;                                     // page 0 stands in for what is not held
+      if (lane < pages_per_tile) {
+        const int kp = j * KT + lane * ps;
+        if (kp < k_end) {
+          const int page = __ldg(table + (kp >> p.page_shift));
+          if (page > 0) row = (page * p.n_kv_heads + c) * ps;
+        }
+      }
+      const uint32_t bar = kv_full0 + 8 * s;
+      if (lane == 0) {
+        ok = !failed && fa_mbar_wait(kv_empty0 + 8 * s, phase ^ 1);
+        if (ok) fa_mbar_expect_tx(bar, 2 * TILE_BYTES);
+        else { atomicExch(&g_fa_error, 1); failed = 1; }
+      }
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (!ok) break;
+      if (lane < pages_per_tile) {
+        fa_tma_load_2d(k_sm + s * TILE_BYTES + lane * ps * 128, &map_k, 0, row, bar);
+        fa_tma_load_2d(v_sm + s * TILE_BYTES + lane * ps * 128, &map_v, 0, row, bar);
+      }
+      if (s == 1) phase ^= 1;
+    }
+    if (!ok) for (int i = 0; i < 2048; ++i) __nanosleep(64);
+  } else if (warp == 1) {
+    // ------------------------------------------------------------- MMA issue
+    if (lane == 0) {
+      const uint32_t idesc_s = idesc_f32_bf16(ROWS, KT, 0), idesc_o = idesc_f32_bf16(ROWS, HD, 1);
+      // the queries are written to shared memory by the softmax warps: p_ready's phase 0 announces them
+      bool ok = !failed && fa_mbar_wait(p_ready, 0);
+      if (!ok) { atomicExch(&g_fa_error, 5); failed = 1; }
+      uint32_t kv_phase = 0;
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int s = j & 1;
+        if (failed || !fa_mbar_wait(kv_full0 + 8 * s, kv_phase)) { atomicExch(&g_fa_error, 2); failed = 1; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks)
+          fa_umma(tmem_s, desc_k_major(q_sm + ks * 32), desc_k_major(k_sm + s * TILE_BYTES + ks * 32), idesc_s, ks > 0 ? 1u : 0u);
+        fa_commit(s_full);
+        // P of this tile (phase j+1 of p_ready: phase 0 was the queries)
+        if (!fa_mbar_wait(p_ready, (uint32_t)(j + 1) & 1u)) { atomicExch(&g_fa_error, 3); failed = 1; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+        for (int kk = 0; kk < KT / 16; ++kk)
+          fa_umma(tmem_o, desc_k_major(p_sm + (kk >> 2) * TILE_BYTES + (kk & 3) * 32),
+                  desc_mn_major(v_sm + s * TILE_BYTES + kk * 2048), idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+        fa_commit(kv_empty0 + 8 * s);
+        fa_commit(pv_done);
+        if (s == 1) kv_phase ^= 1;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------- softmax, one thread per row
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;                    // row of the tile = TMEM lane
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    const int pr = pair0 + r;
+    const bool valid = pr < n_pairs;
+    const int t = valid ? pr / group : 0;
+    const int head = c * group + (valid ? pr - t * group : 0);
+    const int limit = valid ? ctx + t : 0x3fffffff;       // last visible key (rows past the end are not stored)
+
+    // queries -> shared memory in the MMA's swizzle
+    {
+      const bf16* src = p.q + (size_t)(q0 + t) * p.q_stride + head * HD;
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch) {
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (valid) v = *reinterpret_cast<const uint4*>(src + ch * 8);
+        *reinterpret_cast<uint4*>(gen_base + sw128(r, ch)) = v;
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> visible to the tensor core
+      __syncwarp();
+      if (lane == 0) fa_mbar_arrive(p_ready);
+    }
+
+    float m = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_tiles; ++j) {
+      ok = ok && !failed && fa_mbar_wait(s_full, (uint32_t)j & 1u);
+      if (!ok && lane == 0) { atomicExch(&g_fa_error, 4); failed = 1; }
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0 && !failed;
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int k0 = j * KT;
+      // a tile whose last key every row of the warp may see needs no mask
+      const bool interior = __all_sync(0xffffffffu, k0 + KT - 1 <= limit);
+      // scores of the row, 32 at a time, read twice from tensor memory (once for the maximum, once for
+      // the exponentials): 128 scores would not fit the registers beside everything else
+      float mx = -INFINITY;
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        float sc[32];
+        fa_tmem_ld32(tmem_s + lane_addr + q4 * 32, sc);
+        if (interior) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, sc[i]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (k0 + q4 * 32 + i <= limit) mx = fmaxf(mx, sc[i]);
+        }
+      }
+      // The maximum in use follows the true one only when that has grown by more than 2^8 (or is the
+      // first): until then the exponentials are at most 256, which neither bfloat16 nor the float32 sums
+      // mind, and O in tensor memory needs no rescaling.  The result is the same: numerator and
+      // denominator carry the same factor.
+      const float m_cand = fmaxf(m, mx * p.scale_log2);
+      const bool moves = __any_sync(0xffffffffu, m_cand - m > 8.f || (m == -INFINITY && m_cand > -INFINITY));
+      float corr = 1.f;
+      if (moves) {
+        corr = fa_exp2(m - (m_cand == -INFINITY ? 0.f : m_cand));    // 2^(-inf) = 0 the first time
+        m = m_cand;
+      }
+      const float ms = m == -INFINITY ? 0.f : m;
+      // O and the P buffer belong to the MMAs of the tile before until pv_done
+      if (j > 0) {
+        bool ok2 = fa_mbar_wait(pv_done, (uint32_t)(j - 1) & 1u);
+        if (!ok2 && lane == 0) { atomicExch(&g_fa_error, 6); failed = 1; }
+        ok = __shfl_sync(0xffffffffu, ok2 ? 1 : 0, 0) != 0 && !failed;
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (moves) {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            float o[32];
+            fa_tmem_ld32(tmem_o + lane_addr + h * 32, o);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] *= corr;
+            fa_tmem_st32(tmem_o + lane_addr + h * 32, o);
+          }
+          asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        }
+      }
+      float sum = 0.f;
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        float sc[32];
+        fa_tmem_ld32(tmem_s + lane_addr + q4 * 32, sc);
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          float e[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float x = fa_exp2(fmaf(sc[ch * 8 + i], p.scale_log2, -ms));
+            e[i] = (interior || k0 + q4 * 32 + ch * 8 + i <= limit) ? x : 0.f;
+            sum += e[i];
+          }
+          const int col = q4 * 32 + ch * 8;                // key index inside the tile
+          const uint4 v = make_uint4(fa_pack(e[0], e[1]), fa_pack(e[2], e[3]), fa_pack(e[4], e[5]), fa_pack(e[6], e[7]));
+          *reinterpret_cast<uint4*>(gen_base + 5 * TILE_BYTES + (col >> 6) * TILE_BYTES + sw128(r, (col & 63) >> 3)) = v;
+        }
+      }
+      l = l * corr + sum;
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) fa_mbar_arrive(p_ready);
+    }
+    if (ok) {
+      bool ok2 = fa_mbar_wait(pv_done, (uint32_t)(n_tiles - 1) & 1u);
+      if (!ok2 && lane == 0) { atomicExch(&g_fa_error, 7); failed = 1; }
+      ok = __shfl_sync(0xffffffffu, ok2 ? 1 : 0, 0) != 0 && !failed;
+    }
+    if (ok) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      bf16* dst = p.out + (size_t)(q0 + t) * p.out_stride + head * HD;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        float o[32];
+        fa_tmem_ld32(tmem_o + lane_addr + h * 32, o);
+        if (valid) {
+#pragma unroll
+          for (int ch = 0; ch < 4; ++ch) {
+            const uint4 v = make_uint4(fa_pack(o[ch * 8] * inv, o[ch * 8 + 1] * inv), fa_pack(o[ch * 8 + 2] * inv, o[ch * 8 + 3] * inv),
+                                       fa_pack(o[ch * 8 + 4] * inv, o[ch * 8 + 5] * inv), fa_pack(o[ch * 8 + 6] * inv, o[ch * 8 + 7] * inv));
+            *reinterpret_cast<uint4*>(dst + h * 32 + ch * 8) = v;
+          }
+        }
+      }
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 256;" ::"r"(tmem) : "memory");
+  }
+#undef tmem_slot
+#undef failed
+}
+
+typedef CUresult (*FaEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static FaEncodeFn fa_encode_fn() {
+  static FaEncodeFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = (FaEncodeFn)ptr;
+  }
+  return fn;
+}
+
+// the pool as a matrix [pool_rows, 64] of bfloat16 (a row is one key of one head); boxes of one page
+static int fa_make_map(CUtensorMap* map, const void* base, long long pool_rows, int page_size) {
+  FaEncodeFn fn = fa_encode_fn();
+  if (!fn) return IE_BAD_SIZE;
+  const cuuint64_t dims[2] = {(cuuint64_t)HD, (cuuint64_t)pool_rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)HD * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)HD, (cuuint32_t)page_size};
+  const cuuint32_t elem[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? IE_OK : IE_BAD_ALIGN;
+}
+
+}  // namespace
+
+extern "C" int ie_attention_tcgen05_error() {
+  int v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, g_fa_error, sizeof(int)) != cudaSuccess) return -1;
+  if (v) cudaMemcpyToSymbol(g_fa_error, &zero, sizeof(int));
+  return v;
+}
+
+// 1 if the kernel takes the geometry: head size 64, pages of 8..128 keys that divide 128, a power of two
+extern "C" int ie_attention_tcgen05_supports(int hd, int page_size, int window) {
+  if (hd != HD || window > 0) return 0;
+  if (page_size < 8 || page_size > 128 || (page_size & (page_size - 1)) || 128 % page_size) return 0;
+  return 1;
+}
+
+// The work list cuts each request's (token, head-in-group) rows into tiles of 128; n_pool_pages is the
+// number of pages of kpool / vpool ([pages, kv_heads, page_size, 64]).
+extern "C" int ie_attention_tcgen05(const void* q, void* out, const void* kpool, const void* vpool,
+                                    const int* block_table, const int* q_start, const int* ctx_before,
+                                    const int* work_req, const int* work_pair0, int q_stride, int out_stride,
+                                    int table_stride, int n_work, int n_heads, int n_kv_heads, int hd, int page_size,
+                                    int n_pool_pages, float scale, cudaStream_t stream) {
+  if (n_work <= 0) return IE_OK;
+  if (!ie_attention_tcgen05_supports(hd, page_size, 0)) return IE_BAD_SIZE;
+  if (n_kv_heads <= 0 || n_heads % n_kv_heads || n_pool_pages <= 0) return IE_BAD_SIZE;
+  if (((uintptr_t)q | (uintptr_t)out | (uintptr_t)kpool | (uintptr_t)vpool) & 15) return IE_BAD_ALIGN;
+  if ((q_stride | out_stride) & 7) return IE_BAD_ALIGN;
+  CUtensorMap mk, mv;
+  const long long rows = (long long)n_pool_pages * n_kv_heads * page_size;
+  int rc = fa_make_map(&mk, kpool, rows, page_size);
+  if (rc) return rc;
+  rc = fa_make_map(&mv, vpool, rows, page_size);
+  if (rc) return rc;
+  FaParams p;
+  p.q = (const bf16*)q; p.out = (bf16*)out; p.block_table = block_table; p.q_start = q_start; p.ctx_before = ctx_before;
+  p.work_req = work_req; p.work_pair0 = work_pair0; p.q_stride = q_stride; p.out_stride = out_stride;
+  p.table_stride = table_stride; p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.page_size = page_size;
+  p.n_work = n_work;
+  p.page_shift = 0;
+  while ((1 << p.page_shift) < page_size) ++p.page_shift;
+  p.scale_log2 = scale * LOG2E;
+  const size_t smem = 7 * TILE_BYTES + 128;
+  static bool attr = false;
+  if (!attr) {
+    cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    attr = true;
+  }
+  return launch_k(attention_tcgen05_kernel, dim3((unsigned)((long long)n_work * n_kv_heads)), FA_THREADS, smem, stream, mk, mv, p);
+}

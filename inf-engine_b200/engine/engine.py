@@ -16,6 +16,7 @@ from pathlib import Path
 
 import torch
 
+from .. import kernels
 from ..config.registry import detect_config, get_preset
 from ..sampling.sampler import Sampler, SamplingConfig, pack_rows, request_key
 from ..weights.random_init import write_random_model
@@ -186,6 +187,7 @@ class Engine:
         refused = [r for r in requests if not self.submit(r)]
         while self.has_work:
             self.step(time.perf_counter())
+        kernels.check_device_errors()
         out = {r.req_id: r.generated for r in self.completed}
         out.update({r.req_id: [] for r in refused})
         return out
@@ -201,6 +203,7 @@ class Engine:
         while req not in self.completed:
             self.step(time.perf_counter())
         self.completed.remove(req)
+        kernels.check_device_errors()
         return req.generated
 
 

@@ -17,6 +17,8 @@ The graph also holds the sampling kernel, so a step returns token ids.
 
 from __future__ import annotations
 
+import gc
+
 import numpy as np
 import torch
 
@@ -185,8 +187,18 @@ class DecodeGraphs:
                 from .. import kernels
                 g = torch.cuda.CUDAGraph()
                 n0 = kernels.LAUNCHES
-                with torch.cuda.graph(g):
-                    b.logits = self._forward(b)
+                # The collector must not run inside the capture: garbage that owns CUDA objects (an engine
+                # dropped earlier, with graphs of its own) would free them there, which a capture forbids and
+                # which invalidates it.  So collect before, and hold the collector until the capture ends.
+                gc.collect()
+                gc_was_on = gc.isenabled()
+                gc.disable()
+                try:
+                    with torch.cuda.graph(g, capture_error_mode="thread_local"):
+                        b.logits = self._forward(b)
+                finally:
+                    if gc_was_on:
+                        gc.enable()
                 b.n_kernels = kernels.LAUNCHES - n0
                 b.graph, b.generation = g, self.generation
                 self.captures += 1

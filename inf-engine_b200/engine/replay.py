@@ -42,6 +42,7 @@ def main(argv=None) -> int:
 
     import torch
 
+    from .. import kernels
     from .batch import StepEntry
     from .runner import ModelRunner
 
@@ -73,6 +74,7 @@ def main(argv=None) -> int:
                 f.write(data.tobytes())
         else:
             torch.cuda.synchronize()
+        kernels.check_device_errors()
         for rid in rec.get("end", []):
             if runner.is_open(rid):
                 runner.close(rid)

@@ -359,11 +359,63 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epi: str = "
 
     ``epi``: "bf16" store, "residual" adds into the float32 ``c``, "silu_mul" takes w's rows as alternating
     gate/up and writes silu(gate)*up, half as wide."""
-    flush = globals().get("flush_stream_chain")
-    if flush:
-        flush()
     m, k = a.shape
     n = w.shape[0]
     assert a.dtype is torch.bfloat16 and w.dtype is torch.bfloat16 and a.stride(1) == 1 and w.stride(1) == 1
     _check(tcgen05_library().ie_gemm_tcgen05(_ptr(a), _ptr(w), _ptr(c), m, n, k, a.stride(0), w.stride(0), c.stride(0),
                                              _EPI[epi], bn, sm_count(), _stream()), f"gemm_tcgen05(m={m}, n={n}, k={k}, {epi})")
+
+
+# ------------------------------------------- prompt-portion attention on tcgen05 (head size 64)
+_fa5_lib = None
+
+
+def attention_tcgen05_library():
+    global _fa5_lib
+    if _fa5_lib is None:
+        lib = load_library("attn_tcgen05", ["attention_tcgen05.cu"])
+        P, I = c_void_p, c_int
+        lib.ie_attention_tcgen05.argtypes = [P] * 9 + [I] * 9 + [c_float, P]
+        lib.ie_attention_tcgen05.restype = c_int
+        lib.ie_attention_tcgen05_supports.argtypes = [I, I, I]
+        lib.ie_attention_tcgen05_supports.restype = c_int
+        lib.ie_attention_tcgen05_error.restype = c_int
+        _fa5_lib = lib
+    return _fa5_lib
+
+
+def attention_tcgen05_supports(head_dim: int, page_size: int, window) -> bool:
+    return bool(attention_tcgen05_library().ie_attention_tcgen05_supports(head_dim, page_size, int(window or 0)))
+
+
+def attention_tcgen05_error() -> int:
+    """Reads and clears the error word that a timed-out wait of the kernel leaves (0: none)."""
+    return int(attention_tcgen05_library().ie_attention_tcgen05_error())
+
+
+def attention_tcgen05(q, out, kpool, vpool, block_table, q_start, ctx_before, work_req, work_pair0, n_work,
+                      n_heads, n_kv_heads, head_dim, page_size, scale) -> None:
+    """Causal paged attention for prompt portions with tcgen05 tensor cores; bfloat16, head size 64; the
+    work list cuts each request's (token, head-in-group) rows into tiles of 128.  ``kpool``/``vpool`` are
+    one layer's pages, [pages, kv_heads, page_size, 64], contiguous."""
+    assert q.dtype is torch.bfloat16 and q.stride(1) == 1 and out.stride(1) == 1
+    assert kpool.is_contiguous() and vpool.is_contiguous() and kpool.dim() == 4
+    _check(attention_tcgen05_library().ie_attention_tcgen05(
+        _ptr(q), _ptr(out), _ptr(kpool), _ptr(vpool), _ptr(block_table), _ptr(q_start), _ptr(ctx_before),
+        _ptr(work_req), _ptr(work_pair0), q.stride(0), out.stride(0), block_table.stride(0), n_work, n_heads,
+        n_kv_heads, head_dim, page_size, kpool.shape[0], float(scale), _stream()), "attention_tcgen05")
+
+
+def check_device_errors() -> None:
+    """Reads the error words of the kernels that wait on barriers (a wait that ran out records a code and the
+    kernel leaves early) and raises if any is set.  It synchronises the device, so it belongs where the
+    engine is idle anyway: after a replayed step, at the end of a generation."""
+    found = []
+    if _stream_lib is not None and (e := stream_error()):
+        found.append(f"streaming product: code {e}")
+    if _tc_lib is not None and (e := gemm_tcgen05_error()):
+        found.append(f"tcgen05 product: code {e}")
+    if _fa5_lib is not None and (e := attention_tcgen05_error()):
+        found.append(f"tcgen05 attention: code {e}")
+    if found:
+        raise KernelError("a kernel gave up a bounded wait; its results are not valid (" + "; ".join(found) + ")")

@@ -125,6 +125,13 @@ class PagedAttention:
                                              ctx.ctx_before, scratch, ctx.n_requests, ctx.n_tokens, s.n_heads,
                                              s.n_kv_heads, s.head_dim, ctx.page_size, s.window, self.scale,
                                              n_splits, split_keys)
+            elif (ctx.max_q_len * group >= TCGEN05_MIN_ROWS
+                  and kernels.attention_tcgen05_supports(s.head_dim, ctx.page_size, s.window)):
+                # prompt portions: tcgen05 tensor cores, tiles of 128 rows by 128 keys
+                work_req, work_pair0, n_work = ctx.attention_work(group, 128)
+                kernels.attention_tcgen05(q, out, cache.k, cache.v, kvctx.block_table, ctx.q_start, ctx.ctx_before,
+                                          work_req, work_pair0, n_work, s.n_heads, s.n_kv_heads, s.head_dim,
+                                          ctx.page_size, self.scale)
             else:
                 rows = 64      # tiles of 128 rows (8 warps) leave one block per SM at this register count: slower
                 work_req, work_pair0, n_work = ctx.attention_work(group, rows)
@@ -136,6 +143,10 @@ class PagedAttention:
         kernels.attention_general(q, out, cache.k, cache.v, kvctx.block_table, ctx.q_start, ctx.ctx_before,
                                   work_req, work_pair0, n_work, s.n_heads, s.n_kv_heads, s.head_dim,
                                   ctx.page_size, s.window, self.scale)
+
+
+# fewer (token, head-in-group) rows than this in every request: the 64-row mma.sync tiles waste less
+TCGEN05_MIN_ROWS = 128
 
 
 def decode_splits(keys_cap: int, n_streams: int, resident_warps: int = 888) -> tuple[int, int]:
