@@ -37,9 +37,10 @@ struct MmaAttnParams {
   const int* ctx_before;
   const int* work_req;
   const int* work_pair0;
-  float* part_o;   // decode: [n_tokens*n_heads, n_splits, HD]
-  float* part_ml;  // decode: [n_tokens*n_heads, n_splits, 2]
+  float* part_o;   // decode: [n_tokens*n_heads, n_blocks, HD]
+  float* part_ml;  // decode: [n_tokens*n_heads, n_blocks, 2]
   int* tickets;    // decode: [n_requests * n_kv_heads], zero between launches
+  int n_blocks;    // decode: blocks per (request, kv head) = partial results per row
   int q_stride, out_stride, table_stride;
   int n_heads, n_kv_heads, page_size, window;
   int page_shift;  // log2(page_size) when it is a power of two, else -1
@@ -350,20 +351,24 @@ __global__ void __launch_bounds__(PF_WARPS * 32) attention_prefill_kernel(MmaAtt
 }
 
 // -------------------------------------------------------------------- decode
-// One warp per split of the keys: block (x, kv head, request) is one warp, so that a
-// whole step's blocks are resident at once and none waits for a slot.  A request brings at most 16 rows (q_len * group <= 16).
-// A warp keeps up to DC_STAGES key tiles in flight at once (a decode step is a
-// matter of latency: few bytes per warp, all of them wanted as early as
-// possible), writes its unnormalised output, maximum and sum, and takes a ticket
-// of its (request, kv head); the warp that takes the last ticket adds the splits
-// up in ascending order, so the result does not depend on which warp that is.
-constexpr int DC_WARPS = 1;
+// A request brings at most 16 rows (q_len * group <= 16).  Block (x, kv head, request) has DC_WARPS warps,
+// each with one split of the keys: consecutive splits, so that a block covers DC_WARPS * split_keys keys.
+// A warp keeps up to DC_STAGES key tiles in flight (a decode step is a matter of latency: few bytes per
+// warp, all of them wanted as early as possible).  The warps of a block add their partial results up
+// through shared memory, in ascending order of the splits.  A (request, kv head) that one block covers
+// is finished there; otherwise each block writes one partial result and takes a ticket, and the block
+// that takes the last ticket adds the blocks up, again in ascending order: the result does not depend
+// on which block that is.
+#ifndef IE_DC_WARPS
+#define IE_DC_WARPS (HD <= 64 ? 6 : 3)   // 96 KB of tiles per block: two blocks share an SM
+#endif
+constexpr int DC_WARPS = IE_DC_WARPS;
 constexpr int DC_THREADS = DC_WARPS * 32;
 #ifndef IE_DC_KT
 #define IE_DC_KT 32
 #endif
 #ifndef IE_DC_STAGES
-#define IE_DC_STAGES 4
+#define IE_DC_STAGES 2
 #endif
 constexpr int DC_KT = IE_DC_KT;
 constexpr int DC_STAGES = IE_DC_STAGES;
@@ -408,9 +413,12 @@ __global__ void __launch_bounds__(DC_THREADS) attention_decode_kernel(MmaAttnPar
   const int k_lo = max(split * p.split_keys, lo_all);
   const int k_hi = min((split + 1) * p.split_keys, max_lim + 1);
   const bool has_work = split >= s_first && split <= s_last && split < p.n_splits && n_pairs > 0;
+  // blocks that hold at least one such split
+  const int b_first = s_first / DC_WARPS, b_last = s_last / DC_WARPS;
+  const int n_active_blocks = b_last - b_first + 1;
   // A block without keys leaves at once and frees its slot.  It need not wait for the kernel ahead:
-  // split 0 of every (request, kv head) always has keys and waits, so this kernel still ends after it.
-  if (!has_work) return;
+  // block 0 of every (request, kv head) always has keys and waits, so this kernel still ends after it.
+  if ((int)blockIdx.x < b_first || (int)blockIdx.x > b_last || n_pairs <= 0) return;
 
   float o[NT_O][4];
 #pragma unroll
@@ -420,7 +428,7 @@ __global__ void __launch_bounds__(DC_THREADS) attention_decode_kernel(MmaAttnPar
   // Lengths, block tables and the keys of earlier steps are not written by this step's kernels:
   // tiles of old keys only are fetched before the kernel ahead has finished.
   const uint32_t base = smem_u32(smem) + warp * DC_WARP_BYTES;
-  const int n_tiles = (k_hi - k_lo + DC_KT - 1) / DC_KT;
+  const int n_tiles = has_work ? (k_hi - k_lo + DC_KT - 1) / DC_KT : 0;
   const int n_first = min(n_tiles, DC_STAGES);
   int issued = 0;
   for (; issued < n_first && k_lo + (issued + 1) * DC_KT <= ctx; ++issued) {
@@ -429,12 +437,12 @@ __global__ void __launch_bounds__(DC_THREADS) attention_decode_kernel(MmaAttnPar
     cp_async_commit();
   }
   pdl_wait();
-  for (; issued < n_first; ++issued) {
-    const uint32_t sb = base + issued * DC_STAGE_BYTES;
-    load_kv_tile<DC_KT, 32>(p, table, c, k_lo + issued * DC_KT, k_hi, sb, sb + DC_KT * HD * 2, lane);
-    cp_async_commit();
-  }
-  {
+  if (has_work) {
+    for (; issued < n_first; ++issued) {
+      const uint32_t sb = base + issued * DC_STAGE_BYTES;
+      load_kv_tile<DC_KT, 32>(p, table, c, k_lo + issued * DC_KT, k_hi, sb, sb + DC_KT * HD * 2, lane);
+      cp_async_commit();
+    }
     const bf16* qr0 = v0 ? p.q + (size_t)(q0 + t0) * p.q_stride + (c * group + (pr0 - t0 * group)) * HD : nullptr;
     const bf16* qr1 = v1 ? p.q + (size_t)(q0 + t1) * p.q_stride + (c * group + (pr1 - t1 * group)) * HD : nullptr;
     uint32_t qf[KSTEPS][4];
@@ -458,106 +466,99 @@ __global__ void __launch_bounds__(DC_THREADS) attention_decode_kernel(MmaAttnPar
         ++issued;
       }
     }
-  }
-  l[0] += __shfl_xor_sync(0xffffffffu, l[0], 1);
-  l[0] += __shfl_xor_sync(0xffffffffu, l[0], 2);
-  l[1] += __shfl_xor_sync(0xffffffffu, l[1], 1);
-  l[1] += __shfl_xor_sync(0xffffffffu, l[1], 2);
-  const int col = (lane & 3) * 2;
-  if (v0) {
-    const size_t row = (size_t)(q0 + t0) * p.n_heads + c * group + (pr0 - t0 * group);
-    float* po = p.part_o + (row * p.n_splits + split) * HD;
-#pragma unroll
-    for (int i = 0; i < NT_O; ++i) *reinterpret_cast<float2*>(po + i * 8 + col) = make_float2(o[i][0], o[i][1]);
-    if ((lane & 3) == 0) *reinterpret_cast<float2*>(p.part_ml + (row * p.n_splits + split) * 2) = make_float2(m[0], l[0]);
-  }
-  if (v1) {
-    const size_t row = (size_t)(q0 + t1) * p.n_heads + c * group + (pr1 - t1 * group);
-    float* po = p.part_o + (row * p.n_splits + split) * HD;
-#pragma unroll
-    for (int i = 0; i < NT_O; ++i) *reinterpret_cast<float2*>(po + i * 8 + col) = make_float2(o[i][2], o[i][3]);
-    if ((lane & 3) == 0) *reinterpret_cast<float2*>(p.part_ml + (row * p.n_splits + split) * 2) = make_float2(m[1], l[1]);
+    l[0] += __shfl_xor_sync(0xffffffffu, l[0], 1);
+    l[0] += __shfl_xor_sync(0xffffffffu, l[0], 2);
+    l[1] += __shfl_xor_sync(0xffffffffu, l[1], 1);
+    l[1] += __shfl_xor_sync(0xffffffffu, l[1], 2);
   }
 
-  // ticket of this (request, kv head): the last warp to arrive merges
+  // ---- the warps of the block: partial results into shared memory (each warp into its own tile space,
+  // which it has finished reading), then every thread adds one (row, dim) up over the warps
+  float* w_o = reinterpret_cast<float*>(smem + warp * DC_WARP_BYTES);     // [16][HD]
+  float* w_ml = w_o + 16 * HD;                                            // [16][2]
+  static_assert(DC_WARP_BYTES >= (16 * HD + 32) * 4, "a warp's tile space holds its partial result");
+  {
+    const int col = (lane & 3) * 2;
+#pragma unroll
+    for (int i = 0; i < NT_O; ++i) {
+      *reinterpret_cast<float2*>(w_o + pr0 * HD + i * 8 + col) = make_float2(o[i][0], o[i][1]);
+      *reinterpret_cast<float2*>(w_o + pr1 * HD + i * 8 + col) = make_float2(o[i][2], o[i][3]);
+    }
+    if ((lane & 3) == 0) {
+      *reinterpret_cast<float2*>(w_ml + pr0 * 2) = make_float2(m[0], l[0]);   // a warp without keys: (-inf, 0)
+      *reinterpret_cast<float2*>(w_ml + pr1 * 2) = make_float2(m[1], l[1]);
+    }
+  }
+  __syncthreads();
+  const int n_out = n_pairs * HD;
+  const int blk = (int)blockIdx.x - b_first;
+  for (int idx = threadIdx.x; idx < n_out; idx += DC_THREADS) {
+    const int pr = idx / HD, d = idx - pr * HD;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < DC_WARPS; ++w) M = fmaxf(M, *(reinterpret_cast<const float*>(smem + w * DC_WARP_BYTES) + 16 * HD + pr * 2));
+    float acc = 0.f, den = 0.f;
+#pragma unroll
+    for (int w = 0; w < DC_WARPS; ++w) {
+      const float* wo = reinterpret_cast<const float*>(smem + w * DC_WARP_BYTES);
+      const float mw = wo[16 * HD + pr * 2], lw = wo[16 * HD + pr * 2 + 1];
+      const float f = (mw > -INFINITY) ? fast_exp2(mw - M) : 0.f;
+      acc += f * wo[pr * HD + d];
+      den += f * lw;
+    }
+    const int t = pr / group;
+    const size_t row = (size_t)(q0 + t) * p.n_heads + c * group + (pr - t * group);
+    if (n_active_blocks == 1) {
+      const float inv = den > 0.f ? 1.f / den : 0.f;
+      p.out[(size_t)(q0 + t) * p.out_stride + (c * group + (pr - t * group)) * HD + d] = __float2bfloat16(acc * inv);
+    } else {
+      p.part_o[(row * p.n_blocks + blk) * HD + d] = acc;
+      if (d == 0) *reinterpret_cast<float2*>(p.part_ml + (row * p.n_blocks + blk) * 2) = make_float2(M, den);
+    }
+  }
+  if (n_active_blocks == 1) return;
+
+  // ---- ticket of this (request, kv head): the last block to arrive adds the blocks up
+  __shared__ int s_ticket;
   __threadfence();
-  __syncwarp();
+  __syncthreads();
   int* ticket = p.tickets + r_id * p.n_kv_heads + c;
-  int mine = 0;
-  if (lane == 0) mine = atomicAdd(ticket, 1);
-  mine = __shfl_sync(0xffffffffu, mine, 0);
-  if (mine != n_active - 1) return;
+  if (threadIdx.x == 0) s_ticket = atomicAdd(ticket, 1);
+  __syncthreads();
+  if (s_ticket != n_active_blocks - 1) return;
   __threadfence();
-  if (lane == 0) *ticket = 0;   // ready for the next launch
+  if (threadIdx.x == 0) *ticket = 0;   // ready for the next launch
 
-  // out[row] = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M), splits in ascending order.
-  // Lane L owns dims [L*DPL, L*DPL+DPL) of a row.  The partials come from L2 (other SMs wrote them);
-  // four rows are merged side by side so that their loads are in flight together, eight splits at a time.
-  constexpr int DPL = HD / 32;
-  constexpr int RG = 4;   // rows merged together
-  for (int pg = 0; pg < n_pairs; pg += RG) {
-    const float2* ml[RG];
-    const float* po[RG];
-    bf16* dst[RG];
-    float M[RG], den[RG], acc[RG][DPL];
+  // out[row] = sum_b o_b 2^(m_b - M) / sum_b l_b 2^(m_b - M), blocks in ascending order; the partials
+  // come from L2 (other SMs wrote them), eight blocks' loads in flight together
+  for (int idx = threadIdx.x; idx < n_out; idx += DC_THREADS) {
+    const int pr = idx / HD, d = idx - pr * HD;
+    const int t = pr / group;
+    const size_t row = (size_t)(q0 + t) * p.n_heads + c * group + (pr - t * group);
+    const float2* ml = reinterpret_cast<const float2*>(p.part_ml + row * p.n_blocks * 2);
+    const float* po = p.part_o + row * p.n_blocks * HD + d;
+    float M = -INFINITY;
+    for (int j = 0; j < n_active_blocks; ++j) M = fmaxf(M, __ldcg(ml + j).x);
+    float acc = 0.f, den = 0.f;
+    for (int j0 = 0; j0 < n_active_blocks; j0 += 8) {
+      float2 mlv[8];
+      float v[8];
 #pragma unroll
-    for (int r = 0; r < RG; ++r) {
-      const int pr = min(pg + r, n_pairs - 1);   // rows past the end repeat the last one and are not stored
-      const int t = pr / group;
-      const size_t row = (size_t)(q0 + t) * p.n_heads + c * group + (pr - t * group);
-      ml[r] = reinterpret_cast<const float2*>(p.part_ml + (row * p.n_splits + s_first) * 2);
-      po[r] = p.part_o + (row * p.n_splits + s_first) * HD + lane * DPL;
-      dst[r] = p.out + (size_t)(q0 + t) * p.out_stride + (c * group + (pr - t * group)) * HD + lane * DPL;
-      M[r] = -INFINITY;
-      den[r] = 0.f;
-#pragma unroll
-      for (int d = 0; d < DPL; ++d) acc[r][d] = 0.f;
-    }
-    for (int j = lane; j < n_active; j += 32) {
-#pragma unroll
-      for (int r = 0; r < RG; ++r) M[r] = fmaxf(M[r], __ldcg(ml[r] + j).x);
-    }
-#pragma unroll
-    for (int r = 0; r < RG; ++r) M[r] = warp_max(M[r]);
-    for (int j0 = 0; j0 < n_active; j0 += 8) {
-      float2 mlv[RG][8];
-      float v[RG][8][DPL];
-#pragma unroll
-      for (int r = 0; r < RG; ++r) {
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-          const int j = min(j0 + u, n_active - 1);   // the tail repeats the last split and gets weight 0
-          mlv[r][u] = __ldcg(ml[r] + j);
-          if (DPL == 2) {
-            const float2 x = __ldcg(reinterpret_cast<const float2*>(po[r] + (size_t)j * HD));
-            v[r][u][0] = x.x; v[r][u][1 % DPL] = x.y;
-          } else {
-            const float4 x = __ldcg(reinterpret_cast<const float4*>(po[r] + (size_t)j * HD));
-            v[r][u][0] = x.x; v[r][u][1 % DPL] = x.y; v[r][u][2 % DPL] = x.z; v[r][u][3 % DPL] = x.w;
-          }
-        }
+      for (int u = 0; u < 8; ++u) {
+        const int j = min(j0 + u, n_active_blocks - 1);   // the tail repeats the last block and gets weight 0
+        mlv[u] = __ldcg(ml + j);
+        v[u] = __ldcg(po + (size_t)j * HD);
       }
 #pragma unroll
-      for (int r = 0; r < RG; ++r) {
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-          const bool real = j0 + u < n_active && mlv[r][u].x > -INFINITY && M[r] > -INFINITY;
-          const float w = real ? fast_exp2(mlv[r][u].x - M[r]) : 0.f;
-          den[r] += w * mlv[r][u].y;
-#pragma unroll
-          for (int d = 0; d < DPL; ++d) acc[r][d] += w * v[r][u][d];
-        }
+      for (int u = 0; u < 8; ++u) {
+        const bool real = j0 + u < n_active_blocks && mlv[u].x > -INFINITY;
+        const float f = real ? fast_exp2(mlv[u].x - M) : 0.f;
+        acc += f * v[u];
+        den += f * mlv[u].y;
       }
     }
-#pragma unroll
-    for (int r = 0; r < RG; ++r) {
-      if (pg + r < n_pairs) {
-        const float inv = den[r] > 0.f ? 1.f / den[r] : 0.f;
-#pragma unroll
-        for (int d = 0; d < DPL; d += 2)
-          *reinterpret_cast<uint32_t*>(dst[r] + d) = pack_bf16(acc[r][d] * inv, acc[r][d + 1] * inv);
-      }
-    }
+    const float inv = den > 0.f ? 1.f / den : 0.f;
+    p.out[(size_t)(q0 + t) * p.out_stride + (c * group + (pr - t * group)) * HD + d] = __float2bfloat16(acc * inv);
   }
 }
 
@@ -569,7 +570,7 @@ static void fill(MmaAttnParams& p, const void* q, void* out, const void* kpool, 
   p.work_req = nullptr; p.work_pair0 = nullptr; p.part_o = nullptr; p.part_ml = nullptr; p.tickets = nullptr;
   p.q_stride = q_stride; p.out_stride = out_stride; p.table_stride = table_stride;
   p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.page_size = page_size; p.window = window;
-  p.n_splits = 0; p.split_keys = 0; p.scale_log2 = scale * LOG2E;
+  p.n_splits = 0; p.split_keys = 0; p.n_blocks = 0; p.scale_log2 = scale * LOG2E;
   p.page_shift = -1;
   if ((page_size & (page_size - 1)) == 0)
     for (int b = 0; b < 31; ++b)
@@ -624,10 +625,13 @@ extern "C" int ie_attention_prefill(const void* q, void* out, const void* kpool,
 // must be zero before the first launch on a piece of scratch; every launch leaves them zero
 // again, whatever the batch, because they always sit in the same place.  The rest may hold anything.
 #define IE_DECODE_TICKET_WORDS 4096
-#define IE_DECODE_MAX_ACTIVE_SPLITS 64
+#define IE_DECODE_MAX_BLOCKS 64
 extern "C" long long ie_attention_decode_scratch_floats(int n_tokens, int n_heads, int n_splits) {
   return IE_DECODE_TICKET_WORDS + (long long)n_tokens * n_heads * n_splits * (HD + 2);
 }
+// Warps (= splits) of a decode block; a launch takes at most IE_DECODE_MAX_BLOCKS blocks per (request, kv head).
+extern "C" int ie_attention_decode_warps() { return DC_WARPS; }
+extern "C" int ie_attention_decode_max_blocks() { return IE_DECODE_MAX_BLOCKS; }
 // Words at the start of that scratch that must be zero before its first use.
 extern "C" long long ie_attention_decode_ticket_words() { return IE_DECODE_TICKET_WORDS; }
 
@@ -646,10 +650,12 @@ extern "C" int ie_attention_decode(const void* q, void* out, const void* kpool, 
        n_kv_heads, page_size, window, scale);
   p.n_splits = n_splits;
   p.split_keys = split_keys;
-  if ((long long)n_requests * n_kv_heads > IE_DECODE_TICKET_WORDS || n_splits > IE_DECODE_MAX_ACTIVE_SPLITS) return IE_BAD_SIZE;
+  if ((long long)n_requests * n_kv_heads > IE_DECODE_TICKET_WORDS) return IE_BAD_SIZE;
+  p.n_blocks = (n_splits + DC_WARPS - 1) / DC_WARPS;
+  if (p.n_blocks > IE_DECODE_MAX_BLOCKS) return IE_BAD_SIZE;
   p.tickets = reinterpret_cast<int*>(scratch);
   p.part_o = scratch + IE_DECODE_TICKET_WORDS;
-  p.part_ml = p.part_o + (size_t)n_tokens * n_heads * n_splits * HD;
+  p.part_ml = p.part_o + (size_t)n_tokens * n_heads * p.n_blocks * HD;
   const int smem = DC_WARPS * DC_WARP_BYTES;
   static bool attr_set = false;
   if (!attr_set) {
@@ -657,7 +663,7 @@ extern "C" int ie_attention_decode(const void* q, void* out, const void* kpool, 
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
-  dim3 grid((n_splits + DC_WARPS - 1) / DC_WARPS, n_kv_heads, n_requests);
+  dim3 grid(p.n_blocks, n_kv_heads, n_requests);
   return launch_k(attention_decode_kernel, grid, DC_THREADS, smem, stream, p);
 }
 

@@ -8,6 +8,7 @@ missing library is an error.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_longlong, c_void_p
 
 import torch
@@ -202,7 +203,12 @@ def attention_mma_library(head_dim: int):
         raise KernelError(f"tensor-core attention is built for head sizes {MMA_HEAD_DIMS}, not {head_dim}")
     lib = _mma.get(head_dim)
     if lib is None:
-        lib = load_library(f"attn_mma_hd{head_dim}", ["attention_mma.cu"], {"IE_HD": head_dim}, ["attention_noalloc.h"])
+        defines = {"IE_HD": head_dim}
+        # for measurements: IE_ATTN_DEFINES="IE_DC_WARPS=4,IE_DC_STAGES=4" builds a variant of its own
+        for item in filter(None, os.environ.get("IE_ATTN_DEFINES", "").split(",")):
+            name, _, value = item.partition("=")
+            defines[name.strip()] = int(value)
+        lib = load_library(f"attn_mma_hd{head_dim}", ["attention_mma.cu"], defines, ["attention_noalloc.h"])
         P, I, F = c_void_p, c_int, c_float
         lib.ie_attention_prefill.argtypes = [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P]
         lib.ie_attention_prefill.restype = c_int
@@ -211,6 +217,8 @@ def attention_mma_library(head_dim: int):
         lib.ie_attention_decode_scratch_floats.argtypes = [I, I, I]
         lib.ie_attention_decode_scratch_floats.restype = c_longlong
         lib.ie_attention_decode_ticket_words.restype = c_longlong
+        lib.ie_attention_decode_warps.restype = c_int
+        lib.ie_attention_decode_max_blocks.restype = c_int
         _mma[head_dim] = lib
     return lib
 
@@ -231,6 +239,12 @@ def attention_decode_scratch_floats(n_tokens, n_heads, n_splits, head_dim) -> in
     return int(attention_mma_library(head_dim).ie_attention_decode_scratch_floats(n_tokens, n_heads, n_splits))
 
 
+def attention_decode_max_splits(head_dim) -> int:
+    """The most splits a launch takes: warps of a block x the most blocks per (request, kv head)."""
+    lib = attention_mma_library(head_dim)
+    return int(lib.ie_attention_decode_warps()) * int(lib.ie_attention_decode_max_blocks())
+
+
 def attention_decode_ticket_words(head_dim) -> int:
     """How many words at the start of the decode scratch hold tickets; they must be zero before the
     first launch on a piece of scratch (every launch leaves them zero)."""
@@ -244,7 +258,8 @@ def attention_decode_mma(q, out, kpool, vpool, block_table, q_start, ctx_before,
     ``scratch`` is float32 device memory of ``attention_decode_scratch_floats`` elements: partial
     tickets in its first ``attention_decode_ticket_words`` words, which must be zero when the first
     launch starts and are zero again when a launch ends, then partial outputs, maxima and sums of
-    every split, which are written before they are read.  At most 64 splits."""
+    every block, which are written before they are read.  At most ``attention_decode_max_splits`` splits,
+    each a multiple of 32 keys."""
     assert q.dtype is torch.bfloat16 and scratch.dtype is torch.float32
     lib = attention_mma_library(head_dim)
     _check(lib.ie_attention_decode(_ptr(q), _ptr(out), _ptr(kpool), _ptr(vpool), _ptr(block_table), _ptr(q_start),

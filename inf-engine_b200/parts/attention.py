@@ -118,7 +118,8 @@ class PagedAttention:
         if self.rt.act_dtype is torch.bfloat16 and s.head_dim in kernels.MMA_HEAD_DIMS:
             # tensor-core kernels, built for this head size when first used
             if ctx.max_q_len * group <= 16:
-                n_splits, split_keys = decode_splits(ctx.keys_cap, ctx.n_requests * s.n_kv_heads)
+                n_splits, split_keys = decode_splits(ctx.keys_cap, ctx.n_requests * s.n_kv_heads,
+                                                      kernels.attention_decode_max_splits(s.head_dim))
                 n = kernels.attention_decode_scratch_floats(ctx.n_tokens, s.n_heads, n_splits, s.head_dim)
                 scratch = self.rt.ws.take("attn_scratch", (n,), torch.float32)   # zero when made; tickets stay zero
                 kernels.attention_decode_mma(q, out, cache.k, cache.v, kvctx.block_table, ctx.q_start,
@@ -149,15 +150,21 @@ class PagedAttention:
 TCGEN05_MIN_ROWS = 128
 
 
-def decode_splits(keys_cap: int, n_streams: int, resident_warps: int = 888) -> tuple[int, int]:
+def decode_splits(keys_cap: int, n_streams: int, max_splits: int = 384, target_warps: int = 1200) -> tuple[int, int]:
     """How the decode kernel cuts the keys: (number of splits, keys per split).
 
-    One warp works on one split of one (request, kv head) and keeps four tiles of 32 keys in
-    flight, so a split is at least 128 keys; with many streams the splits grow so that the
-    warps of a step (counted at half of ``keys_cap``, the usual fill) fit the GPU at once.
-    ``keys_cap`` is the most keys any request of the step can hold.  At most 64 splits.
+    One warp works on one split of one (request, kv head); a block's warps take consecutive splits
+    and add up in shared memory, and only blocks add up through memory.  Measured on B200: a step
+    is fastest when its warps (counted at half of ``keys_cap``, the usual fill) about fill the GPU
+    once, ``target_warps``, with splits of 64 to 512 keys, a power of two; few streams want short
+    splits (latency), many streams long ones (one block then covers a stream and nothing goes
+    through memory).  ``keys_cap`` is the most keys any request of the step can hold.
     """
     keys_cap = max(int(keys_cap), 1)
-    per = -(-keys_cap * max(n_streams, 1) // (2 * resident_warps))
-    split_keys = max(128, min(512, -(-per // 128) * 128), -(-keys_cap // (64 * 128)) * 128)   # at most 64 splits
+    per = keys_cap * max(n_streams, 1) / (2.0 * target_warps)
+    split_keys = 64
+    while split_keys < 512 and split_keys < per:
+        split_keys *= 2
+    while -(-keys_cap // split_keys) > max_splits:      # very long contexts: as few keys per split as the launch allows
+        split_keys *= 2
     return -(-keys_cap // split_keys), split_keys
