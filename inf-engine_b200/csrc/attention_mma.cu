@@ -46,6 +46,18 @@ struct MmaAttnParams {
   int page_shift;  // log2(page_size) when it is a power of two, else -1
   int n_splits, split_keys;
   float scale_log2;
+  // decode with the position encoding and the cache write folded in (every request brings one token):
+  // fuse bit 0: q arrives unrotated and is rotated as it is loaded; bit 1: the token's key and value arrive
+  // in k_new / v_new ([n_tokens, kv_stride] rows), the key is rotated, both join the keys of the step and
+  // are written to their slot of the pool
+  int fuse;
+  const bf16* k_new;
+  const bf16* v_new;
+  int kv_stride;
+  const float* cos_t;   // [positions, HD/2] float32, or null for no rotation
+  const float* sin_t;
+  const int* positions;
+  const int* slot_mapping;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -350,6 +362,74 @@ __global__ void __launch_bounds__(PF_WARPS * 32) attention_prefill_kernel(MmaAtt
   }
 }
 
+// ---- rotation folded into the decode kernel (half-split pairs: dim i with dim i + HD/2;
+// engine/layers.py:82-115 of the reference: x*cos + rotate_half(x)*sin)
+__device__ __forceinline__ void rotate_pair(uint32_t& lo, uint32_t& hi, float c0, float c1, float s0, float s1) {
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&lo));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&hi));
+  lo = pack_bf16(a.x * c0 - b.x * s0, a.y * c1 - b.y * s1);
+  hi = pack_bf16(b.x * c0 + a.x * s0, b.y * c1 + a.y * s1);
+}
+
+// q fragments of one token (both rows of a lane belong to it) rotated in registers: the partner of the
+// dims of k-step ks sits at the same place of k-step ks + KSTEPS/2
+__device__ __forceinline__ void rotate_q_frags(uint32_t (&qf)[KSTEPS][4], const float* cos_row, const float* sin_row,
+                                               int lane) {
+  const int col = (lane & 3) * 2;
+#pragma unroll
+  for (int ks = 0; ks < KSTEPS / 2; ++ks) {
+#pragma unroll
+    for (int h8 = 0; h8 < 2; ++h8) {
+      const float2 cc = *reinterpret_cast<const float2*>(cos_row + ks * 16 + h8 * 8 + col);
+      const float2 ss = *reinterpret_cast<const float2*>(sin_row + ks * 16 + h8 * 8 + col);
+      rotate_pair(qf[ks][h8 * 2], qf[ks + KSTEPS / 2][h8 * 2], cc.x, cc.y, ss.x, ss.y);
+      rotate_pair(qf[ks][h8 * 2 + 1], qf[ks + KSTEPS / 2][h8 * 2 + 1], cc.x, cc.y, ss.x, ss.y);
+    }
+  }
+}
+
+// The step's own key (rotated) and value of kv head c: into row `row` of the tile in shared memory and,
+// if the token has a slot, into the pool.  Lanes [0, HD/16) take the key, eight pairs each; the next
+// HD/8 lanes copy the value.
+__device__ __forceinline__ void insert_new_kv(const MmaAttnParams& p, int token, int c, int row, uint32_t ks_addr,
+                                              uint32_t vs_addr, int lane) {
+  constexpr int KL = HD / 16;
+  const int slot = p.slot_mapping ? p.slot_mapping[token] : -1;
+  size_t dst = 0;
+  if (slot >= 0) {
+    int page, off;
+    page_of(p, slot, page, off);
+    dst = ((size_t)(page * p.n_kv_heads + c) * p.page_size + off) * HD;
+  }
+  if (lane < KL) {
+    const bf16* src = p.k_new + (size_t)token * p.kv_stride + c * HD + lane * 8;
+    uint4 lo = *reinterpret_cast<const uint4*>(src), hi = *reinterpret_cast<const uint4*>(src + HD / 2);
+    if (p.cos_t) {
+      const int pos = p.positions[token];
+      const float* cr = p.cos_t + (size_t)pos * (HD / 2) + lane * 8;
+      const float* sr = p.sin_t + (size_t)pos * (HD / 2) + lane * 8;
+      const float4 c0 = *reinterpret_cast<const float4*>(cr), c1 = *reinterpret_cast<const float4*>(cr + 4);
+      const float4 s0 = *reinterpret_cast<const float4*>(sr), s1 = *reinterpret_cast<const float4*>(sr + 4);
+      rotate_pair(lo.x, hi.x, c0.x, c0.y, s0.x, s0.y);
+      rotate_pair(lo.y, hi.y, c0.z, c0.w, s0.z, s0.w);
+      rotate_pair(lo.z, hi.z, c1.x, c1.y, s1.x, s1.y);
+      rotate_pair(lo.w, hi.w, c1.z, c1.w, s1.z, s1.w);
+    }
+    asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(ks_addr + swz(row, lane)), "r"(lo.x), "r"(lo.y), "r"(lo.z), "r"(lo.w) : "memory");
+    asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(ks_addr + swz(row, lane + KL)), "r"(hi.x), "r"(hi.y), "r"(hi.z), "r"(hi.w) : "memory");
+    if (slot >= 0) {
+      bf16* kp = const_cast<bf16*>(p.kpool) + dst + lane * 8;
+      *reinterpret_cast<uint4*>(kp) = lo;
+      *reinterpret_cast<uint4*>(kp + HD / 2) = hi;
+    }
+  } else if (lane < KL + CHUNKS) {
+    const int ch = lane - KL;
+    const uint4 v = *reinterpret_cast<const uint4*>(p.v_new + (size_t)token * p.kv_stride + c * HD + ch * 8);
+    asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(vs_addr + swz(row, ch)), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+    if (slot >= 0) *reinterpret_cast<uint4*>(const_cast<bf16*>(p.vpool) + dst + ch * 8) = v;
+  }
+}
+
 // -------------------------------------------------------------------- decode
 // A request brings at most 16 rows (q_len * group <= 16).  Block (x, kv head, request) has DC_WARPS warps,
 // each with one split of the keys: consecutive splits, so that a block covers DC_WARPS * split_keys keys.
@@ -409,7 +489,6 @@ __global__ void __launch_bounds__(DC_THREADS) attention_decode_kernel(MmaAttnPar
 
   // splits that hold at least one key some row can see
   const int s_first = lo_all / p.split_keys, s_last = max_lim / p.split_keys;
-  const int n_active = s_last - s_first + 1;
   const int k_lo = max(split * p.split_keys, lo_all);
   const int k_hi = min((split + 1) * p.split_keys, max_lim + 1);
   const bool has_work = split >= s_first && split <= s_last && split < p.n_splits && n_pairs > 0;
@@ -447,11 +526,20 @@ __global__ void __launch_bounds__(DC_THREADS) attention_decode_kernel(MmaAttnPar
     const bf16* qr1 = v1 ? p.q + (size_t)(q0 + t1) * p.q_stride + (c * group + (pr1 - t1 * group)) * HD : nullptr;
     uint32_t qf[KSTEPS][4];
     load_q_frags(qf, qr0, qr1, lane);
+    if ((p.fuse & 1) && p.cos_t) {
+      const int pos = p.positions[q0];
+      rotate_q_frags(qf, p.cos_t + (size_t)pos * (HD / 2), p.sin_t + (size_t)pos * (HD / 2), lane);
+    }
     for (int i = 0; i < n_tiles; ++i) {
       const int k0 = k_lo + i * DC_KT;
       cp_async_wait_pending(issued - (i + 1));
       __syncwarp();
       const uint32_t sb = base + (i % DC_STAGES) * DC_STAGE_BYTES;
+      if ((p.fuse & 2) && ctx >= k0 && ctx < k0 + DC_KT) {
+        // the tile that holds the step's own position: what the cache had there is replaced
+        insert_new_kv(p, q0, c, ctx - k0, sb, sb + DC_KT * HD * 2, lane);
+        __syncwarp();
+      }
       const bool need_mask = (k0 + DC_KT - 1 > ctx) || (p.window > 0);
       if (n_pairs <= 8)
         warp_tile<DC_KT, true>(qf, o, m, l, sb, sb + DC_KT * HD * 2, k0, lim0, lim1, first0, first1, need_mask,
@@ -571,6 +659,8 @@ static void fill(MmaAttnParams& p, const void* q, void* out, const void* kpool, 
   p.q_stride = q_stride; p.out_stride = out_stride; p.table_stride = table_stride;
   p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.page_size = page_size; p.window = window;
   p.n_splits = 0; p.split_keys = 0; p.n_blocks = 0; p.scale_log2 = scale * LOG2E;
+  p.fuse = 0; p.k_new = nullptr; p.v_new = nullptr; p.kv_stride = 0; p.cos_t = nullptr; p.sin_t = nullptr;
+  p.positions = nullptr; p.slot_mapping = nullptr;
   p.page_shift = -1;
   if ((page_size & (page_size - 1)) == 0)
     for (int b = 0; b < 31; ++b)
@@ -635,19 +725,10 @@ extern "C" int ie_attention_decode_max_blocks() { return IE_DECODE_MAX_BLOCKS; }
 // Words at the start of that scratch that must be zero before its first use.
 extern "C" long long ie_attention_decode_ticket_words() { return IE_DECODE_TICKET_WORDS; }
 
-extern "C" int ie_attention_decode(const void* q, void* out, const void* kpool, const void* vpool,
-                                   const int* block_table, const int* q_start, const int* ctx_before, float* scratch,
-                                   int q_stride, int out_stride, int table_stride, int n_requests, int n_tokens,
-                                   int n_heads, int n_kv_heads, int hd, int page_size, int window, float scale,
-                                   int n_splits, int split_keys, cudaStream_t stream) {
-  if (n_requests <= 0) return IE_OK;
-  int rc = check_common(q, out, kpool, vpool, q_stride, out_stride, n_heads, n_kv_heads, hd, page_size);
-  if (rc) return rc;
+static int decode_launch(MmaAttnParams& p, float* scratch, int n_requests, int n_tokens, int n_heads, int n_kv_heads,
+                         int n_splits, int split_keys, cudaStream_t stream) {
   if (n_splits <= 0 || split_keys <= 0 || split_keys % DC_KT) return IE_BAD_SIZE;
   if ((uintptr_t)scratch & 15) return IE_BAD_ALIGN;
-  MmaAttnParams p;
-  fill(p, q, out, kpool, vpool, block_table, q_start, ctx_before, q_stride, out_stride, table_stride, n_heads,
-       n_kv_heads, page_size, window, scale);
   p.n_splits = n_splits;
   p.split_keys = split_keys;
   if ((long long)n_requests * n_kv_heads > IE_DECODE_TICKET_WORDS) return IE_BAD_SIZE;
@@ -665,6 +746,53 @@ extern "C" int ie_attention_decode(const void* q, void* out, const void* kpool, 
   }
   dim3 grid(p.n_blocks, n_kv_heads, n_requests);
   return launch_k(attention_decode_kernel, grid, DC_THREADS, smem, stream, p);
+}
+
+extern "C" int ie_attention_decode(const void* q, void* out, const void* kpool, const void* vpool,
+                                   const int* block_table, const int* q_start, const int* ctx_before, float* scratch,
+                                   int q_stride, int out_stride, int table_stride, int n_requests, int n_tokens,
+                                   int n_heads, int n_kv_heads, int hd, int page_size, int window, float scale,
+                                   int n_splits, int split_keys, cudaStream_t stream) {
+  if (n_requests <= 0) return IE_OK;
+  int rc = check_common(q, out, kpool, vpool, q_stride, out_stride, n_heads, n_kv_heads, hd, page_size);
+  if (rc) return rc;
+  MmaAttnParams p;
+  fill(p, q, out, kpool, vpool, block_table, q_start, ctx_before, q_stride, out_stride, table_stride, n_heads,
+       n_kv_heads, page_size, window, scale);
+  return decode_launch(p, scratch, n_requests, n_tokens, n_heads, n_kv_heads, n_splits, split_keys, stream);
+}
+
+// The same for steps in which every request brings exactly one token (n_tokens == n_requests), with the
+// position encoding and the cache write folded in: q, k_new and v_new are the projections as they come
+// (k_new / v_new rows kv_stride apart); q and the key are rotated by the cos / sin tables ([positions, hd/2]
+// float32; null: no rotation) at positions[token]; with write_kv the key and value join the step's keys
+// and go to slot_mapping[token] of the pool (a negative slot: not stored), without it the cache must
+// already hold them (a layer that reads another layer's cache).
+extern "C" int ie_attention_decode_fused(const void* q, const void* k_new, const void* v_new, void* out, void* kpool,
+                                         void* vpool, const int* block_table, const int* q_start,
+                                         const int* ctx_before, float* scratch, const float* cos_t,
+                                         const float* sin_t, const int* positions, const int* slot_mapping,
+                                         int q_stride, int kv_stride, int out_stride, int table_stride,
+                                         int n_requests, int n_heads, int n_kv_heads, int hd, int page_size,
+                                         int window, float scale, int write_kv, int n_splits, int split_keys,
+                                         cudaStream_t stream) {
+  if (n_requests <= 0) return IE_OK;
+  int rc = check_common(q, out, kpool, vpool, q_stride, out_stride, n_heads, n_kv_heads, hd, page_size);
+  if (rc) return rc;
+  if (!positions || (cos_t == nullptr) != (sin_t == nullptr)) return IE_BAD_SIZE;
+  if (((uintptr_t)cos_t | (uintptr_t)sin_t) & 15) return IE_BAD_ALIGN;
+  if (write_kv) {
+    if (!k_new || !v_new) return IE_BAD_SIZE;
+    if ((((uintptr_t)k_new | (uintptr_t)v_new) & 15) || (kv_stride & 7)) return IE_BAD_ALIGN;
+  }
+  if ((n_heads / n_kv_heads) > 16) return IE_BAD_SIZE;
+  MmaAttnParams p;
+  fill(p, q, out, kpool, vpool, block_table, q_start, ctx_before, q_stride, out_stride, table_stride, n_heads,
+       n_kv_heads, page_size, window, scale);
+  p.fuse = 1 | (write_kv ? 2 : 0);
+  p.k_new = (const bf16*)k_new; p.v_new = (const bf16*)v_new; p.kv_stride = kv_stride;
+  p.cos_t = cos_t; p.sin_t = sin_t; p.positions = positions; p.slot_mapping = slot_mapping;
+  return decode_launch(p, scratch, n_requests, n_requests, n_heads, n_kv_heads, n_splits, split_keys, stream);
 }
 
 // ------------------------------------------------- decode without any allocation

@@ -44,6 +44,21 @@ extern "C" int ie_patch_tokens(int* ids, const int* src, const int* prev, int n,
   return launch_k(patch_tokens_kernel, (n + 127) / 128, 128, 0, stream, ids, src, prev, n);
 }
 
+// A time stamp in stream order, for timelines of a step (diagnostics only): slot[0] = the GPU's nanosecond
+// clock at the moment everything launched before it has finished.
+__global__ void stamp_kernel(unsigned long long* slot) {
+  pdl_trigger();
+  pdl_wait();
+  if (threadIdx.x == 0) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    *slot = t;
+  }
+}
+extern "C" int ie_stamp(unsigned long long* slot, cudaStream_t stream) {
+  return launch_k(stamp_kernel, 1, 32, 0, stream, slot);
+}
+
 // -------------------------------------------------------------------- RMSNorm
 // x = residual[row] (+ delta[row]);  residual[row] = x (unless rows are gathered);
 // out[m] = x / sqrt(mean(x^2) + eps) * gain          (engine/layers.py:24-25)

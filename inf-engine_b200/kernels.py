@@ -68,6 +68,8 @@ def core():
         lib.ie_embed_gather.argtypes = [P, P, I, P, I, I, I, P]
         lib.ie_patch_tokens.argtypes = [P, P, P, I, P]
         lib.ie_patch_tokens.restype = c_int
+        lib.ie_stamp.argtypes = [P, P]
+        lib.ie_stamp.restype = c_int
         lib.ie_rmsnorm.argtypes = [P, P, P, I, P, I, P, I, I, F, P]
         lib.ie_residual_add.argtypes = [P, P, I, I, I, P]
         lib.ie_rope_kv_write.argtypes = [P, P, P, I, I, P, P, P, P, P, P, I, I, I, I, I, I, I, P]
@@ -97,6 +99,15 @@ def patch_tokens(ids: torch.Tensor, src: torch.Tensor, prev: torch.Tensor) -> No
     """ids[i] = prev[src[i]] where src[i] >= 0 (token ids that are still on the device)."""
     assert ids.dtype == src.dtype == prev.dtype == torch.int32 and src.shape[0] >= ids.shape[0]
     _check(core().ie_patch_tokens(_ptr(ids), _ptr(src), _ptr(prev), ids.shape[0], _stream()), "patch_tokens")
+
+
+def stamp(slots: torch.Tensor, index: int) -> None:
+    """slots[index] = the GPU's nanosecond clock once everything enqueued before has finished (int64 tensor);
+    for timelines of a step.  Not counted as a launch of the step."""
+    global LAUNCHES
+    assert slots.dtype is torch.int64 and 0 <= index < slots.numel()
+    _check(core().ie_stamp(slots.data_ptr() + 8 * index, _stream()), "stamp")
+    LAUNCHES -= 1
 
 
 def rmsnorm(residual: torch.Tensor, delta: torch.Tensor | None, gain: torch.Tensor, out: torch.Tensor,
@@ -214,6 +225,8 @@ def attention_mma_library(head_dim: int):
         lib.ie_attention_prefill.restype = c_int
         lib.ie_attention_decode.argtypes = [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, I, P]
         lib.ie_attention_decode.restype = c_int
+        lib.ie_attention_decode_fused.argtypes = [P] * 14 + [I] * 10 + [F, I, I, I, P]
+        lib.ie_attention_decode_fused.restype = c_int
         lib.ie_attention_decode_scratch_floats.argtypes = [I, I, I]
         lib.ie_attention_decode_scratch_floats.restype = c_longlong
         lib.ie_attention_decode_ticket_words.restype = c_longlong
@@ -269,6 +282,25 @@ def attention_decode_mma(q, out, kpool, vpool, block_table, q_start, ctx_before,
            "attention_decode_mma")
 
 
+def attention_decode_fused(q, k_new, v_new, out, kpool, vpool, block_table, q_start, ctx_before, scratch, cos, sin,
+                           positions, slot_mapping, n_requests, n_heads, n_kv_heads, head_dim, page_size, window,
+                           scale, write_kv, n_splits, split_keys) -> None:
+    """``attention_decode_mma`` for steps in which every request brings exactly one token, with the rotary
+    encoding and the cache write folded in: ``q`` and ``k_new`` arrive unrotated; with ``write_kv`` the
+    token's key (rotated) and value join the keys of the step and are stored at ``slot_mapping`` in the
+    pools.  ``cos``/``sin`` are float32 tables [positions, head_dim/2], or None for no rotation."""
+    assert q.dtype is torch.bfloat16 and scratch.dtype is torch.float32
+    assert k_new.stride(0) == v_new.stride(0) and k_new.stride(1) == 1 and v_new.stride(1) == 1
+    lib = attention_mma_library(head_dim)
+    _check(lib.ie_attention_decode_fused(_ptr(q), _ptr(k_new), _ptr(v_new), _ptr(out), _ptr(kpool), _ptr(vpool),
+                                         _ptr(block_table), _ptr(q_start), _ptr(ctx_before), _ptr(scratch),
+                                         _ptr(cos), _ptr(sin), _ptr(positions), _ptr(slot_mapping), q.stride(0),
+                                         k_new.stride(0), out.stride(0), block_table.stride(0), n_requests, n_heads,
+                                         n_kv_heads, head_dim, page_size, int(window or 0), float(scale),
+                                         1 if write_kv else 0, n_splits, split_keys, _stream()),
+           "attention_decode_fused")
+
+
 # ----------------------------------------------- weight-streaming product for few rows
 STREAM_MAX_ROWS = 64        # what the kernel takes
 STREAM_BEST_ROWS = 16       # beyond this the library product is faster (activations are re-read per block)
@@ -279,7 +311,12 @@ _stream_lib = None
 def stream_library():
     global _stream_lib
     if _stream_lib is None:
-        lib = load_library("stream", ["gemm_stream.cu", "gemm_stream_tma.cu"])
+        # for measurements: IE_STREAM_DEFINES="IE_STREAM_TRACE=1" builds a variant that notes clock values
+        defines = {}
+        for item in filter(None, os.environ.get("IE_STREAM_DEFINES", "").split(",")):
+            name, _, value = item.partition("=")
+            defines[name.strip()] = int(value)
+        lib = load_library("stream", ["gemm_stream.cu", "gemm_stream_tma.cu"], defines)
         P, I, F = c_void_p, c_int, c_float
         lib.ie_gemm_stream.argtypes = [P, P, P, P, I, P, I, I, I, I, I, I, F, I, I, I, P]
         lib.ie_gemm_stream.restype = c_int

@@ -102,15 +102,32 @@ class PagedAttention:
         v = qkv[:, self.q_width + self.kv_width:]
         kvctx = ctx.kv[cache.group]
         tables = self.position.rotary_tables()
+        out = rt.ws.take("attn_out", (n, self.q_width), rt.act_dtype)
+        if (tables is not None and ctx.max_q_len == 1 and ctx.n_tokens == ctx.n_requests
+                and rt.act_dtype is torch.bfloat16 and s.head_dim in kernels.MMA_HEAD_DIMS
+                and s.n_heads // s.n_kv_heads <= 16):
+            # a decode step: rotation and cache write ride in the attention kernel
+            n_splits, split_keys = decode_splits(ctx.keys_cap, ctx.n_requests * s.n_kv_heads,
+                                                 kernels.attention_decode_max_splits(s.head_dim))
+            scratch = self._decode_scratch(ctx, n_splits)
+            kernels.attention_decode_fused(q, k, v, out, cache.k, cache.v, kvctx.block_table, ctx.q_start,
+                                           ctx.ctx_before, scratch, tables[0], tables[1], ctx.positions,
+                                           kvctx.slot_mapping, ctx.n_requests, s.n_heads, s.n_kv_heads, s.head_dim,
+                                           ctx.page_size, s.window, self.scale, cache.write, n_splits, split_keys)
+            return out
         if tables is None:
             self.position.rotate(q, k, ctx)
         cos, sin = tables if tables is not None else (None, None)
         kernels.rope_kv_write(q, k, v, cos, sin, ctx.positions, kvctx.slot_mapping,
                               cache.k if cache.write else None, cache.v if cache.write else None,
                               s.n_heads, s.n_kv_heads, s.head_dim, ctx.page_size)
-        out = rt.ws.take("attn_out", (n, self.q_width), rt.act_dtype)
         self._attend(q, out, cache, ctx, kvctx)
         return out
+
+    def _decode_scratch(self, ctx, n_splits: int) -> torch.Tensor:
+        s = self.spec
+        n = kernels.attention_decode_scratch_floats(ctx.n_tokens, s.n_heads, n_splits, s.head_dim)
+        return self.rt.ws.take("attn_scratch", (n,), torch.float32)   # zero when made; tickets stay zero
 
     def _attend(self, q, out, cache, ctx, kvctx) -> None:
         s = self.spec
@@ -120,8 +137,7 @@ class PagedAttention:
             if ctx.max_q_len * group <= 16:
                 n_splits, split_keys = decode_splits(ctx.keys_cap, ctx.n_requests * s.n_kv_heads,
                                                       kernels.attention_decode_max_splits(s.head_dim))
-                n = kernels.attention_decode_scratch_floats(ctx.n_tokens, s.n_heads, n_splits, s.head_dim)
-                scratch = self.rt.ws.take("attn_scratch", (n,), torch.float32)   # zero when made; tickets stay zero
+                scratch = self._decode_scratch(ctx, n_splits)
                 kernels.attention_decode_mma(q, out, cache.k, cache.v, kvctx.block_table, ctx.q_start,
                                              ctx.ctx_before, scratch, ctx.n_requests, ctx.n_tokens, s.n_heads,
                                              s.n_kv_heads, s.head_dim, ctx.page_size, s.window, self.scale,

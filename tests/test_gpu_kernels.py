@@ -500,6 +500,82 @@ def test_attention_decode_split_keys(case):
         assert torch.allclose(out.float().cpu(), ref, **tol(act))
 
 
+FUSED_DECODE_CASES = [
+    # H, Hk, hd, page, ctx_before, window, split_keys, rotate, write_kv
+    (8, 2, 64, 16, [0, 300, 15, 511, 512], None, 64, True, True),
+    (6, 2, 64, 8, [70, 129, 31], None, 128, True, True),
+    (4, 1, 128, 16, [50, 333, 0, 127], None, 64, True, True),
+    (4, 4, 64, 16, [3, 1000], 37, 256, True, True),
+    (8, 2, 64, 16, [64, 200], None, 64, False, True),
+    (8, 2, 64, 16, [64, 200], None, 64, True, False),
+]
+
+
+@pytest.mark.parametrize("case", FUSED_DECODE_CASES)
+def test_attention_decode_with_rotation_and_cache_write_folded_in(case):
+    """One token per request: q and the new key arrive unrotated, the kernel rotates them, puts the new key and
+    value among the keys of the step and stores them in the pool; compared with rotation in float32 on the
+    host followed by plain attention, and with the pool the separate kernels would leave."""
+    H, Hk, hd, ps, ctx_before, window, split_keys, rotate, write_kv = case
+    act = torch.bfloat16
+    R = len(ctx_before)
+    q_lens = [1] * R
+    c = paged_case(act, H, Hk, hd, ps, q_lens, ctx_before, seed=7 * hd + R)
+    g = torch.Generator().manual_seed(R)
+    half = hd // 2
+    n_pos = max(ctx_before) + 1
+    ang = torch.rand(n_pos, half, generator=g) * 6.28
+    cos, sin = (ang.cos(), ang.sin()) if rotate else (None, None)
+
+    def rot(x, pos):                               # x [heads, hd] float32
+        if not rotate:
+            return x
+        a, b = x[:, :half], x[:, half:]
+        cc, ss = cos[pos][None], sin[pos][None]
+        return torch.cat([a * cc - b * ss, b * cc + a * ss], dim=1)
+
+    # the step's own token: raw q / k / v as the projections give them (bfloat16 values)
+    q_raw = c["q"]                                                       # [R, H*hd], already bfloat16-rounded
+    k_raw = torch.stack([c["kd"][r][ctx_before[r]] for r in range(R)])   # [R, Hk, hd]
+    v_raw = torch.stack([c["vd"][r][ctx_before[r]] for r in range(R)])
+    q_rot = torch.stack([rot(q_raw[r].view(H, hd), ctx_before[r]) for r in range(R)]).to(act).float().view(R, H * hd)
+    k_rot = torch.stack([rot(k_raw[r], ctx_before[r]) for r in range(R)]).to(act).float()
+    kd = [t.clone() for t in c["kd"]]
+    for r in range(R):
+        kd[r][ctx_before[r]] = k_rot[r]
+    ref = paged_reference(q_rot, kd, c["vd"], q_lens, ctx_before, H, Hk, hd, window)
+
+    # pools: poison where the new token goes when the kernel is to write it, the rotated key when it is not
+    kpool, vpool = c["kpool"].clone(), c["vpool"].clone()
+    slots = []
+    for r in range(R):
+        page = int(c["table"][r, ctx_before[r] // ps])
+        off = ctx_before[r] % ps
+        slots.append(page * ps + off)
+        kpool[page, :, off] = 1e4 if write_kv else k_rot[r]
+        if write_kv:
+            vpool[page, :, off] = 1e4
+    kpool, vpool = kpool.to(DEV, act), vpool.to(DEV, act)
+    dev = lambda t: torch.as_tensor(t, dtype=torch.int32).to(DEV)
+    qkv = torch.cat([q_raw, k_raw.reshape(R, Hk * hd), v_raw.reshape(R, Hk * hd)], dim=1).to(DEV, act)
+    qw, kw = H * hd, Hk * hd
+    cap = max(ctx_before) + 1 + 50
+    n_splits = -(-cap // split_keys)
+    scratch = torch.zeros(k().attention_decode_scratch_floats(R, H, n_splits, hd), device=DEV)
+    out = torch.full((R, H * hd), float("nan"), device=DEV, dtype=act)
+    k().attention_decode_fused(qkv[:, :qw], qkv[:, qw:qw + kw], qkv[:, qw + kw:], out, kpool, vpool,
+                               c["table"].to(DEV), dev(c["q_start"]), dev(ctx_before), scratch,
+                               cos.to(DEV) if rotate else None, sin.to(DEV) if rotate else None, dev(ctx_before),
+                               dev(slots), R, H, Hk, hd, ps, window, hd ** -0.5, write_kv, n_splits, split_keys)
+    assert torch.allclose(out.float().cpu(), ref, **tol(act))
+    for r in range(R):
+        page, off = slots[r] // ps, slots[r] % ps
+        assert torch.allclose(kpool[page, :, off].float().cpu(), k_rot[r], atol=2e-2, rtol=2e-2)
+        assert torch.equal(vpool[page, :, off].float().cpu(), v_raw[r])
+    # the unrotated inputs are left as they were
+    assert torch.equal(qkv[:, :qw].float().cpu(), q_raw)
+
+
 @pytest.mark.parametrize("kind", ["prefill", "decode"])
 def test_tensor_core_attention_finds_one_far_key_among_hundreds(kind):
     H, Hk, hd, ps, act = 4, 2, 64, 16, torch.bfloat16
