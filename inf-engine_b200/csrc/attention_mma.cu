@@ -66,6 +66,18 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool v
   const int sz = valid ? 16 : 0;  // 0 bytes read: the 16 bytes are filled with zeros
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(sz) : "memory");
 }
+// The same with an L2 policy.  A decode step reads every key and value once, and together they are far larger
+// than L2: marked "evict first" they do not push out what the step reads again and again (activations, norm
+// gains, the kernels' own code).
+__device__ __forceinline__ uint64_t l2_evict_first_policy() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ void cp_async16_hint(uint32_t dst, const void* src, bool valid, uint64_t pol) {
+  const int sz = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2, %3;\n" ::"r"(dst), "l"(src), "r"(sz), "l"(pol) : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
@@ -114,7 +126,7 @@ __device__ __forceinline__ void page_of(const MmaAttnParams& p, int kp, int& pag
   }
 }
 
-template <int KT, int NTHREADS>
+template <int KT, int NTHREADS, bool STREAM = false>   // STREAM: keys read once (decode), marked "evict first" in L2
 __device__ __forceinline__ void load_kv_tile(const MmaAttnParams& p, const int* table, int c, int k0, int k_end,
                                              uint32_t ks_addr, uint32_t vs_addr, int tid) {
   constexpr int ITERS = (KT * CHUNKS + NTHREADS - 1) / NTHREADS;
@@ -144,8 +156,14 @@ __device__ __forceinline__ void load_kv_tile(const MmaAttnParams& p, const int* 
       const bool valid = src_row[it] >= 0;
       const size_t off = valid ? (size_t)src_row[it] * HD + chunk * 8 : 0;
       const uint32_t so = swz(row, chunk);
-      cp_async16(ks_addr + so, p.kpool + off, valid);
-      cp_async16(vs_addr + so, p.vpool + off, valid);
+      if (STREAM) {
+        const uint64_t pol = l2_evict_first_policy();
+        cp_async16_hint(ks_addr + so, p.kpool + off, valid, pol);
+        cp_async16_hint(vs_addr + so, p.vpool + off, valid, pol);
+      } else {
+        cp_async16(ks_addr + so, p.kpool + off, valid);
+        cp_async16(vs_addr + so, p.vpool + off, valid);
+      }
     }
   }
 }
@@ -512,14 +530,14 @@ __global__ void __launch_bounds__(DC_THREADS) attention_decode_kernel(MmaAttnPar
   int issued = 0;
   for (; issued < n_first && k_lo + (issued + 1) * DC_KT <= ctx; ++issued) {
     const uint32_t sb = base + issued * DC_STAGE_BYTES;
-    load_kv_tile<DC_KT, 32>(p, table, c, k_lo + issued * DC_KT, k_hi, sb, sb + DC_KT * HD * 2, lane);
+    load_kv_tile<DC_KT, 32, true>(p, table, c, k_lo + issued * DC_KT, k_hi, sb, sb + DC_KT * HD * 2, lane);
     cp_async_commit();
   }
   pdl_wait();
   if (has_work) {
     for (; issued < n_first; ++issued) {
       const uint32_t sb = base + issued * DC_STAGE_BYTES;
-      load_kv_tile<DC_KT, 32>(p, table, c, k_lo + issued * DC_KT, k_hi, sb, sb + DC_KT * HD * 2, lane);
+      load_kv_tile<DC_KT, 32, true>(p, table, c, k_lo + issued * DC_KT, k_hi, sb, sb + DC_KT * HD * 2, lane);
       cp_async_commit();
     }
     const bf16* qr0 = v0 ? p.q + (size_t)(q0 + t0) * p.q_stride + (c * group + (pr0 - t0 * group)) * HD : nullptr;
@@ -549,7 +567,7 @@ __global__ void __launch_bounds__(DC_THREADS) attention_decode_kernel(MmaAttnPar
                                 p.scale_log2, lane);
       __syncwarp();
       if (issued < n_tiles) {
-        load_kv_tile<DC_KT, 32>(p, table, c, k_lo + issued * DC_KT, k_hi, sb, sb + DC_KT * HD * 2, lane);
+        load_kv_tile<DC_KT, 32, true>(p, table, c, k_lo + issued * DC_KT, k_hi, sb, sb + DC_KT * HD * 2, lane);
         cp_async_commit();
         ++issued;
       }

@@ -39,6 +39,26 @@ constexpr unsigned SPIN_LIMIT = 1u << 20;   // polls of a wait that normally las
 
 __device__ int g_stream_error = 0;
 
+// Diagnostics, compiled in with -DIE_STREAM_TRACE only: thread 0 of block 0 of every launch notes the GPU's
+// nanosecond clock at eight points of its life; ie_gemm_stream_trace_read() hands the notes to the host.
+#ifdef IE_STREAM_TRACE
+constexpr int TRACE_LAUNCHES = 4096, TRACE_POINTS = 8;
+__device__ unsigned long long g_trace[TRACE_LAUNCHES * TRACE_POINTS];
+__device__ unsigned int g_trace_n = 0;
+__device__ __forceinline__ unsigned long long trace_now() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define TRACE_BEGIN() unsigned int trace_id = TRACE_LAUNCHES; \
+  if (blockIdx.x == 0 && threadIdx.x == 0) { trace_id = atomicAdd(&g_trace_n, 1u); \
+    if (trace_id < TRACE_LAUNCHES) for (int i_ = 0; i_ < TRACE_POINTS; ++i_) g_trace[trace_id * TRACE_POINTS + i_] = 0; }
+#define TRACE(point) { if (trace_id < TRACE_LAUNCHES) g_trace[trace_id * TRACE_POINTS + (point)] = trace_now(); }
+#else
+#define TRACE_BEGIN()
+#define TRACE(point)
+#endif
+
 struct TmaParams {
   const void* A;          // PLAIN: bf16 [M, lda];  NORM: float32 residual rows [*, lda]
   const bf16* W;          // [N, ldw]
@@ -75,9 +95,16 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
   }
   return false;
 }
-__device__ __forceinline__ void bulk_copy(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+// Weights are read once a step and are far larger than L2: they are marked "evict first", so that the stream
+// does not push out what the step reads again and again (activations, norm gains, the kernels' own code).
+__device__ __forceinline__ uint64_t l2_evict_first_policy() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ void bulk_copy(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar, uint64_t pol) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar), "l"(pol) : "memory");
 }
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
   uint4 v;
@@ -107,6 +134,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_stream_tma_kernel(TmaParams p
   __shared__ volatile int failed;
 
   pdl_trigger();
+  TRACE_BEGIN();
+  TRACE(0);                                                  // entry
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n_units = (p.N + UNIT_ROWS - 1) / UNIT_ROWS;
   const int k_stages = p.K / p.ks;
@@ -135,6 +164,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_stream_tma_kernel(TmaParams p
     uint32_t phase = 0;
     bool ok = true;
     const uint32_t row_bytes = (uint32_t)p.ks * 2;
+    const uint64_t pol = l2_evict_first_policy();
     for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
       const int n0 = u * UNIT_ROWS;
       const int rows = min(UNIT_ROWS, p.N - n0);
@@ -147,7 +177,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_stream_tma_kernel(TmaParams p
         }
         ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
         if (!ok) break;
-        if (lane < rows) bulk_copy(ring + s * stage_bytes + lane * w_pitch, src + (size_t)ksi * p.ks, row_bytes, bar);
+        if (lane < rows) bulk_copy(ring + s * stage_bytes + lane * w_pitch, src + (size_t)ksi * p.ks, row_bytes, bar, pol);
         if (++s == p.n_stages) { s = 0; phase ^= 1; }
       }
     }
@@ -162,7 +192,19 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_stream_tma_kernel(TmaParams p
   }
 
   // --------------------------------------------------------------- consumers
+  // The norm's gain does not depend on the kernel ahead, and it is cold (read once a step, long evicted): it
+  // comes from HBM, behind the weights that every producer is streaming.  Ask for it before waiting.
+  // (a lane takes four consecutive columns per round of 128, so that a warp's load is one contiguous 512 bytes)
+  uint2 gpre[PRO == PRO_NORM ? 16 : 1];    // bfloat16 gain of the first 2,048 columns (a float32 gain is read later)
+  if (PRO == PRO_NORM && XS && !p.gain_is_f32) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+      if (lane * 4 + i * 128 < p.K)   // a volatile statement: the compiler must not sink it below the wait
+        asm volatile("ld.global.nc.v2.u32 {%0,%1}, [%2];" : "=r"(gpre[i].x), "=r"(gpre[i].y)
+                     : "l"((const bf16*)p.gain + lane * 4 + i * 128));
+  }
   pdl_wait();
+  TRACE(2);                                                  // the kernel ahead has finished
   const int g = lane >> 2, t = lane & 3;
   // activations -> shared memory, once per block (plain activations of a long K stay in L2 instead:
   // they would crowd the ring out of shared memory)
@@ -176,45 +218,76 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_stream_tma_kernel(TmaParams p
       }
       if (PRO == PRO_PLAIN) {
         const bf16* src = (const bf16*)p.A + (size_t)m * p.lda;
-#pragma unroll 4
-        for (int k = lane * 8; k < p.K; k += 256)
-          *reinterpret_cast<uint4*>(dst + k) = *reinterpret_cast<const uint4*>(src + k);
+        // read-only loads, eight rounds in flight: staging a row is a matter of trips to L2
+        for (int kb = lane * 8; kb < p.K; kb += 2048) {
+          uint4 v[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            if (kb + i * 256 < p.K) v[i] = __ldg(reinterpret_cast<const uint4*>(src + kb + i * 256));
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            if (kb + i * 256 < p.K) *reinterpret_cast<uint4*>(dst + kb + i * 256) = v[i];
+        }
       } else {
         const int row = p.row_index ? p.row_index[m] : m;
         const float* src = (const float*)p.A + (size_t)row * p.lda;
         float ssq = 0.f;
-#pragma unroll 4
-        for (int k = lane * 8; k < p.K; k += 256) {
-          const float4 x0 = *reinterpret_cast<const float4*>(src + k), x1 = *reinterpret_cast<const float4*>(src + k + 4);
-          float gv[8];
-          if (p.gain_is_f32) {
-            const float4 g0 = *reinterpret_cast<const float4*>((const float*)p.gain + k);
-            const float4 g1 = *reinterpret_cast<const float4*>((const float*)p.gain + k + 4);
-            gv[0] = g0.x; gv[1] = g0.y; gv[2] = g0.z; gv[3] = g0.w; gv[4] = g1.x; gv[5] = g1.y; gv[6] = g1.z; gv[7] = g1.w;
-          } else {
-            const uint4 gr = *reinterpret_cast<const uint4*>((const bf16*)p.gain + k);
-            const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&gr);
+        // Four rounds (1,024 columns) at a time: first every load of the batch (read-only loads, which the
+        // compiler may move ahead of the stores to shared memory), then the arithmetic: a batch costs one
+        // trip to L2, not one per round.
+        for (int kb = lane * 4; kb < p.K; kb += 2048) {
+          float4 xa[16];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const float2 f = __bfloat1622float2(gp[i]);
-              gv[2 * i] = f.x;
-              gv[2 * i + 1] = f.y;
+          for (int i = 0; i < 16; ++i)
+            if (kb + i * 128 < p.K) xa[i] = __ldcg(reinterpret_cast<const float4*>(src + kb + i * 128));
+#ifdef IE_STREAM_TRACE
+          if (trace_id < TRACE_LAUNCHES && kb < 2048) {   // the moment the row's loads have all arrived
+            unsigned long long t_;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_) : "f"(xa[0].x), "f"(xa[3].x), "f"(xa[7].x), "f"(xa[11].x), "f"(xa[15].x));
+            g_trace[trace_id * TRACE_POINTS + 1] = t_;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_) : "r"(gpre[0].x), "r"(gpre[5].x), "r"(gpre[10].x), "r"(gpre[15].x));
+            g_trace[trace_id * TRACE_POINTS + 4] = t_;
+          }
+#endif
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const int k = kb + i * 128;
+            if (k < p.K) {
+              float gv[4];
+              if (p.gain_is_f32) {
+                const float4 g0 = __ldg(reinterpret_cast<const float4*>((const float*)p.gain + k));
+                gv[0] = g0.x; gv[1] = g0.y; gv[2] = g0.z; gv[3] = g0.w;
+              } else {
+                uint2 gr = gpre[i];                       // fetched before the wait
+                if (kb >= 2048) gr = __ldg(reinterpret_cast<const uint2*>((const bf16*)p.gain + k));
+                const float2 f0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gr.x));
+                const float2 f1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gr.y));
+                gv[0] = f0.x; gv[1] = f0.y; gv[2] = f1.x; gv[3] = f1.y;
+              }
+              const float4 x0 = xa[i];
+              ssq += x0.x * x0.x + x0.y * x0.y + x0.z * x0.z + x0.w * x0.w;
+              uint2 o;
+              o.x = pack2(x0.x * gv[0], x0.y * gv[1]);
+              o.y = pack2(x0.z * gv[2], x0.w * gv[3]);
+              *reinterpret_cast<uint2*>(dst + k) = o;
             }
           }
-          ssq += x0.x * x0.x + x0.y * x0.y + x0.z * x0.z + x0.w * x0.w + x1.x * x1.x + x1.y * x1.y + x1.z * x1.z + x1.w * x1.w;
-          uint4 o;
-          o.x = pack2(x0.x * gv[0], x0.y * gv[1]);
-          o.y = pack2(x0.z * gv[2], x0.w * gv[3]);
-          o.z = pack2(x1.x * gv[4], x1.y * gv[5]);
-          o.w = pack2(x1.z * gv[6], x1.w * gv[7]);
-          *reinterpret_cast<uint4*>(dst + k) = o;
         }
+#ifdef IE_STREAM_TRACE
+        if (trace_id < TRACE_LAUNCHES) {   // arithmetic and stores of the row issued
+          unsigned long long t_;
+          asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_) : "f"(ssq));
+          g_trace[trace_id * TRACE_POINTS + 5] = t_;
+        }
+#endif
         ssq = warp_sum(ssq);
         if (lane == 0) inv_rms[m] = 1.f / sqrtf(ssq / (float)p.K + p.eps);
       }
     }
   }
+  TRACE(7);                                                  // warp 0 has staged its rows
   consumer_sync();
+  TRACE(3);                                                  // activations staged
 
   const int kw = warp * (p.ks / CONSUMER_WARPS);        // this warp's k offset inside a stage
   const int chunks = p.ks / (CONSUMER_WARPS * 32);      // 32-wide chunks per warp per stage
@@ -327,6 +400,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_stream_tma_kernel(TmaParams p
     }
     parity ^= 1;
   }
+  TRACE(6);                                                  // last unit stored
 }
 
 template <int NT, int PRO, int EPI, bool XS>
@@ -377,6 +451,19 @@ extern "C" int ie_gemm_stream_tma_error() {
   if (v) cudaMemcpyToSymbol(g_stream_error, &zero, sizeof(int));
   return v;
 }
+
+#ifdef IE_STREAM_TRACE
+// copies the notes of the launches so far to `out` ([launches][8] nanosecond clocks) and starts over; returns the number of launches
+extern "C" int ie_gemm_stream_trace_read(unsigned long long* out, int max_launches) {
+  unsigned int n = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&n, g_trace_n, sizeof(n)) != cudaSuccess) return -1;
+  if ((int)n > max_launches) n = max_launches;
+  if (n > TRACE_LAUNCHES) n = TRACE_LAUNCHES;
+  if (n && cudaMemcpyFromSymbol(out, g_trace, (size_t)n * TRACE_POINTS * sizeof(unsigned long long)) != cudaSuccess) return -1;
+  cudaMemcpyToSymbol(g_trace_n, &zero, sizeof(zero));
+  return (int)n;
+}
+#endif
 
 extern "C" int ie_gemm_stream_tma(const void* A, const void* W, void* C, const void* gain, int gain_dtype,
                                   const int* row_index, int M, int N, int K, int lda, int ldw, int ldc, float eps,
