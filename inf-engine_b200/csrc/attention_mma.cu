@@ -390,7 +390,14 @@ __device__ __forceinline__ void rotate_pair(uint32_t& lo, uint32_t& hi, float c0
 }
 
 // q fragments of one token (both rows of a lane belong to it) rotated in registers: the partner of the
-// dims of k-step ks sits at the same place of k-step ks + KSTEPS/2
+// dims of k-step ks sits at the same place of k-step ks + KSTEPS/2.  cs / sn hold the lane's cosines and
+// sines: [ks][0] for dims ks*16 + col, col+1, [ks][1] for dims ks*16 + 8 + col, col+1.
+__device__ __forceinline__ float2 ld_nc_f2(const float* p) {   // volatile: stays where it is written (before a wait)
+  float2 v;
+  asm volatile("ld.global.nc.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "l"(p));
+  return v;
+}
+// cos_row / sin_row: the position's HD/2 cosines and sines in shared memory
 __device__ __forceinline__ void rotate_q_frags(uint32_t (&qf)[KSTEPS][4], const float* cos_row, const float* sin_row,
                                                int lane) {
   const int col = (lane & 3) * 2;
@@ -406,13 +413,30 @@ __device__ __forceinline__ void rotate_q_frags(uint32_t (&qf)[KSTEPS][4], const 
   }
 }
 
-// The step's own key (rotated) and value of kv head c: into row `row` of the tile in shared memory and,
-// if the token has a slot, into the pool.  Lanes [0, HD/16) take the key, eight pairs each; the next
-// HD/8 lanes copy the value.
-__device__ __forceinline__ void insert_new_kv(const MmaAttnParams& p, int token, int c, int row, uint32_t ks_addr,
-                                              uint32_t vs_addr, int lane) {
+// The step's own key (rotated) and value of kv head c go into row `row` of the tile in shared memory and, if
+// the token has a slot, into the pool.  Lanes [0, HD/16) take the key, eight pairs each; the next HD/8 lanes
+// copy the value.  The projections are fetched right after the kernel ahead has finished (NewKv); rotation and
+// stores happen when the tile has arrived.
+struct NewKv {
+  uint4 a, b;   // key lanes: dims lane*8.. and their partners; value lanes: a only
+};
+__device__ __forceinline__ void load_new_kv(NewKv& n, const MmaAttnParams& p, int token, int c, int lane) {
   constexpr int KL = HD / 16;
-  const int slot = p.slot_mapping ? p.slot_mapping[token] : -1;
+  if (lane < KL) {
+    const bf16* src = p.k_new + (size_t)token * p.kv_stride + c * HD + lane * 8;
+    n.a = *reinterpret_cast<const uint4*>(src);
+    n.b = *reinterpret_cast<const uint4*>(src + HD / 2);
+  } else if (lane < KL + CHUNKS) {
+    n.a = *reinterpret_cast<const uint4*>(p.v_new + (size_t)token * p.kv_stride + c * HD + (lane - KL) * 8);
+  }
+}
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, const uint4& v) {
+  asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ void insert_new_kv(const MmaAttnParams& p, NewKv n, const float* cos_row, const float* sin_row,
+                                              bool rotate, int slot, int c, int row, uint32_t ks_addr, uint32_t vs_addr,
+                                              int lane) {
+  constexpr int KL = HD / 16;
   size_t dst = 0;
   if (slot >= 0) {
     int page, off;
@@ -420,33 +444,47 @@ __device__ __forceinline__ void insert_new_kv(const MmaAttnParams& p, int token,
     dst = ((size_t)(page * p.n_kv_heads + c) * p.page_size + off) * HD;
   }
   if (lane < KL) {
-    const bf16* src = p.k_new + (size_t)token * p.kv_stride + c * HD + lane * 8;
-    uint4 lo = *reinterpret_cast<const uint4*>(src), hi = *reinterpret_cast<const uint4*>(src + HD / 2);
-    if (p.cos_t) {
-      const int pos = p.positions[token];
-      const float* cr = p.cos_t + (size_t)pos * (HD / 2) + lane * 8;
-      const float* sr = p.sin_t + (size_t)pos * (HD / 2) + lane * 8;
-      const float4 c0 = *reinterpret_cast<const float4*>(cr), c1 = *reinterpret_cast<const float4*>(cr + 4);
-      const float4 s0 = *reinterpret_cast<const float4*>(sr), s1 = *reinterpret_cast<const float4*>(sr + 4);
-      rotate_pair(lo.x, hi.x, c0.x, c0.y, s0.x, s0.y);
-      rotate_pair(lo.y, hi.y, c0.z, c0.w, s0.z, s0.w);
-      rotate_pair(lo.z, hi.z, c1.x, c1.y, s1.x, s1.y);
-      rotate_pair(lo.w, hi.w, c1.z, c1.w, s1.z, s1.w);
+    if (rotate) {
+      const float4 c0 = *reinterpret_cast<const float4*>(cos_row + lane * 8), c1 = *reinterpret_cast<const float4*>(cos_row + lane * 8 + 4);
+      const float4 s0 = *reinterpret_cast<const float4*>(sin_row + lane * 8), s1 = *reinterpret_cast<const float4*>(sin_row + lane * 8 + 4);
+      rotate_pair(n.a.x, n.b.x, c0.x, c0.y, s0.x, s0.y);
+      rotate_pair(n.a.y, n.b.y, c0.z, c0.w, s0.z, s0.w);
+      rotate_pair(n.a.z, n.b.z, c1.x, c1.y, s1.x, s1.y);
+      rotate_pair(n.a.w, n.b.w, c1.z, c1.w, s1.z, s1.w);
     }
-    asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(ks_addr + swz(row, lane)), "r"(lo.x), "r"(lo.y), "r"(lo.z), "r"(lo.w) : "memory");
-    asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(ks_addr + swz(row, lane + KL)), "r"(hi.x), "r"(hi.y), "r"(hi.z), "r"(hi.w) : "memory");
+    st_shared_v4(ks_addr + swz(row, lane), n.a);
+    st_shared_v4(ks_addr + swz(row, lane + KL), n.b);
     if (slot >= 0) {
       bf16* kp = const_cast<bf16*>(p.kpool) + dst + lane * 8;
-      *reinterpret_cast<uint4*>(kp) = lo;
-      *reinterpret_cast<uint4*>(kp + HD / 2) = hi;
+      *reinterpret_cast<uint4*>(kp) = n.a;
+      *reinterpret_cast<uint4*>(kp + HD / 2) = n.b;
     }
   } else if (lane < KL + CHUNKS) {
     const int ch = lane - KL;
-    const uint4 v = *reinterpret_cast<const uint4*>(p.v_new + (size_t)token * p.kv_stride + c * HD + ch * 8);
-    asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(vs_addr + swz(row, ch)), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
-    if (slot >= 0) *reinterpret_cast<uint4*>(const_cast<bf16*>(p.vpool) + dst + ch * 8) = v;
+    st_shared_v4(vs_addr + swz(row, ch), n.a);
+    if (slot >= 0) *reinterpret_cast<uint4*>(const_cast<bf16*>(p.vpool) + dst + ch * 8) = n.a;
   }
 }
+
+// Diagnostics, compiled in with -DIE_ATTN_TRACE only: thread 0 of block (0, 0, 0) of every decode launch notes the
+// GPU's nanosecond clock at eight points of its life; ie_attention_trace_read() hands the notes to the host.
+#ifdef IE_ATTN_TRACE
+constexpr int TRACE_LAUNCHES = 4096, TRACE_POINTS = 8;
+__device__ unsigned long long g_trace[TRACE_LAUNCHES * TRACE_POINTS];
+__device__ unsigned int g_trace_n = 0;
+__device__ __forceinline__ unsigned long long trace_now() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define TRACE_BEGIN() unsigned int trace_id = TRACE_LAUNCHES; \
+  if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0) { trace_id = atomicAdd(&g_trace_n, 1u); \
+    if (trace_id < TRACE_LAUNCHES) for (int i_ = 0; i_ < TRACE_POINTS; ++i_) g_trace[trace_id * TRACE_POINTS + i_] = 0; }
+#define TRACE(point) { if (trace_id < TRACE_LAUNCHES) g_trace[trace_id * TRACE_POINTS + (point)] = trace_now(); }
+#else
+#define TRACE_BEGIN()
+#define TRACE(point)
+#endif
 
 // -------------------------------------------------------------------- decode
 // A request brings at most 16 rows (q_len * group <= 16).  Block (x, kv head, request) has DC_WARPS warps,
@@ -482,9 +520,13 @@ __device__ __forceinline__ void cp_async_wait_pending(int pending) {
   }
 }
 
-__global__ void __launch_bounds__(DC_THREADS) attention_decode_kernel(MmaAttnParams p) {
+// head size 64: at most 112 registers at 192 threads, so that the block fits beside the product kernels ahead of
+// and behind it in the stream
+__global__ void __launch_bounds__(DC_THREADS, HD <= 64 ? 3 : 2) attention_decode_kernel(MmaAttnParams p) {
   extern __shared__ __align__(128) unsigned char smem[];
   pdl_trigger();
+  TRACE_BEGIN();
+  TRACE(0);                                                  // entry
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int split = blockIdx.x * DC_WARPS + warp;
   const int c = blockIdx.y, r_id = blockIdx.z;
@@ -533,7 +575,24 @@ __global__ void __launch_bounds__(DC_THREADS) attention_decode_kernel(MmaAttnPar
     load_kv_tile<DC_KT, 32, true>(p, table, c, k_lo + issued * DC_KT, k_hi, sb, sb + DC_KT * HD * 2, lane);
     cp_async_commit();
   }
+  // what the rotation needs does not depend on the kernel ahead either (positions, tables, slots): the
+  // position's cosines and sines go to shared memory before the wait
+  __shared__ __align__(16) float s_cos[HD / 2], s_sin[HD / 2];
+  const bool rotate = (p.fuse & 1) && p.cos_t != nullptr;
+  const bool owner = has_work && (p.fuse & 2) && ctx >= k_lo && ctx < k_hi;   // this warp's keys include the step's own
+  int new_slot = -1;
+  if (rotate && warp == 0 && lane < HD / 4) {
+    const int pos = p.positions[q0];
+    *reinterpret_cast<float2*>(s_cos + lane * 2) = ld_nc_f2(p.cos_t + (size_t)pos * (HD / 2) + lane * 2);
+    *reinterpret_cast<float2*>(s_sin + lane * 2) = ld_nc_f2(p.sin_t + (size_t)pos * (HD / 2) + lane * 2);
+  }
+  if (owner && p.slot_mapping) new_slot = p.slot_mapping[q0];
+  TRACE(1);                                                  // early tiles requested
   pdl_wait();
+  __syncthreads();                                           // the tables' row is in shared memory
+  TRACE(2);                                                  // the kernel ahead has finished
+  NewKv new_kv;
+  if (owner) load_new_kv(new_kv, p, q0, c, lane);
   if (has_work) {
     for (; issued < n_first; ++issued) {
       const uint32_t sb = base + issued * DC_STAGE_BYTES;
@@ -544,18 +603,17 @@ __global__ void __launch_bounds__(DC_THREADS) attention_decode_kernel(MmaAttnPar
     const bf16* qr1 = v1 ? p.q + (size_t)(q0 + t1) * p.q_stride + (c * group + (pr1 - t1 * group)) * HD : nullptr;
     uint32_t qf[KSTEPS][4];
     load_q_frags(qf, qr0, qr1, lane);
-    if ((p.fuse & 1) && p.cos_t) {
-      const int pos = p.positions[q0];
-      rotate_q_frags(qf, p.cos_t + (size_t)pos * (HD / 2), p.sin_t + (size_t)pos * (HD / 2), lane);
-    }
+    if (rotate) rotate_q_frags(qf, s_cos, s_sin, lane);
+    TRACE(3);                                                  // q loaded and rotated (issued)
     for (int i = 0; i < n_tiles; ++i) {
       const int k0 = k_lo + i * DC_KT;
       cp_async_wait_pending(issued - (i + 1));
       __syncwarp();
+      if (i == 0) TRACE(4);                                    // first tile has arrived
       const uint32_t sb = base + (i % DC_STAGES) * DC_STAGE_BYTES;
-      if ((p.fuse & 2) && ctx >= k0 && ctx < k0 + DC_KT) {
+      if (owner && ctx >= k0 && ctx < k0 + DC_KT) {
         // the tile that holds the step's own position: what the cache had there is replaced
-        insert_new_kv(p, q0, c, ctx - k0, sb, sb + DC_KT * HD * 2, lane);
+        insert_new_kv(p, new_kv, s_cos, s_sin, rotate, new_slot, c, ctx - k0, sb, sb + DC_KT * HD * 2, lane);
         __syncwarp();
       }
       const bool need_mask = (k0 + DC_KT - 1 > ctx) || (p.window > 0);
@@ -595,7 +653,9 @@ __global__ void __launch_bounds__(DC_THREADS) attention_decode_kernel(MmaAttnPar
       *reinterpret_cast<float2*>(w_ml + pr1 * 2) = make_float2(m[1], l[1]);
     }
   }
+  TRACE(5);                                                  // warp 0's tiles done, partial in shared memory
   __syncthreads();
+  TRACE(6);                                                  // all warps of the block done
   const int n_out = n_pairs * HD;
   const int blk = (int)blockIdx.x - b_first;
   for (int idx = threadIdx.x; idx < n_out; idx += DC_THREADS) {
@@ -622,6 +682,7 @@ __global__ void __launch_bounds__(DC_THREADS) attention_decode_kernel(MmaAttnPar
       if (d == 0) *reinterpret_cast<float2*>(p.part_ml + (row * p.n_blocks + blk) * 2) = make_float2(M, den);
     }
   }
+  TRACE(7);                                                  // block's result written (output or partial)
   if (n_active_blocks == 1) return;
 
   // ---- ticket of this (request, kv head): the last block to arrive adds the blocks up
@@ -812,6 +873,18 @@ extern "C" int ie_attention_decode_fused(const void* q, const void* k_new, const
   p.cos_t = cos_t; p.sin_t = sin_t; p.positions = positions; p.slot_mapping = slot_mapping;
   return decode_launch(p, scratch, n_requests, n_requests, n_heads, n_kv_heads, n_splits, split_keys, stream);
 }
+
+#ifdef IE_ATTN_TRACE
+extern "C" int ie_attention_trace_read(unsigned long long* out, int max_launches) {
+  unsigned int n = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&n, g_trace_n, sizeof(n)) != cudaSuccess) return -1;
+  if ((int)n > max_launches) n = max_launches;
+  if (n > TRACE_LAUNCHES) n = TRACE_LAUNCHES;
+  if (n && cudaMemcpyFromSymbol(out, g_trace, (size_t)n * TRACE_POINTS * sizeof(unsigned long long)) != cudaSuccess) return -1;
+  cudaMemcpyToSymbol(g_trace_n, &zero, sizeof(zero));
+  return (int)n;
+}
+#endif
 
 // ------------------------------------------------- decode without any allocation
 // See attention_noalloc.h.  The scratch of the split pass is this static array;

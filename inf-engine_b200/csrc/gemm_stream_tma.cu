@@ -125,7 +125,9 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 // NT: 8*NT weight rows per unit (NT n-tiles of the MMA per warp)
 // XS: activations staged in shared memory (true) or read from L2 per stage (false; plain prologue only)
 template <int NT, int PRO, int EPI, bool XS>
-__global__ void __launch_bounds__(THREADS, 1) gemm_stream_tma_kernel(TmaParams p) {
+// Units of 8 rows (short products: qkv, output) keep within 112 registers, so that the kernel behind them in
+// the stream (decode attention, say) finds room on the SM and starts its own fetches early.
+__global__ void __launch_bounds__(THREADS, NT == 1 ? 2 : 1) gemm_stream_tma_kernel(TmaParams p) {
   constexpr int UNIT_ROWS = 8 * NT;
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ __align__(8) unsigned long long bars[2 * MAX_STAGES];   // full[], empty[]
@@ -192,6 +194,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_stream_tma_kernel(TmaParams p
   }
 
   // --------------------------------------------------------------- consumers
+  TRACE(1);                                                  // barriers set up
   // The norm's gain does not depend on the kernel ahead, and it is cold (read once a step, long evicted): it
   // comes from HBM, behind the weights that every producer is streaming.  Ask for it before waiting.
   // (a lane takes four consecutive columns per round of 128, so that a warp's load is one contiguous 512 bytes)
@@ -235,22 +238,13 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_stream_tma_kernel(TmaParams p
         // Four rounds (1,024 columns) at a time: first every load of the batch (read-only loads, which the
         // compiler may move ahead of the stores to shared memory), then the arithmetic: a batch costs one
         // trip to L2, not one per round.
-        for (int kb = lane * 4; kb < p.K; kb += 2048) {
-          float4 xa[16];
+        for (int kb = lane * 4; kb < p.K; kb += 1024) {
+          float4 xa[8];
 #pragma unroll
-          for (int i = 0; i < 16; ++i)
+          for (int i = 0; i < 8; ++i)
             if (kb + i * 128 < p.K) xa[i] = __ldcg(reinterpret_cast<const float4*>(src + kb + i * 128));
-#ifdef IE_STREAM_TRACE
-          if (trace_id < TRACE_LAUNCHES && kb < 2048) {   // the moment the row's loads have all arrived
-            unsigned long long t_;
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_) : "f"(xa[0].x), "f"(xa[3].x), "f"(xa[7].x), "f"(xa[11].x), "f"(xa[15].x));
-            g_trace[trace_id * TRACE_POINTS + 1] = t_;
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_) : "r"(gpre[0].x), "r"(gpre[5].x), "r"(gpre[10].x), "r"(gpre[15].x));
-            g_trace[trace_id * TRACE_POINTS + 4] = t_;
-          }
-#endif
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
+          for (int i = 0; i < 8; ++i) {
             const int k = kb + i * 128;
             if (k < p.K) {
               float gv[4];
@@ -258,7 +252,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_stream_tma_kernel(TmaParams p
                 const float4 g0 = __ldg(reinterpret_cast<const float4*>((const float*)p.gain + k));
                 gv[0] = g0.x; gv[1] = g0.y; gv[2] = g0.z; gv[3] = g0.w;
               } else {
-                uint2 gr = gpre[i];                       // fetched before the wait
+                uint2 gr = (kb < 1024) ? gpre[i] : gpre[i + 8];     // fetched before the wait
                 if (kb >= 2048) gr = __ldg(reinterpret_cast<const uint2*>((const bf16*)p.gain + k));
                 const float2 f0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gr.x));
                 const float2 f1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gr.y));
@@ -273,13 +267,6 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_stream_tma_kernel(TmaParams p
             }
           }
         }
-#ifdef IE_STREAM_TRACE
-        if (trace_id < TRACE_LAUNCHES) {   // arithmetic and stores of the row issued
-          unsigned long long t_;
-          asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_) : "f"(ssq));
-          g_trace[trace_id * TRACE_POINTS + 5] = t_;
-        }
-#endif
         ssq = warp_sum(ssq);
         if (lane == 0) inv_rms[m] = 1.f / sqrtf(ssq / (float)p.K + p.eps);
       }
@@ -325,6 +312,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_stream_tma_kernel(TmaParams p
         if (lane == 0) { atomicExch(&g_stream_error, 2); failed = 1; }
       }
       if (dead) continue;
+      if (u == (int)blockIdx.x && ksi == 0) TRACE(4);        // first stage has arrived
       const uint32_t wbase = ring + s * stage_bytes + g * w_pitch + (kw + t * 8) * 2;
       if (XS) {
         const uint32_t xbase = xs + g * x_pitch + (ksi * p.ks + kw + t * 8) * 2;
@@ -363,6 +351,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_stream_tma_kernel(TmaParams p
 #pragma unroll
       for (int e = 0; e < 4; ++e) red[parity][warp][nt * 4 + e][lane] = acc[nt][0][e] + acc[nt][1][e];
     consumer_sync();
+    if (u == (int)blockIdx.x) TRACE(5);                      // first unit multiplied
     if (tid < 64 * NT && !failed) {
       const int ln = tid & 31, h = (tid >> 5) & 1, nt = tid >> 6;
       const int gg = ln >> 2, tt = ln & 3;
