@@ -705,9 +705,31 @@ __global__ void __launch_bounds__(DC_THREADS, HD <= 64 ? 3 : 2) attention_decode
     const float2* ml = reinterpret_cast<const float2*>(p.part_ml + row * p.n_blocks * 2);
     const float* po = p.part_o + row * p.n_blocks * HD + d;
     float M = -INFINITY;
-    for (int j = 0; j < n_active_blocks; ++j) M = fmaxf(M, __ldcg(ml + j).x);
     float acc = 0.f, den = 0.f;
-    for (int j0 = 0; j0 < n_active_blocks; j0 += 8) {
+    if (n_active_blocks <= 8) {
+      // the usual case: everything in one round of loads, the maximum taken from what they bring
+      float2 mlv[8];
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int j = min(u, n_active_blocks - 1);
+        mlv[u] = __ldcg(ml + j);
+        v[u] = __ldcg(po + (size_t)j * HD);
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        if (u < n_active_blocks) M = fmaxf(M, mlv[u].x);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const bool real = u < n_active_blocks && mlv[u].x > -INFINITY;
+        const float f = real ? fast_exp2(mlv[u].x - M) : 0.f;
+        acc += f * v[u];
+        den += f * mlv[u].y;
+      }
+    } else {
+      for (int j = 0; j < n_active_blocks; ++j) M = fmaxf(M, __ldcg(ml + j).x);
+    }
+    for (int j0 = 0; j0 < n_active_blocks && n_active_blocks > 8; j0 += 8) {
       float2 mlv[8];
       float v[8];
 #pragma unroll
