@@ -721,3 +721,29 @@ def test_sampling_is_reproducible_and_independent_of_the_batch():
     one = torch.empty(1, device=DEV, dtype=torch.int32)
     k().sample(logits[4:5], _rows(cfgs[4:5], keys[4:5], 1000), one)
     assert int(one[0]) == int(a[4])
+
+
+def test_patch_tokens_takes_ids_that_are_still_on_the_device():
+    ids = torch.tensor([11, 12, 13, 14, 15], dtype=torch.int32, device=DEV)
+    src = torch.tensor([-1, 2, -1, 0, 0, 7, 7, 7], dtype=torch.int32, device=DEV)      # longer than ids: a graph's buffer
+    prev = torch.tensor([100, 101, 102], dtype=torch.int32, device=DEV)
+    k().patch_tokens(ids, src, prev)
+    assert ids.tolist() == [11, 102, 13, 100, 100]
+
+
+def test_stamps_follow_stream_order():
+    slots = torch.zeros(4, dtype=torch.int64, device=DEV)
+    x = torch.randn(1 << 20, device=DEV)
+    k().stamp(slots, 0)
+    for _ in range(4):
+        x = x * 1.0001
+    k().stamp(slots, 1)
+    k().stamp(slots, 3)
+    torch.cuda.synchronize()
+    t = slots.tolist()
+    assert 0 < t[0] <= t[1] <= t[3] and t[2] == 0
+
+
+def test_device_error_words_are_clear_after_everything_above():
+    k().check_device_errors()
+

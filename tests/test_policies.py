@@ -19,3 +19,9 @@ def test_decode_splits_grow_with_the_number_of_streams():
     many = decode_splits(4096, 512)[1]
     assert few <= some <= many
     assert few == 64 and many == 512
+
+
+def test_checking_device_errors_needs_no_device_when_nothing_was_loaded():
+    import inf_engine_b200.kernels as kernels
+    if kernels._stream_lib is None and kernels._tc_lib is None and kernels._fa5_lib is None:
+        kernels.check_device_errors()          # nothing loaded: nothing to read, no CUDA call
