@@ -41,6 +41,9 @@ class _Captured:
         self.generation = -1
 
 
+KEYS_STEP = 256      # graphs are captured per this many keys of the longest context
+
+
 class DecodeGraphs:
     def __init__(self, runner):
         self.runner = runner
@@ -76,8 +79,8 @@ class DecodeGraphs:
         n += B
         return off, n
 
-    def _get(self, B: int, widths: tuple[int, ...]):
-        key = (B, widths)
+    def _get(self, B: int, widths: tuple[int, ...], keys_hint: int):
+        key = (B, widths, keys_hint)
         b = self._buckets.get(key)
         if b is None:
             b = _Captured()
@@ -96,7 +99,7 @@ class DecodeGraphs:
                       for g, w in enumerate(widths)]
             ctx.n_tokens = ctx.n_requests = ctx.n_logits = B
             ctx.max_q_len = 1
-            ctx.keys_cap = min(widths) * self.runner.page_size if widths else 0
+            ctx.keys_cap = min(keys_hint, min(widths) * self.runner.page_size) if widths else 0
             ctx.host = {"q_lens": [1] * B, "q_start": list(range(B + 1)), "slots": [0] * B, "graph": True}
             b.ctx = ctx
             b.rows = view("sample_rows").view(B, 7)
@@ -160,7 +163,10 @@ class DecodeGraphs:
         B = _bucket(R, BATCH_BUCKETS)
         widths = tuple(_bucket(max(len(g.tables[e.rid]) for e in entries), [1 << i for i in range(3, 24)])
                        for g in cache.kv_groups)
-        b = self._get(B, widths)
+        # the split-key attention is cut for the longest context of the step, in steps of KEYS_STEP keys: a
+        # graph serves until some request has grown past its step
+        keys_hint = -(-(max(cache.lengths[e.rid] for e in entries) + 1) // KEYS_STEP) * KEYS_STEP
+        b = self._get(B, widths, keys_hint)
         self._fill(b, entries, sample_rows, token_src)
         if device_tokens is not None:
             if token_src is None:

@@ -252,10 +252,10 @@ def attention_decode_scratch_floats(n_tokens, n_heads, n_splits, head_dim) -> in
     return int(attention_mma_library(head_dim).ie_attention_decode_scratch_floats(n_tokens, n_heads, n_splits))
 
 
-def attention_decode_max_splits(head_dim) -> int:
-    """The most splits a launch takes: warps of a block x the most blocks per (request, kv head)."""
+def attention_decode_geometry(head_dim) -> tuple[int, int]:
+    """(warps, i.e. splits, of a decode block; the most blocks per (request, kv head) a launch takes)."""
     lib = attention_mma_library(head_dim)
-    return int(lib.ie_attention_decode_warps()) * int(lib.ie_attention_decode_max_blocks())
+    return int(lib.ie_attention_decode_warps()), int(lib.ie_attention_decode_max_blocks())
 
 
 def attention_decode_ticket_words(head_dim) -> int:
@@ -271,8 +271,8 @@ def attention_decode_mma(q, out, kpool, vpool, block_table, q_start, ctx_before,
     ``scratch`` is float32 device memory of ``attention_decode_scratch_floats`` elements: partial
     tickets in its first ``attention_decode_ticket_words`` words, which must be zero when the first
     launch starts and are zero again when a launch ends, then partial outputs, maxima and sums of
-    every block, which are written before they are read.  At most ``attention_decode_max_splits`` splits,
-    each a multiple of 32 keys."""
+    every block, which are written before they are read.  At most warps x blocks of
+    ``attention_decode_geometry`` splits, each a multiple of 32 keys."""
     assert q.dtype is torch.bfloat16 and scratch.dtype is torch.float32
     lib = attention_mma_library(head_dim)
     _check(lib.ie_attention_decode(_ptr(q), _ptr(out), _ptr(kpool), _ptr(vpool), _ptr(block_table), _ptr(q_start),

@@ -108,7 +108,7 @@ class PagedAttention:
                 and s.n_heads // s.n_kv_heads <= 16):
             # a decode step: rotation and cache write ride in the attention kernel
             n_splits, split_keys = decode_splits(ctx.keys_cap, ctx.n_requests * s.n_kv_heads,
-                                                 kernels.attention_decode_max_splits(s.head_dim))
+                                                 *kernels.attention_decode_geometry(s.head_dim))
             scratch = self._decode_scratch(ctx, n_splits)
             kernels.attention_decode_fused(q, k, v, out, cache.k, cache.v, kvctx.block_table, ctx.q_start,
                                            ctx.ctx_before, scratch, tables[0], tables[1], ctx.positions,
@@ -136,7 +136,7 @@ class PagedAttention:
             # tensor-core kernels, built for this head size when first used
             if ctx.max_q_len * group <= 16:
                 n_splits, split_keys = decode_splits(ctx.keys_cap, ctx.n_requests * s.n_kv_heads,
-                                                      kernels.attention_decode_max_splits(s.head_dim))
+                                                      *kernels.attention_decode_geometry(s.head_dim))
                 scratch = self._decode_scratch(ctx, n_splits)
                 kernels.attention_decode_mma(q, out, cache.k, cache.v, kvctx.block_table, ctx.q_start,
                                              ctx.ctx_before, scratch, ctx.n_requests, ctx.n_tokens, s.n_heads,
@@ -166,21 +166,23 @@ class PagedAttention:
 TCGEN05_MIN_ROWS = 128
 
 
-def decode_splits(keys_cap: int, n_streams: int, max_splits: int = 384, target_warps: int = 1200) -> tuple[int, int]:
+def decode_splits(keys: int, n_streams: int, warps_per_block: int = 6, max_blocks: int = 64,
+                  target_warps: int = 1200) -> tuple[int, int]:
     """How the decode kernel cuts the keys: (number of splits, keys per split).
 
-    One warp works on one split of one (request, kv head); a block's warps take consecutive splits
-    and add up in shared memory, and only blocks add up through memory.  Measured on B200: a step
-    is fastest when its warps (counted at half of ``keys_cap``, the usual fill) about fill the GPU
-    once, ``target_warps``, with splits of 64 to 512 keys, a power of two; few streams want short
-    splits (latency), many streams long ones (one block then covers a stream and nothing goes
-    through memory).  ``keys_cap`` is the most keys any request of the step can hold.
+    One warp works on one split of one (request, kv head); a block's ``warps_per_block`` warps take
+    consecutive splits and add up in shared memory, and only blocks add up through memory.  Measured on
+    B200: a step is fastest when its warps about fill the GPU once (``target_warps``) and every warp of
+    every block has keys: the blocks per stream follow from the number of streams, the split is the
+    stream's keys over that many warps, in steps of 32 keys between 64 and 512.  Few streams get short
+    splits and several blocks each (latency), many streams one block each (nothing goes through memory).
+    ``keys`` is an upper bound of the keys any request of the step holds, the tighter the better.
     """
-    keys_cap = max(int(keys_cap), 1)
-    per = keys_cap * max(n_streams, 1) / (2.0 * target_warps)
-    split_keys = 64
-    while split_keys < 512 and split_keys < per:
-        split_keys *= 2
-    while -(-keys_cap // split_keys) > max_splits:      # very long contexts: as few keys per split as the launch allows
-        split_keys *= 2
-    return -(-keys_cap // split_keys), split_keys
+    keys = max(int(keys), 1)
+    w = max(int(warps_per_block), 1)
+    blocks = max(1, round(target_warps / (max(n_streams, 1) * w)))
+    blocks = min(blocks, max(1, keys // (64 * w)), max_blocks)           # no split shorter than 64 keys
+    blocks = max(blocks, -(-keys // (512 * w)))                           # nor longer than 512, if the launch allows
+    blocks = min(blocks, max_blocks)
+    split_keys = max(64, -(-keys // (blocks * w * 32)) * 32)
+    return -(-keys // split_keys), split_keys

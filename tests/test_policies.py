@@ -4,21 +4,29 @@ from inf_engine_b200.parts.attention import decode_splits
 
 
 def test_decode_splits_cover_the_keys_and_respect_the_launch_limit():
-    for keys_cap in (1, 63, 64, 300, 2048, 4096, 8192, 131072, 1 << 20):
+    for keys in (1, 63, 64, 300, 2048, 2304, 4096, 8192, 131072, 1 << 20):
         for n_streams in (1, 8, 64, 512, 4096):
-            for max_splits in (192, 384):
-                n, sk = decode_splits(keys_cap, n_streams, max_splits)
-                assert n * sk >= keys_cap and (n - 1) * sk < keys_cap
-                assert n <= max_splits
-                assert sk >= 64 and sk & (sk - 1) == 0 and sk % 32 == 0
+            for warps in (3, 6):
+                n, sk = decode_splits(keys, n_streams, warps, 64)
+                assert n * sk >= keys and (n - 1) * sk < keys
+                assert -(-n // warps) <= 64
+                assert sk >= 64 and sk % 32 == 0
 
 
 def test_decode_splits_grow_with_the_number_of_streams():
     few = decode_splits(4096, 8)[1]
     some = decode_splits(4096, 64)[1]
     many = decode_splits(4096, 512)[1]
-    assert few <= some <= many
-    assert few == 64 and many == 512
+    assert few < some < many
+    assert few <= 96 and many > 256
+
+
+def test_decode_splits_fill_the_warps_of_a_block():
+    # many streams: one block a stream, every warp with keys
+    n, sk = decode_splits(2304, 512, 6)
+    assert n == 6 and sk == 384
+    # the measured best at batch 8: three blocks of six warps, 128 keys a warp
+    assert decode_splits(2304, 64, 6) == (18, 128)
 
 
 def test_checking_device_errors_needs_no_device_when_nothing_was_loaded():
