@@ -557,7 +557,8 @@ __global__ void __launch_bounds__(DC_THREADS, HD <= 64 ? 3 : 2) attention_decode
   const int n_active_blocks = b_last - b_first + 1;
   // A block without keys leaves at once and frees its slot.  It need not wait for the kernel ahead:
   // block 0 of every (request, kv head) always has keys and waits, so this kernel still ends after it.
-  if ((int)blockIdx.x < b_first || (int)blockIdx.x > b_last || n_pairs <= 0) return;
+  // (a request with more than 16 rows is not this kernel's: in a mixed step the prefill kernel takes it)
+  if ((int)blockIdx.x < b_first || (int)blockIdx.x > b_last || n_pairs <= 0 || n_pairs > 16) return;
 
   float o[NT_O][4];
 #pragma unroll
@@ -815,7 +816,7 @@ extern "C" int ie_attention_prefill(const void* q, void* out, const void* kpool,
 // request and kv head) at the start, then partial outputs, then maxima and sums.  The tickets
 // must be zero before the first launch on a piece of scratch; every launch leaves them zero
 // again, whatever the batch, because they always sit in the same place.  The rest may hold anything.
-#define IE_DECODE_TICKET_WORDS 4096
+#define IE_DECODE_TICKET_WORDS 16384
 #define IE_DECODE_MAX_BLOCKS 64
 extern "C" long long ie_attention_decode_scratch_floats(int n_tokens, int n_heads, int n_splits) {
   return IE_DECODE_TICKET_WORDS + (long long)n_tokens * n_heads * n_splits * (HD + 2);

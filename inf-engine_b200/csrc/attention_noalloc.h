@@ -12,8 +12,9 @@
  *
  * - The array holds IE_NOALLOC_SCRATCH_FLOATS floats.  Every GPU that loads the
  *   library keeps that much memory until the process exits.
- * - A call needs 4096 + n_tokens * n_heads * n_splits * (head_dim + 2) words and is
- *   refused with IE_NOALLOC_TOO_LARGE when that exceeds the array.
+ * - A call needs ie_attention_decode_scratch_floats(n_tokens, n_heads, n_splits) words
+ *   (16384 tickets + n_tokens * n_heads * n_splits * (head_dim + 2)) and is refused with
+ *   IE_NOALLOC_TOO_LARGE when that exceeds the array.
  * - The first call on a device looks the array's device address up
  *   (cudaGetSymbolAddress) and remembers it; make that first call before any
  *   stream capture begins.  Later calls on the device only launch.

@@ -55,20 +55,36 @@ class StepContext:
         self.max_seq_len = 0
         self.keys_cap = 0          # no request of the step holds more keys than this (sizes split-key grids)
 
-    def attention_work(self, group: int, rows: int):
+    def attention_work(self, group: int, rows: int, more_than: int = 0):
         """Work list for attention kernels that tile (token, head-in-group) pairs
-        in tiles of ``rows``: arrays (request, first pair) and their count."""
-        key = (group, rows)
+        in tiles of ``rows``: arrays (request, first pair) and their count.  With
+        ``more_than`` only requests that bring more pairs than that are listed."""
+        key = (group, rows, more_than)
         if key not in self._work:
             req, pair0 = [], []
             for r, q_len in enumerate(self.host["q_lens"]):
+                if q_len * group <= more_than:
+                    continue
                 for p in range(0, q_len * group, rows):
                     req.append(r)
                     pair0.append(p)
             n = len(req)
-            dev = self.rt.staging.upload(np.asarray(req + pair0, dtype=np.int32))
-            self._work[key] = (dev[:n], dev[n:], n)
+            dev = self.rt.staging.upload(np.asarray(req + pair0, dtype=np.int32)) if n else None
+            self._work[key] = (dev[:n], dev[n:], n) if n else (None, None, 0)
         return self._work[key]
+
+    def keys_of_small_requests(self, group: int, at_most: int) -> tuple[int, int]:
+        """(how many requests bring at most ``at_most`` (token, head-in-group) pairs, the most keys one of them
+        holds after this step); needs the host's copy of the step."""
+        n, keys = 0, 0
+        q_lens, before = self.host["q_lens"], self.host.get("ctx_before")
+        if before is None:
+            return 0, 0
+        for q_len, b in zip(q_lens, before):
+            if q_len * group <= at_most:
+                n += 1
+                keys = max(keys, b + q_len)
+        return n, keys
 
 
 def build_context(rt, manager, entries: list[StepEntry]) -> StepContext:

@@ -134,24 +134,33 @@ class PagedAttention:
         group = s.n_heads // s.n_kv_heads
         if self.rt.act_dtype is torch.bfloat16 and s.head_dim in kernels.MMA_HEAD_DIMS:
             # tensor-core kernels, built for this head size when first used
-            if ctx.max_q_len * group <= 16:
-                n_splits, split_keys = decode_splits(ctx.keys_cap, ctx.n_requests * s.n_kv_heads,
+            n_small, small_keys = (ctx.n_requests, ctx.keys_cap) if ctx.max_q_len * group <= 16 \
+                else ctx.keys_of_small_requests(group, 16)
+            if ctx.n_requests * s.n_kv_heads > kernels.attention_decode_ticket_words(s.head_dim):
+                n_small = 0        # more (request, kv head) pairs than the split-key kernel has tickets for
+            if n_small:
+                # requests with at most 16 rows (decode tokens, as a rule): the split-key kernel; in a mixed step
+                # it leaves the others alone, and the prefill kernel below is given those only
+                n_splits, split_keys = decode_splits(small_keys, n_small * s.n_kv_heads,
                                                       *kernels.attention_decode_geometry(s.head_dim))
                 scratch = self._decode_scratch(ctx, n_splits)
                 kernels.attention_decode_mma(q, out, cache.k, cache.v, kvctx.block_table, ctx.q_start,
                                              ctx.ctx_before, scratch, ctx.n_requests, ctx.n_tokens, s.n_heads,
                                              s.n_kv_heads, s.head_dim, ctx.page_size, s.window, self.scale,
                                              n_splits, split_keys)
-            elif (ctx.max_q_len * group >= TCGEN05_MIN_ROWS
-                  and kernels.attention_tcgen05_supports(s.head_dim, ctx.page_size, s.window)):
+            if n_small == ctx.n_requests:
+                return
+            more_than = 16 if n_small else 0
+            if (ctx.max_q_len * group >= TCGEN05_MIN_ROWS
+                    and kernels.attention_tcgen05_supports(s.head_dim, ctx.page_size, s.window)):
                 # prompt portions: tcgen05 tensor cores, tiles of 128 rows by 128 keys
-                work_req, work_pair0, n_work = ctx.attention_work(group, 128)
+                work_req, work_pair0, n_work = ctx.attention_work(group, 128, more_than)
                 kernels.attention_tcgen05(q, out, cache.k, cache.v, kvctx.block_table, ctx.q_start, ctx.ctx_before,
                                           work_req, work_pair0, n_work, s.n_heads, s.n_kv_heads, s.head_dim,
                                           ctx.page_size, self.scale)
             else:
                 rows = 64      # tiles of 128 rows (8 warps) leave one block per SM at this register count: slower
-                work_req, work_pair0, n_work = ctx.attention_work(group, rows)
+                work_req, work_pair0, n_work = ctx.attention_work(group, rows, more_than)
                 kernels.attention_prefill_mma(q, out, cache.k, cache.v, kvctx.block_table, ctx.q_start,
                                               ctx.ctx_before, work_req, work_pair0, n_work, s.n_heads,
                                               s.n_kv_heads, s.head_dim, ctx.page_size, s.window, self.scale, rows)
