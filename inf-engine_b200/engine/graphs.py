@@ -42,6 +42,7 @@ class _Captured:
 
 
 KEYS_STEP = 256      # graphs are captured per this many keys of the longest context
+MAX_GRAPHS = 48      # captured graphs kept; the one unused for longest goes first
 
 
 class DecodeGraphs:
@@ -82,7 +83,11 @@ class DecodeGraphs:
     def _get(self, B: int, widths: tuple[int, ...], keys_hint: int):
         key = (B, widths, keys_hint)
         b = self._buckets.get(key)
+        if b is not None:
+            self._buckets[key] = self._buckets.pop(key)       # most recently used last
         if b is None:
+            while len(self._buckets) >= MAX_GRAPHS:
+                self._buckets.pop(next(iter(self._buckets)))
             b = _Captured()
             b.B, b.widths = B, widths
             b.off, b.n = self._layout(B, widths)

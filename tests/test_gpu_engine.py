@@ -245,6 +245,31 @@ def test_greedy_generation_through_the_entry_point(tmp_path, name, dtype):
         assert out[0] == plain_llama.greedy_generate(weights, config, prompts[0], 8)
 
 
+@pytest.mark.parametrize("name,dtype", [("tiny_a", "float32"), ("tiny_d", "bfloat16")])
+def test_graphs_follow_the_growing_context_and_old_ones_are_dropped(tmp_path, monkeypatch, name, dtype):
+    """Decode graphs are captured per step of the longest context; with a step of 8 keys and room for two
+    graphs, 40 generated tokens go through many captures and evictions and still equal the plain choice."""
+    from inf_engine_b200 import Engine, Request
+    from inf_engine_b200.engine import graphs
+    monkeypatch.setattr(graphs, "KEYS_STEP", 8)
+    monkeypatch.setattr(graphs, "MAX_GRAPHS", 2)
+    d = make_model_dir(tmp_path, name)
+    config, weights = plain_inputs(d)
+    prompts = [random_tokens(config["vocab_size"], n, 70 + n) for n in (3, 11)]
+    engine = Engine.from_dir(d, dtype=dtype, n_total_blocks=32, block_size=8)
+    out = engine.run_offline([Request(i, p, max_new_tokens=40) for i, p in enumerate(prompts)])
+    g = engine.runner.graphs
+    assert g.captures >= 5 and len(g._buckets) <= 2
+    for i, p in enumerate(prompts):
+        logits = plain_llama.forward_logits(weights, config, p + out[i])
+        for j, tok in enumerate(out[i]):
+            row = logits[len(p) + j - 1]
+            if dtype == "float32":
+                assert tok == int(row.argmax())
+            else:
+                assert float(row.max() - row[tok]) <= 4e-2 * max(1.0, float(row.abs().max()))
+
+
 def test_generation_survives_a_pool_that_runs_out(tmp_path):
     """Pages run out while decoding: the youngest request is preempted and recomputed;
     every request still gets exactly the tokens it gets when it runs alone."""
