@@ -1,5 +1,5 @@
-// Causal paged attention for prompt portions on the fifth-generation tensor cores (sm_100a), head size 64,
-// bfloat16: S = Q K^T and O += P V are tcgen05.mma instructions with their accumulators in tensor memory;
+// Causal paged attention for prompt portions on the fifth-generation tensor cores (sm_100a), head sizes 64
+// (key tiles of 128) and 128 (key tiles of 64), bfloat16: S = Q K^T and O += P V are tcgen05.mma instructions with their accumulators in tensor memory;
 // keys and values arrive page by page through TMA (cp.async.bulk.tensor over the cache pool); the online
 // softmax runs one thread per row straight out of tensor memory (tcgen05.ld), with no shuffles.
 //
@@ -23,13 +23,26 @@
 
 namespace {
 
-constexpr int HD = 64;
 constexpr int ROWS = 128;            // rows of a block's tile
-constexpr int KT = 128;              // keys of a tile
 constexpr int FA_THREADS = 192;
 constexpr unsigned FA_SPIN_LIMIT = 1u << 20;
 constexpr float LOG2E = 1.4426950408889634f;
-constexpr uint32_t TILE_BYTES = 128 * 64 * 2;   // 16 KB: Q, one K stage, one V stage, half of P
+constexpr uint32_t ATOM_BYTES = 128 * 64 * 2;   // 16 KB: 128 rows of one 128-byte swizzle atom (64 bfloat16)
+
+// Shared-memory geometry for head size HD and key tiles of KT keys.  Operands are kept as "halves" of 64
+// elements along their contiguous dimension (one swizzle atom wide): Q is HD/64 halves of [128 rows][64 dims],
+// a K or V stage HD/64 halves of [KT keys][64 dims], P is KT/64 (at least one) halves of [128 rows][64 keys].
+template <int HD, int KT>
+struct Geo {
+  static constexpr int HALVES = HD / 64;
+  static constexpr uint32_t Q_BYTES = HALVES * ATOM_BYTES;
+  static constexpr uint32_t KV_HALF = KT * 128;
+  static constexpr uint32_t KV_STAGE = HALVES * KV_HALF;
+  static constexpr uint32_t P_BYTES = (KT / 64 > 0 ? KT / 64 : 1) * ATOM_BYTES;
+  static constexpr uint32_t K_OFF = Q_BYTES, V_OFF = K_OFF + 2 * KV_STAGE, P_OFF = V_OFF + 2 * KV_STAGE;
+  static constexpr uint32_t TILES_BYTES = P_OFF + P_BYTES;
+  static_assert(HD % 64 == 0 && HD <= 128 && KT % 64 == 0 && KT <= 128, "S takes columns [0, KT), O columns [128, 128 + HD) of 256");
+};
 
 __device__ int g_fa_error = 0;
 
@@ -73,10 +86,10 @@ __device__ __forceinline__ void fa_tma_load_2d(uint32_t dst, const CUtensorMap* 
 __device__ __forceinline__ uint64_t desc_k_major(uint32_t addr) {
   return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
 }
-// MN-major operand of 64 contiguous elements (one swizzle atom wide): K advances by rows of 128 bytes,
-// groups of 8 rows 1024 bytes apart (stride offset); the leading offset (between 64-element groups) is not used
-__device__ __forceinline__ uint64_t desc_mn_major(uint32_t addr) {
-  return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)(TILE_BYTES >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) |
+// MN-major operand (its rows are K, 128 bytes = 64 elements of MN each): K advances by rows, groups of 8 rows
+// 1024 bytes apart (stride offset); groups of 64 MN elements `lbo_bytes` apart (leading offset)
+__device__ __forceinline__ uint64_t desc_mn_major(uint32_t addr, uint32_t lbo_bytes) {
+  return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)(lbo_bytes >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) |
          ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
 }
 __device__ __forceinline__ uint32_t idesc_f32_bf16(int m, int n, int b_mn_major) {
@@ -131,16 +144,18 @@ __device__ __forceinline__ uint32_t fa_pack(float lo, float hi) {
 // byte offset of 16-byte chunk `chunk` (0..7) of row `row` in a tile of 128-byte rows under the 128-byte swizzle
 __device__ __forceinline__ uint32_t sw128(int row, int chunk) { return (uint32_t)(row * 128 + ((chunk ^ (row & 7)) << 4)); }
 
+template <int HD, int KT>
 __global__ void __launch_bounds__(FA_THREADS, 2) attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
                                                                           const __grid_constant__ CUtensorMap map_v,
                                                                           FaParams p) {
-  // seven tiles of 16 KB (Q, two stages of K, two of V, two halves of P), then the barriers
-  // (kv_full[2], kv_empty[2], s_full, p_ready, pv_done), the tensor-memory slot and the failure flag.
-  // No static shared memory and no padding: two blocks have to fit one SM.
+  // 112 KB of tiles (Q, two stages of K, two of V, P), then the barriers (kv_full[2], kv_empty[2], s_full,
+  // p_ready, pv_done), the tensor-memory slot and the failure flag.  No static shared memory and no padding: two
+  // blocks have to fit one SM.
+  using G = Geo<HD, KT>;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
-  unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem_raw + 7 * TILE_BYTES);
-  uint32_t* tmem_slot_p = reinterpret_cast<uint32_t*>(smem_raw + 7 * TILE_BYTES + 64);
-  volatile int* failed_p = reinterpret_cast<volatile int*>(smem_raw + 7 * TILE_BYTES + 72);
+  unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem_raw + G::TILES_BYTES);
+  uint32_t* tmem_slot_p = reinterpret_cast<uint32_t*>(smem_raw + G::TILES_BYTES + 64);
+  volatile int* failed_p = reinterpret_cast<volatile int*>(smem_raw + G::TILES_BYTES + 72);
 #define tmem_slot (*tmem_slot_p)
 #define failed (*failed_p)
 
@@ -151,7 +166,7 @@ __global__ void __launch_bounds__(FA_THREADS, 2) attention_tcgen05_kernel(const 
     if (tid == 0) atomicExch(&g_fa_error, 8);
     return;
   }
-  const uint32_t q_sm = base, k_sm = base + TILE_BYTES, v_sm = base + 3 * TILE_BYTES, p_sm = base + 5 * TILE_BYTES;
+  const uint32_t q_sm = base, k_sm = base + G::K_OFF, v_sm = base + G::V_OFF, p_sm = base + G::P_OFF;
   unsigned char* gen_base = smem_raw;
   const uint32_t kv_full0 = saddr(&bars[0]), kv_empty0 = saddr(&bars[2]);
   const uint32_t s_full = saddr(&bars[4]), p_ready = saddr(&bars[5]), pv_done = saddr(&bars[6]);
@@ -184,7 +199,7 @@ __global__ void __launch_bounds__(FA_THREADS, 2) attention_tcgen05_kernel(const 
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
-    // 256 columns: S in [0, 128), O in [128, 192)
+    // 256 columns: S in [0, KT), O in [128, 128 + HD)
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 256;" ::"r"(saddr(tmem_slot_p)) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -217,14 +232,17 @@ __global__ void __launch_bounds__(FA_THREADS, 2) attention_tcgen05_kernel(const 
       const uint32_t bar = kv_full0 + 8 * s;
       if (lane == 0) {
         ok = !failed && fa_mbar_wait(kv_empty0 + 8 * s, phase ^ 1);
-        if (ok) fa_mbar_expect_tx(bar, 2 * TILE_BYTES);
+        if (ok) fa_mbar_expect_tx(bar, 2 * G::KV_STAGE);
         else { atomicExch(&g_fa_error, 1); failed = 1; }
       }
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       if (!ok) break;
       if (lane < pages_per_tile) {
-        fa_tma_load_2d(k_sm + s * TILE_BYTES + lane * ps * 128, &map_k, 0, row, bar);
-        fa_tma_load_2d(v_sm + s * TILE_BYTES + lane * ps * 128, &map_v, 0, row, bar);
+#pragma unroll
+        for (int h = 0; h < G::HALVES; ++h) {
+          fa_tma_load_2d(k_sm + s * G::KV_STAGE + h * G::KV_HALF + lane * ps * 128, &map_k, h * 64, row, bar);
+          fa_tma_load_2d(v_sm + s * G::KV_STAGE + h * G::KV_HALF + lane * ps * 128, &map_v, h * 64, row, bar);
+        }
       }
       if (s == 1) phase ^= 1;
     }
@@ -243,15 +261,16 @@ __global__ void __launch_bounds__(FA_THREADS, 2) attention_tcgen05_kernel(const 
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks)
-          fa_umma(tmem_s, desc_k_major(q_sm + ks * 32), desc_k_major(k_sm + s * TILE_BYTES + ks * 32), idesc_s, ks > 0 ? 1u : 0u);
+          fa_umma(tmem_s, desc_k_major(q_sm + (ks >> 2) * ATOM_BYTES + (ks & 3) * 32),
+                  desc_k_major(k_sm + s * G::KV_STAGE + (ks >> 2) * G::KV_HALF + (ks & 3) * 32), idesc_s, ks > 0 ? 1u : 0u);
         fa_commit(s_full);
         // P of this tile (phase j+1 of p_ready: phase 0 was the queries)
         if (!fa_mbar_wait(p_ready, (uint32_t)(j + 1) & 1u)) { atomicExch(&g_fa_error, 3); failed = 1; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
         for (int kk = 0; kk < KT / 16; ++kk)
-          fa_umma(tmem_o, desc_k_major(p_sm + (kk >> 2) * TILE_BYTES + (kk & 3) * 32),
-                  desc_mn_major(v_sm + s * TILE_BYTES + kk * 2048), idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+          fa_umma(tmem_o, desc_k_major(p_sm + (kk >> 2) * ATOM_BYTES + (kk & 3) * 32),
+                  desc_mn_major(v_sm + s * G::KV_STAGE + kk * 2048, G::KV_HALF), idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
         fa_commit(kv_empty0 + 8 * s);
         fa_commit(pv_done);
         if (s == 1) kv_phase ^= 1;
@@ -272,10 +291,10 @@ __global__ void __launch_bounds__(FA_THREADS, 2) attention_tcgen05_kernel(const 
     {
       const bf16* src = p.q + (size_t)(q0 + t) * p.q_stride + head * HD;
 #pragma unroll
-      for (int ch = 0; ch < 8; ++ch) {
+      for (int ch = 0; ch < HD / 8; ++ch) {
         uint4 v = make_uint4(0u, 0u, 0u, 0u);
         if (valid) v = *reinterpret_cast<const uint4*>(src + ch * 8);
-        *reinterpret_cast<uint4*>(gen_base + sw128(r, ch)) = v;
+        *reinterpret_cast<uint4*>(gen_base + (ch >> 3) * ATOM_BYTES + sw128(r, ch & 7)) = v;
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> visible to the tensor core
       __syncwarp();
@@ -297,7 +316,7 @@ __global__ void __launch_bounds__(FA_THREADS, 2) attention_tcgen05_kernel(const 
       // the exponentials): 128 scores would not fit the registers beside everything else
       float mx = -INFINITY;
 #pragma unroll
-      for (int q4 = 0; q4 < 4; ++q4) {
+      for (int q4 = 0; q4 < KT / 32; ++q4) {
         float sc[32];
         fa_tmem_ld32(tmem_s + lane_addr + q4 * 32, sc);
         if (interior) {
@@ -330,7 +349,7 @@ __global__ void __launch_bounds__(FA_THREADS, 2) attention_tcgen05_kernel(const 
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (moves) {
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
+          for (int h = 0; h < HD / 32; ++h) {
             float o[32];
             fa_tmem_ld32(tmem_o + lane_addr + h * 32, o);
 #pragma unroll
@@ -342,7 +361,7 @@ __global__ void __launch_bounds__(FA_THREADS, 2) attention_tcgen05_kernel(const 
       }
       float sum = 0.f;
 #pragma unroll
-      for (int q4 = 0; q4 < 4; ++q4) {
+      for (int q4 = 0; q4 < KT / 32; ++q4) {
         float sc[32];
         fa_tmem_ld32(tmem_s + lane_addr + q4 * 32, sc);
 #pragma unroll
@@ -356,7 +375,7 @@ __global__ void __launch_bounds__(FA_THREADS, 2) attention_tcgen05_kernel(const 
           }
           const int col = q4 * 32 + ch * 8;                // key index inside the tile
           const uint4 v = make_uint4(fa_pack(e[0], e[1]), fa_pack(e[2], e[3]), fa_pack(e[4], e[5]), fa_pack(e[6], e[7]));
-          *reinterpret_cast<uint4*>(gen_base + 5 * TILE_BYTES + (col >> 6) * TILE_BYTES + sw128(r, (col & 63) >> 3)) = v;
+          *reinterpret_cast<uint4*>(gen_base + G::P_OFF + (col >> 6) * ATOM_BYTES + sw128(r, (col & 63) >> 3)) = v;
         }
       }
       l = l * corr + sum;
@@ -375,7 +394,7 @@ __global__ void __launch_bounds__(FA_THREADS, 2) attention_tcgen05_kernel(const 
       const float inv = l > 0.f ? 1.f / l : 0.f;
       bf16* dst = p.out + (size_t)(q0 + t) * p.out_stride + head * HD;
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
+      for (int h = 0; h < HD / 32; ++h) {
         float o[32];
         fa_tmem_ld32(tmem_o + lane_addr + h * 32, o);
         if (valid) {
@@ -416,13 +435,13 @@ static FaEncodeFn fa_encode_fn() {
   return fn;
 }
 
-// the pool as a matrix [pool_rows, 64] of bfloat16 (a row is one key of one head); boxes of one page
-static int fa_make_map(CUtensorMap* map, const void* base, long long pool_rows, int page_size) {
+// the pool as a matrix [pool_rows, hd] of bfloat16 (a row is one key of one head); boxes of one page by 64 dims
+static int fa_make_map(CUtensorMap* map, const void* base, long long pool_rows, int page_size, int hd) {
   FaEncodeFn fn = fa_encode_fn();
   if (!fn) return IE_BAD_SIZE;
-  const cuuint64_t dims[2] = {(cuuint64_t)HD, (cuuint64_t)pool_rows};
-  const cuuint64_t strides[1] = {(cuuint64_t)HD * 2};
-  const cuuint32_t box[2] = {(cuuint32_t)HD, (cuuint32_t)page_size};
+  const cuuint64_t dims[2] = {(cuuint64_t)hd, (cuuint64_t)pool_rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)hd * 2};
+  const cuuint32_t box[2] = {64u, (cuuint32_t)page_size};
   const cuuint32_t elem[2] = {1, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -439,15 +458,34 @@ extern "C" int ie_attention_tcgen05_error() {
   return v;
 }
 
-// 1 if the kernel takes the geometry: head size 64, pages of 8..128 keys that divide 128, a power of two
+// keys of a tile for a head size (0: not taken)
+static int fa_key_tile(int hd) { return hd == 64 ? 128 : (hd == 128 ? 64 : 0); }
+
+// 1 if the kernel takes the geometry: head size 64 or 128, pages of at least 8 keys, a power of two, that divide a
+// key tile (128 keys at head size 64, 64 keys at head size 128); no window
 extern "C" int ie_attention_tcgen05_supports(int hd, int page_size, int window) {
-  if (hd != HD || window > 0) return 0;
-  if (page_size < 8 || page_size > 128 || (page_size & (page_size - 1)) || 128 % page_size) return 0;
+  const int kt = fa_key_tile(hd);
+  if (!kt || window > 0) return 0;
+  if (page_size < 8 || page_size > kt || (page_size & (page_size - 1)) || kt % page_size) return 0;
   return 1;
 }
 
+template <int HD, int KT>
+static int fa_launch(const CUtensorMap& mk, const CUtensorMap& mv, const FaParams& p, int n_work, int n_kv_heads,
+                     cudaStream_t stream) {
+  const size_t smem = Geo<HD, KT>::TILES_BYTES + 128;
+  static bool attr = false;
+  if (!attr) {
+    cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel<HD, KT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    attr = true;
+  }
+  return launch_k(attention_tcgen05_kernel<HD, KT>, dim3((unsigned)((long long)n_work * n_kv_heads)), FA_THREADS, smem,
+                  stream, mk, mv, p);
+}
+
 // The work list cuts each request's (token, head-in-group) rows into tiles of 128; n_pool_pages is the
-// number of pages of kpool / vpool ([pages, kv_heads, page_size, 64]).
+// number of pages of kpool / vpool ([pages, kv_heads, page_size, hd]).
 extern "C" int ie_attention_tcgen05(const void* q, void* out, const void* kpool, const void* vpool,
                                     const int* block_table, const int* q_start, const int* ctx_before,
                                     const int* work_req, const int* work_pair0, int q_stride, int out_stride,
@@ -460,9 +498,9 @@ extern "C" int ie_attention_tcgen05(const void* q, void* out, const void* kpool,
   if ((q_stride | out_stride) & 7) return IE_BAD_ALIGN;
   CUtensorMap mk, mv;
   const long long rows = (long long)n_pool_pages * n_kv_heads * page_size;
-  int rc = fa_make_map(&mk, kpool, rows, page_size);
+  int rc = fa_make_map(&mk, kpool, rows, page_size, hd);
   if (rc) return rc;
-  rc = fa_make_map(&mv, vpool, rows, page_size);
+  rc = fa_make_map(&mv, vpool, rows, page_size, hd);
   if (rc) return rc;
   FaParams p;
   p.q = (const bf16*)q; p.out = (bf16*)out; p.block_table = block_table; p.q_start = q_start; p.ctx_before = ctx_before;
@@ -472,12 +510,6 @@ extern "C" int ie_attention_tcgen05(const void* q, void* out, const void* kpool,
   p.page_shift = 0;
   while ((1 << p.page_shift) < page_size) ++p.page_shift;
   p.scale_log2 = scale * LOG2E;
-  const size_t smem = 7 * TILE_BYTES + 128;
-  static bool attr = false;
-  if (!attr) {
-    cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-    attr = true;
-  }
-  return launch_k(attention_tcgen05_kernel, dim3((unsigned)((long long)n_work * n_kv_heads)), FA_THREADS, smem, stream, mk, mv, p);
+  if (hd == 64) return fa_launch<64, 128>(mk, mv, p, n_work, n_kv_heads, stream);
+  return fa_launch<128, 64>(mk, mv, p, n_work, n_kv_heads, stream);
 }

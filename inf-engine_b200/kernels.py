@@ -418,7 +418,7 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epi: str = "
                                              _EPI[epi], bn, sm_count(), _stream()), f"gemm_tcgen05(m={m}, n={n}, k={k}, {epi})")
 
 
-# ------------------------------------------- prompt-portion attention on tcgen05 (head size 64)
+# ------------------------------------------- prompt-portion attention on tcgen05 (head sizes 64 and 128)
 _fa5_lib = None
 
 
@@ -447,9 +447,9 @@ def attention_tcgen05_error() -> int:
 
 def attention_tcgen05(q, out, kpool, vpool, block_table, q_start, ctx_before, work_req, work_pair0, n_work,
                       n_heads, n_kv_heads, head_dim, page_size, scale) -> None:
-    """Causal paged attention for prompt portions with tcgen05 tensor cores; bfloat16, head size 64; the
-    work list cuts each request's (token, head-in-group) rows into tiles of 128.  ``kpool``/``vpool`` are
-    one layer's pages, [pages, kv_heads, page_size, 64], contiguous."""
+    """Causal paged attention for prompt portions with tcgen05 tensor cores; bfloat16, head size 64 or 128;
+    the work list cuts each request's (token, head-in-group) rows into tiles of 128.  ``kpool``/``vpool``
+    are one layer's pages, [pages, kv_heads, page_size, head_dim], contiguous."""
     assert q.dtype is torch.bfloat16 and q.stride(1) == 1 and out.stride(1) == 1
     assert kpool.is_contiguous() and vpool.is_contiguous() and kpool.dim() == 4
     _check(attention_tcgen05_library().ie_attention_tcgen05(

@@ -417,22 +417,26 @@ def test_attention_prefill_tensor_cores(case, rows):
 
 
 TCGEN05_ATTENTION_CASES = [
-    # H, Hk, page, q_lens, ctx_before
-    (8, 2, 16, [200], [0]),
-    (6, 2, 8, [1, 9, 1, 70, 130], [70, 0, 129, 31, 515]),
-    (4, 4, 16, [17, 1, 64, 300], [3, 300, 64, 0]),
-    (3, 1, 32, [5, 166], [11, 200]),
-    (8, 1, 64, [129, 2], [127, 1000]),
-    (2, 2, 128, [3, 150, 257], [9, 40, 0]),
+    # H, Hk, hd, page, q_lens, ctx_before
+    (8, 2, 64, 16, [200], [0]),
+    (6, 2, 64, 8, [1, 9, 1, 70, 130], [70, 0, 129, 31, 515]),
+    (4, 4, 64, 16, [17, 1, 64, 300], [3, 300, 64, 0]),
+    (3, 1, 64, 32, [5, 166], [11, 200]),
+    (8, 1, 64, 64, [129, 2], [127, 1000]),
+    (2, 2, 64, 128, [3, 150, 257], [9, 40, 0]),
+    (8, 2, 128, 16, [200], [0]),
+    (6, 2, 128, 8, [1, 9, 1, 70, 130], [70, 0, 129, 31, 515]),
+    (3, 3, 128, 32, [17, 1, 300], [3, 300, 64]),
+    (4, 1, 128, 64, [129, 2, 40], [127, 1000, 0]),
 ]
 
 
 @pytest.mark.parametrize("case", TCGEN05_ATTENTION_CASES)
 def test_attention_prefill_tcgen05(case):
-    H, Hk, ps, q_lens, ctx_before = case
-    hd, act = 64, torch.bfloat16
+    H, Hk, hd, ps, q_lens, ctx_before = case
+    act = torch.bfloat16
     assert k().attention_tcgen05_supports(hd, ps, None)
-    c = paged_case(act, H, Hk, hd, ps, q_lens, ctx_before, seed=5 * ps + len(q_lens))
+    c = paged_case(act, H, Hk, hd, ps, q_lens, ctx_before, seed=5 * ps + len(q_lens) + hd)
     ref = paged_reference(c["q"], c["kd"], c["vd"], q_lens, ctx_before, H, Hk, hd, None)
     req, pair0 = work_list(q_lens, H // Hk, 128)
     dev = lambda t: torch.as_tensor(t, dtype=torch.int32).to(DEV)
@@ -445,8 +449,9 @@ def test_attention_prefill_tcgen05(case):
     assert torch.allclose(out.float().cpu(), ref, **tol(act))
 
 
-def test_attention_tcgen05_finds_one_far_key_among_hundreds():
-    H, Hk, hd, ps, act = 4, 2, 64, 16, torch.bfloat16
+@pytest.mark.parametrize("hd", [64, 128])
+def test_attention_tcgen05_finds_one_far_key_among_hundreds(hd):
+    H, Hk, ps, act = 4, 2, 16, torch.bfloat16
     q_lens, ctx_before = [140, 6], [700, 420]
     c = paged_case(act, H, Hk, hd, ps, q_lens, ctx_before, seed=11, spike=True)
     ref = paged_reference(c["q"], c["kd"], c["vd"], q_lens, ctx_before, H, Hk, hd, None)
@@ -462,7 +467,8 @@ def test_attention_tcgen05_finds_one_far_key_among_hundreds():
 
 
 def test_attention_tcgen05_refuses_what_it_cannot_do():
-    assert not k().attention_tcgen05_supports(128, 16, None)
+    assert not k().attention_tcgen05_supports(96, 16, None)
+    assert not k().attention_tcgen05_supports(128, 128, None)
     assert not k().attention_tcgen05_supports(64, 4, None)
     assert not k().attention_tcgen05_supports(64, 16, 32)
 
