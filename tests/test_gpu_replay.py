@@ -15,8 +15,8 @@ from helpers import TINY, TraceBuilder, assert_close, make_model_dir, plain_inpu
 pytestmark = pytest.mark.gpu
 
 LENGTHS = {"tiny_a": [70, 45, 130, 20, 97, 33, 150], "tiny_b": [64, 129, 40, 200, 31, 16, 77],
-           "tiny_d": [81, 300, 47, 160, 33, 210, 65]}
-PAGE = {"tiny_a": 16, "tiny_b": 8, "tiny_d": 16}
+           "tiny_d": [81, 300, 47, 160, 33, 210, 65], "tiny_e": [150, 66, 260, 40, 129, 90, 35]}
+PAGE = {"tiny_a": 16, "tiny_b": 8, "tiny_d": 16, "tiny_e": 32}
 
 
 def schedules(name: str, requests: dict[str, list[int]], seed: int) -> TraceBuilder:
@@ -67,7 +67,7 @@ def schedules(name: str, requests: dict[str, list[int]], seed: int) -> TraceBuil
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_d"])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_d", "tiny_e"])
 def test_replay_under_every_cut(tmp_path, name, dtype):
     model_dir = make_model_dir(tmp_path, name)
     config, weights = plain_inputs(model_dir)
