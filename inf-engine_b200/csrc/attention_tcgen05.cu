@@ -1,5 +1,5 @@
 // Causal paged attention for prompt portions on the fifth-generation tensor cores (sm_100a), head sizes 64
-// (key tiles of 128) and 128 (key tiles of 64), bfloat16: S = Q K^T and O += P V are tcgen05.mma instructions with their accumulators in tensor memory;
+// and 128 (key tiles of 64 keys), bfloat16: S = Q K^T and O += P V are tcgen05.mma instructions with their accumulators in tensor memory;
 // keys and values arrive page by page through TMA (cp.async.bulk.tensor over the cache pool); the online
 // softmax runs one thread per row straight out of tensor memory (tcgen05.ld), with no shuffles.
 //
@@ -10,8 +10,10 @@
 //   warp 0      TMA producer: for each key tile looks the pages up in the block table and issues one tensor
 //               copy per page for K and for V into a two-stage ring (a page that is not held or lies past the
 //               end is replaced by page 0: its keys are masked and its values get weight zero)
-//   warp 1      allocates tensor memory, issues  S = Q K^T  (4 MMAs of K = 16), later  O += P V  (8 MMAs; V is
-//               the MN-major operand: its rows are keys, as the cache stores them)
+//   warp 1      allocates tensor memory, issues  S = Q K^T  and  O += P V  (V is the MN-major operand: its rows
+//               are keys, as the cache stores them).  S has two buffers in tensor memory: the scores of tile j+1
+//               are issued before the thread waits for the softmax of tile j, so a softmax thread finds its next
+//               scores ready when it has written P
 //   warps 2-5   thread r owns row r: reads S from tensor memory, masks, keeps the running maximum and sum in
 //               float32, rescales O in tensor memory when the maximum moved, writes P as bfloat16 into shared
 //               memory in the 128-byte swizzle that the MMA expects
@@ -24,28 +26,33 @@
 namespace {
 
 constexpr int ROWS = 128;            // rows of a block's tile
-constexpr int FA_THREADS = 192;
+// threads that share a row of the softmax (1 or 2).  Measured at 2,048 tokens, head size 64: 44.9 us with one thread a
+// row, 48.7 us with two (more warps to hide latency, but an exchange per tile and twice the hand-overs).
+constexpr int FA_SOFTMAX_SPLIT = 1;
+constexpr int FA_THREADS = 64 + 128 * FA_SOFTMAX_SPLIT;
 constexpr unsigned FA_SPIN_LIMIT = 1u << 20;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr uint32_t ATOM_BYTES = 128 * 64 * 2;   // 16 KB: 128 rows of one 128-byte swizzle atom (64 bfloat16)
 
-// Shared-memory geometry for head size HD and key tiles of KT keys.  Operands are kept as "halves" of 64
+// Shared-memory geometry for head size HD, key tiles of KT keys and a ring of STAGES key/value stages.  Operands are kept as "halves" of 64
 // elements along their contiguous dimension (one swizzle atom wide): Q is HD/64 halves of [128 rows][64 dims],
 // a K or V stage HD/64 halves of [KT keys][64 dims], P is KT/64 (at least one) halves of [128 rows][64 keys].
-template <int HD, int KT>
+template <int HD, int KT, int STAGES>
 struct Geo {
   static constexpr int HALVES = HD / 64;
   static constexpr uint32_t Q_BYTES = HALVES * ATOM_BYTES;
   static constexpr uint32_t KV_HALF = KT * 128;
   static constexpr uint32_t KV_STAGE = HALVES * KV_HALF;
   static constexpr uint32_t P_BYTES = (KT / 64 > 0 ? KT / 64 : 1) * ATOM_BYTES;
-  static constexpr uint32_t K_OFF = Q_BYTES, V_OFF = K_OFF + 2 * KV_STAGE, P_OFF = V_OFF + 2 * KV_STAGE;
+  static constexpr uint32_t K_OFF = Q_BYTES, V_OFF = K_OFF + STAGES * KV_STAGE, P_OFF = V_OFF + STAGES * KV_STAGE;
   static constexpr uint32_t TILES_BYTES = P_OFF + P_BYTES;
-  // tensor memory: S in columns [0, KT), O in [KT, KT + HD), rounded up to a power of two
-  static constexpr int TMEM_COLS = KT + HD <= 128 ? 128 : 256;
+  // tensor memory: two S buffers in columns [0, 2 KT), O in [2 KT, 2 KT + HD), rounded up to a power of two
+  static constexpr int O_COL = 2 * KT;
+  static constexpr int TMEM_COLS = O_COL + HD <= 128 ? 128 : (O_COL + HD <= 256 ? 256 : 512);
   // blocks that fit an SM (shared memory, tensor memory); the register budget follows from it
-  static constexpr int BLOCKS_PER_SM = (TILES_BYTES + 1152) * 3 <= 232448 && TMEM_COLS * 3 <= 512 ? 3 : 2;
-  static_assert(HD % 64 == 0 && HD <= 128 && KT % 64 == 0 && KT <= 128, "S and O share at most 256 columns of tensor memory");
+  static constexpr int BLOCKS_PER_SM = (TILES_BYTES + 1152) * 3 <= 232448 && TMEM_COLS * 3 <= 512 ? 3
+                                       : ((TILES_BYTES + 1152) * 2 <= 232448 && TMEM_COLS * 2 <= 512 ? 2 : 1);
+  static_assert(HD % 64 == 0 && HD <= 128 && KT % 64 == 0 && KT <= 128 && STAGES >= 2 && STAGES <= 4, "geometry");
 };
 
 __device__ int g_fa_error = 0;
@@ -148,18 +155,18 @@ __device__ __forceinline__ uint32_t fa_pack(float lo, float hi) {
 // byte offset of 16-byte chunk `chunk` (0..7) of row `row` in a tile of 128-byte rows under the 128-byte swizzle
 __device__ __forceinline__ uint32_t sw128(int row, int chunk) { return (uint32_t)(row * 128 + ((chunk ^ (row & 7)) << 4)); }
 
-template <int HD, int KT>
-__global__ void __launch_bounds__(FA_THREADS, Geo<HD, KT>::BLOCKS_PER_SM) attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
+template <int HD, int KT, int STAGES>
+__global__ void __launch_bounds__(FA_THREADS, Geo<HD, KT, STAGES>::BLOCKS_PER_SM) attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
                                                                           const __grid_constant__ CUtensorMap map_v,
                                                                           FaParams p) {
-  // 112 KB of tiles (Q, two stages of K, two of V, P), then the barriers (kv_full[2], kv_empty[2], s_full,
+  // The tiles (Q, STAGES stages of K, as many of V, P), then the barriers (kv_full[4], kv_empty[4], s_full[2],
   // p_ready, pv_done), the tensor-memory slot and the failure flag.  No static shared memory and no padding: two
   // blocks have to fit one SM.
-  using G = Geo<HD, KT>;
+  using G = Geo<HD, KT, STAGES>;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem_raw + G::TILES_BYTES);
-  uint32_t* tmem_slot_p = reinterpret_cast<uint32_t*>(smem_raw + G::TILES_BYTES + 64);
-  volatile int* failed_p = reinterpret_cast<volatile int*>(smem_raw + G::TILES_BYTES + 72);
+  uint32_t* tmem_slot_p = reinterpret_cast<uint32_t*>(smem_raw + G::TILES_BYTES + 104);
+  volatile int* failed_p = reinterpret_cast<volatile int*>(smem_raw + G::TILES_BYTES + 112);
 #define tmem_slot (*tmem_slot_p)
 #define failed (*failed_p)
 
@@ -172,8 +179,8 @@ __global__ void __launch_bounds__(FA_THREADS, Geo<HD, KT>::BLOCKS_PER_SM) attent
   }
   const uint32_t q_sm = base, k_sm = base + G::K_OFF, v_sm = base + G::V_OFF, p_sm = base + G::P_OFF;
   unsigned char* gen_base = smem_raw;
-  const uint32_t kv_full0 = saddr(&bars[0]), kv_empty0 = saddr(&bars[2]);
-  const uint32_t s_full = saddr(&bars[4]), p_ready = saddr(&bars[5]), pv_done = saddr(&bars[6]);
+  const uint32_t kv_full0 = saddr(&bars[0]), kv_empty0 = saddr(&bars[4]);
+  const uint32_t s_full0 = saddr(&bars[8]), p_ready = saddr(&bars[10]), pv_done = saddr(&bars[11]);
 
   // heads are the fast index and the work list is walked from its end: in a long prompt the tiles with the
   // most keys start first, and the short ones fill the tail of the launch
@@ -193,12 +200,13 @@ __global__ void __launch_bounds__(FA_THREADS, Geo<HD, KT>::BLOCKS_PER_SM) attent
 
   if (tid == 0) {
     failed = 0;
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < STAGES; ++s) {
       fa_mbar_init(kv_full0 + 8 * s, 1);
       fa_mbar_init(kv_empty0 + 8 * s, 1);
     }
-    fa_mbar_init(s_full, 1);
-    fa_mbar_init(p_ready, 4);
+    fa_mbar_init(s_full0, 1);
+    fa_mbar_init(s_full0 + 8, 1);
+    fa_mbar_init(p_ready, 4 * FA_SOFTMAX_SPLIT);
     fa_mbar_init(pv_done, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -210,7 +218,7 @@ __global__ void __launch_bounds__(FA_THREADS, Geo<HD, KT>::BLOCKS_PER_SM) attent
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem = tmem_slot;
-  const uint32_t tmem_s = tmem, tmem_o = tmem + KT;
+  const uint32_t tmem_s = tmem, tmem_o = tmem + G::O_COL;
 
   pdl_wait();
 
@@ -220,10 +228,10 @@ __global__ void __launch_bounds__(FA_THREADS, Geo<HD, KT>::BLOCKS_PER_SM) attent
     // a trip to L2 each), and every lane issues its own two copies
     const int ps = p.page_size;
     const int pages_per_tile = KT / ps;
-    uint32_t phase = 0;
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
-      const int s = j & 1;
+      const int s = j % STAGES;
+      const uint32_t phase = (uint32_t)(j / STAGES) & 1u;
       int row = c * ps;                                     // page 0 stands in for what is not held
       if (lane < pages_per_tile) {
         const int kp = j * KT + lane * ps;
@@ -247,41 +255,67 @@ __global__ void __launch_bounds__(FA_THREADS, Geo<HD, KT>::BLOCKS_PER_SM) attent
           fa_tma_load_2d(v_sm + s * G::KV_STAGE + h * G::KV_HALF + lane * ps * 128, &map_v, h * 64, row, bar);
         }
       }
-      if (s == 1) phase ^= 1;
     }
     if (!ok) for (int i = 0; i < 2048; ++i) __nanosleep(64);
   } else if (warp == 1) {
     // ------------------------------------------------------------- MMA issue
     if (lane == 0) {
       const uint32_t idesc_s = idesc_f32_bf16(ROWS, KT, 0), idesc_o = idesc_f32_bf16(ROWS, HD, 1);
+      // descriptors differ only in their address field (bits 0-13, in units of 16 bytes): one base each, offsets added
+      const uint64_t q_desc = desc_k_major(q_sm), k_desc = desc_k_major(k_sm), p_desc = desc_k_major(p_sm);
+      const uint64_t v_desc = desc_mn_major(v_sm, G::KV_HALF);
+      auto issue_s = [&](int j) {                          // S_j = Q K_j^T into buffer j & 1
+        const uint64_t kd = k_desc + (uint64_t)(((uint32_t)(j % STAGES) * G::KV_STAGE) >> 4);
+        const uint32_t d = tmem_s + (uint32_t)((j & 1) * KT);
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks)
+          fa_umma(d, q_desc + (uint64_t)(((ks >> 2) * ATOM_BYTES + (ks & 3) * 32) >> 4),
+                  kd + (uint64_t)(((ks >> 2) * G::KV_HALF + (ks & 3) * 32) >> 4), idesc_s, ks > 0 ? 1u : 0u);
+        fa_commit(s_full0 + 8 * (j & 1));
+      };
       // the queries are written to shared memory by the softmax warps: p_ready's phase 0 announces them
       bool ok = !failed && fa_mbar_wait(p_ready, 0);
       if (!ok) { atomicExch(&g_fa_error, 5); failed = 1; }
-      uint32_t kv_phase = 0;
+      if (ok) {
+        if (fa_mbar_wait(kv_full0, 0)) {
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          issue_s(0);
+        } else { atomicExch(&g_fa_error, 2); failed = 1; ok = false; }
+      }
       for (int j = 0; j < n_tiles && ok; ++j) {
-        const int s = j & 1;
-        if (failed || !fa_mbar_wait(kv_full0 + 8 * s, kv_phase)) { atomicExch(&g_fa_error, 2); failed = 1; break; }
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-        for (int ks = 0; ks < HD / 16; ++ks)
-          fa_umma(tmem_s, desc_k_major(q_sm + (ks >> 2) * ATOM_BYTES + (ks & 3) * 32),
-                  desc_k_major(k_sm + s * G::KV_STAGE + (ks >> 2) * G::KV_HALF + (ks & 3) * 32), idesc_s, ks > 0 ? 1u : 0u);
-        fa_commit(s_full);
+        // the scores of the next tile go out before the softmax of this one is waited for: their buffer was
+        // read last for tile j - 1, whose P this thread has already seen
+        if (j + 1 < n_tiles) {
+          const int sn = (j + 1) % STAGES;
+          if (failed || !fa_mbar_wait(kv_full0 + 8 * sn, (uint32_t)((j + 1) / STAGES) & 1u)) { atomicExch(&g_fa_error, 2); failed = 1; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          issue_s(j + 1);
+        }
         // P of this tile (phase j+1 of p_ready: phase 0 was the queries)
         if (!fa_mbar_wait(p_ready, (uint32_t)(j + 1) & 1u)) { atomicExch(&g_fa_error, 3); failed = 1; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const int s = j % STAGES;
+        const uint64_t vd = v_desc + (uint64_t)(((uint32_t)s * G::KV_STAGE) >> 4);
 #pragma unroll
         for (int kk = 0; kk < KT / 16; ++kk)
-          fa_umma(tmem_o, desc_k_major(p_sm + (kk >> 2) * ATOM_BYTES + (kk & 3) * 32),
-                  desc_mn_major(v_sm + s * G::KV_STAGE + kk * 2048, G::KV_HALF), idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
-        fa_commit(kv_empty0 + 8 * s);
+          fa_umma(tmem_o, p_desc + (uint64_t)(((kk >> 2) * ATOM_BYTES + (kk & 3) * 32) >> 4), vd + (uint64_t)((kk * 2048) >> 4),
+                  idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+        fa_commit(kv_empty0 + 8 * s);                      // K of the stage was read by S_j, V by these
         fa_commit(pv_done);
-        if (s == 1) kv_phase ^= 1;
       }
     }
   } else {
-    // ------------------------------------------------------------- softmax, one thread per row
+    // ------------------------------------------------------------- softmax
+    // FA_SOFTMAX_SPLIT threads share a row: thread (row r, part h) takes columns [h*KT/SPLIT, (h+1)*KT/SPLIT) of S
+    // and [h*HD/SPLIT, ...) of O.  Warps 2-5 are part 0, warps 6-9 part 1; a warp reads the 32 lanes of tensor
+    // memory of quarter warp % 4.  The parts of a row tell each other their maximum (and at the end their sum)
+    // through shared memory: a part writes {value, tag} into the first 8 bytes of the OTHER part's stretch of the
+    // P tile (which that part overwrites with its own P only after it has read them) and polls its own, bounded.
+    constexpr int SPLIT = FA_SOFTMAX_SPLIT;
+    constexpr int SCOLS = KT / SPLIT, OCOLS = HD / SPLIT;
+    static_assert(SCOLS % 32 == 0 && OCOLS % 32 == 0, "a part takes whole loads of 32 columns");
     const int quarter = warp & 3;
+    const int part = (warp - 2) >> 2;
     const int r = quarter * 32 + lane;                    // row of the tile = TMEM lane
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     const int pr = pair0 + r;
@@ -289,12 +323,31 @@ __global__ void __launch_bounds__(FA_THREADS, Geo<HD, KT>::BLOCKS_PER_SM) attent
     const int t = valid ? pr / group : 0;
     const int head = c * group + (valid ? pr - t * group : 0);
     const int limit = valid ? ctx + t : 0x3fffffff;       // last visible key (rows past the end are not stored)
+    const int c_base = part * SCOLS;                      // first S column of this part
+    // where a part's stretch of the P tile begins, for row r
+    auto p_slot = [&](int which) -> unsigned char* {
+      const int col = which * SCOLS;
+      return gen_base + G::P_OFF + (col >> 6) * ATOM_BYTES + sw128(r, (col & 63) >> 3);
+    };
+    // hand `value` to the other part and take its value; false if it never came
+    auto exchange = [&](float value, uint32_t tag, float& other) -> bool {
+      if (SPLIT == 1) { other = value; return true; }
+      asm volatile("st.volatile.shared.v2.b32 [%0], {%1, %2};" ::"r"(saddr(p_slot(part ^ 1))), "r"(__float_as_uint(value)), "r"(tag) : "memory");
+      const uint32_t mine = saddr(p_slot(part));
+      for (unsigned i = 0; i < FA_SPIN_LIMIT; ++i) {
+        uint32_t v, tg;
+        asm volatile("ld.volatile.shared.v2.b32 {%0, %1}, [%2];" : "=r"(v), "=r"(tg) : "r"(mine) : "memory");
+        if (tg == tag) { other = __uint_as_float(v); return true; }
+      }
+      return false;
+    };
 
     // queries -> shared memory in the MMA's swizzle
     {
       const bf16* src = p.q + (size_t)(q0 + t) * p.q_stride + head * HD;
 #pragma unroll
-      for (int ch = 0; ch < HD / 8; ++ch) {
+      for (int cc = 0; cc < HD / 8 / SPLIT; ++cc) {
+        const int ch = part * (HD / 8 / SPLIT) + cc;
         uint4 v = make_uint4(0u, 0u, 0u, 0u);
         if (valid) v = *reinterpret_cast<const uint4*>(src + ch * 8);
         *reinterpret_cast<uint4*>(gen_base + (ch >> 3) * ATOM_BYTES + sw128(r, ch & 7)) = v;
@@ -307,7 +360,7 @@ __global__ void __launch_bounds__(FA_THREADS, Geo<HD, KT>::BLOCKS_PER_SM) attent
     float m = -INFINITY, l = 0.f;
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
-      ok = ok && !failed && fa_mbar_wait(s_full, (uint32_t)j & 1u);
+      ok = ok && !failed && fa_mbar_wait(s_full0 + 8 * (j & 1), (uint32_t)(j >> 1) & 1u);
       if (!ok && lane == 0) { atomicExch(&g_fa_error, 4); failed = 1; }
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0 && !failed;
       if (!ok) break;
@@ -315,26 +368,44 @@ __global__ void __launch_bounds__(FA_THREADS, Geo<HD, KT>::BLOCKS_PER_SM) attent
       const int k0 = j * KT;
       // a tile whose last key every row of the warp may see needs no mask
       const bool interior = __all_sync(0xffffffffu, k0 + KT - 1 <= limit);
-      // scores of the row, 32 at a time, read twice from tensor memory (once for the maximum, once for
-      // the exponentials): 128 scores would not fit the registers beside everything else
+      // this part's scores of the row, 32 at a time, read twice from tensor memory (once for the maximum, once
+      // for the exponentials)
       float mx = -INFINITY;
 #pragma unroll
-      for (int q4 = 0; q4 < KT / 32; ++q4) {
+      for (int q4 = 0; q4 < SCOLS / 32; ++q4) {
         float sc[32];
-        fa_tmem_ld32(tmem_s + lane_addr + q4 * 32, sc);
+        fa_tmem_ld32(tmem_s + lane_addr + (j & 1) * KT + c_base + q4 * 32, sc);
         if (interior) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) mx = fmaxf(mx, sc[i]);
         } else {
 #pragma unroll
           for (int i = 0; i < 32; ++i)
-            if (k0 + q4 * 32 + i <= limit) mx = fmaxf(mx, sc[i]);
+            if (k0 + c_base + q4 * 32 + i <= limit) mx = fmaxf(mx, sc[i]);
         }
+      }
+      // O and the P buffer belong to the MMAs of the tile before until pv_done
+      if (j > 0) {
+        bool ok2 = fa_mbar_wait(pv_done, (uint32_t)(j - 1) & 1u);
+        if (!ok2 && lane == 0) { atomicExch(&g_fa_error, 6); failed = 1; }
+        ok = __shfl_sync(0xffffffffu, ok2 ? 1 : 0, 0) != 0 && !failed;
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      }
+      {
+        float other;
+        bool got = exchange(mx, 0x7fc00000u | (uint32_t)(2 * j + 1), other);
+        if (!__all_sync(0xffffffffu, got)) {
+          if (lane == 0) { atomicExch(&g_fa_error, 9); failed = 1; }
+          ok = false;
+          break;
+        }
+        mx = fmaxf(mx, other);
       }
       // The maximum in use follows the true one only when that has grown by more than 2^8 (or is the
       // first): until then the exponentials are at most 256, which neither bfloat16 nor the float32 sums
       // mind, and O in tensor memory needs no rescaling.  The result is the same: numerator and
-      // denominator carry the same factor.
+      // denominator carry the same factor.  (Both parts of a row see the same maximum and decide alike.)
       const float m_cand = fmaxf(m, mx * p.scale_log2);
       const bool moves = __any_sync(0xffffffffu, m_cand - m > 8.f || (m == -INFINITY && m_cand > -INFINITY));
       float corr = 1.f;
@@ -343,40 +414,32 @@ __global__ void __launch_bounds__(FA_THREADS, Geo<HD, KT>::BLOCKS_PER_SM) attent
         m = m_cand;
       }
       const float ms = m == -INFINITY ? 0.f : m;
-      // O and the P buffer belong to the MMAs of the tile before until pv_done
-      if (j > 0) {
-        bool ok2 = fa_mbar_wait(pv_done, (uint32_t)(j - 1) & 1u);
-        if (!ok2 && lane == 0) { atomicExch(&g_fa_error, 6); failed = 1; }
-        ok = __shfl_sync(0xffffffffu, ok2 ? 1 : 0, 0) != 0 && !failed;
-        if (!ok) break;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (moves) {
+      if (j > 0 && moves) {
 #pragma unroll
-          for (int h = 0; h < HD / 32; ++h) {
-            float o[32];
-            fa_tmem_ld32(tmem_o + lane_addr + h * 32, o);
+        for (int h = 0; h < OCOLS / 32; ++h) {
+          float o[32];
+          fa_tmem_ld32(tmem_o + lane_addr + part * OCOLS + h * 32, o);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] *= corr;
-            fa_tmem_st32(tmem_o + lane_addr + h * 32, o);
-          }
-          asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+          for (int i = 0; i < 32; ++i) o[i] *= corr;
+          fa_tmem_st32(tmem_o + lane_addr + part * OCOLS + h * 32, o);
         }
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       }
       float sum = 0.f;
 #pragma unroll
-      for (int q4 = 0; q4 < KT / 32; ++q4) {
+      for (int q4 = 0; q4 < SCOLS / 32; ++q4) {
         float sc[32];
-        fa_tmem_ld32(tmem_s + lane_addr + q4 * 32, sc);
+        fa_tmem_ld32(tmem_s + lane_addr + (j & 1) * KT + c_base + q4 * 32, sc);
 #pragma unroll
         for (int ch = 0; ch < 4; ++ch) {
           float e[8];
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             const float x = fa_exp2(fmaf(sc[ch * 8 + i], p.scale_log2, -ms));
-            e[i] = (interior || k0 + q4 * 32 + ch * 8 + i <= limit) ? x : 0.f;
+            e[i] = (interior || k0 + c_base + q4 * 32 + ch * 8 + i <= limit) ? x : 0.f;
             sum += e[i];
           }
-          const int col = q4 * 32 + ch * 8;                // key index inside the tile
+          const int col = c_base + q4 * 32 + ch * 8;       // key index inside the tile
           const uint4 v = make_uint4(fa_pack(e[0], e[1]), fa_pack(e[2], e[3]), fa_pack(e[4], e[5]), fa_pack(e[6], e[7]));
           *reinterpret_cast<uint4*>(gen_base + G::P_OFF + (col >> 6) * ATOM_BYTES + sw128(r, (col & 63) >> 3)) = v;
         }
@@ -393,13 +456,24 @@ __global__ void __launch_bounds__(FA_THREADS, Geo<HD, KT>::BLOCKS_PER_SM) attent
       ok = __shfl_sync(0xffffffffu, ok2 ? 1 : 0, 0) != 0 && !failed;
     }
     if (ok) {
+      // the row's sum is the sum of its parts' sums (they used the same maximum)
+      float other;
+      bool got = exchange(l, 0x7fc00000u | (uint32_t)(2 * n_tiles + 2), other);
+      if (!__all_sync(0xffffffffu, got)) {
+        if (lane == 0) { atomicExch(&g_fa_error, 10); failed = 1; }
+        ok = false;
+      } else if (SPLIT > 1) {
+        l += other;
+      }
+    }
+    if (ok) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const float inv = l > 0.f ? 1.f / l : 0.f;
-      bf16* dst = p.out + (size_t)(q0 + t) * p.out_stride + head * HD;
+      bf16* dst = p.out + (size_t)(q0 + t) * p.out_stride + head * HD + part * OCOLS;
 #pragma unroll
-      for (int h = 0; h < HD / 32; ++h) {
+      for (int h = 0; h < OCOLS / 32; ++h) {
         float o[32];
-        fa_tmem_ld32(tmem_o + lane_addr + h * 32, o);
+        fa_tmem_ld32(tmem_o + lane_addr + part * OCOLS + h * 32, o);
         if (valid) {
 #pragma unroll
           for (int ch = 0; ch < 4; ++ch) {
@@ -462,11 +536,10 @@ extern "C" int ie_attention_tcgen05_error() {
 }
 
 // keys of a tile for a head size (0: not taken)
-// (key tiles of 64 at head size 64 would fit three blocks to an SM: measured 64 us against 55 us at 2,048 tokens)
-static int fa_key_tile(int hd) { return hd == 64 ? 128 : (hd == 128 ? 64 : 0); }
+static int fa_key_tile(int hd) { return (hd == 64 || hd == 128) ? 64 : 0; }
 
 // 1 if the kernel takes the geometry: head size 64 or 128, pages of at least 8 keys, a power of two, that divide a
-// key tile (128 keys at head size 64, 64 keys at head size 128); no window
+// key tile (64 keys); no window
 extern "C" int ie_attention_tcgen05_supports(int hd, int page_size, int window) {
   const int kt = fa_key_tile(hd);
   if (!kt || window > 0) return 0;
@@ -474,17 +547,17 @@ extern "C" int ie_attention_tcgen05_supports(int hd, int page_size, int window) 
   return 1;
 }
 
-template <int HD, int KT>
+template <int HD, int KT, int STAGES>
 static int fa_launch(const CUtensorMap& mk, const CUtensorMap& mv, const FaParams& p, int n_work, int n_kv_heads,
                      cudaStream_t stream) {
-  const size_t smem = Geo<HD, KT>::TILES_BYTES + 128;
+  const size_t smem = Geo<HD, KT, STAGES>::TILES_BYTES + 128;
   static bool attr = false;
   if (!attr) {
-    cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel<HD, KT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel<HD, KT, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     attr = true;
   }
-  return launch_k(attention_tcgen05_kernel<HD, KT>, dim3((unsigned)((long long)n_work * n_kv_heads)), FA_THREADS, smem,
+  return launch_k(attention_tcgen05_kernel<HD, KT, STAGES>, dim3((unsigned)((long long)n_work * n_kv_heads)), FA_THREADS, smem,
                   stream, mk, mv, p);
 }
 
@@ -514,6 +587,6 @@ extern "C" int ie_attention_tcgen05(const void* q, void* out, const void* kpool,
   p.page_shift = 0;
   while ((1 << p.page_shift) < page_size) ++p.page_shift;
   p.scale_log2 = scale * LOG2E;
-  if (hd == 64) return fa_launch<64, 128>(mk, mv, p, n_work, n_kv_heads, stream);
-  return fa_launch<128, 64>(mk, mv, p, n_work, n_kv_heads, stream);
+  if (hd == 64) return fa_launch<64, 64, 4>(mk, mv, p, n_work, n_kv_heads, stream);
+  return fa_launch<128, 64, 2>(mk, mv, p, n_work, n_kv_heads, stream);
 }

@@ -425,7 +425,11 @@ _fa5_lib = None
 def attention_tcgen05_library():
     global _fa5_lib
     if _fa5_lib is None:
-        lib = load_library("attn_tcgen05", ["attention_tcgen05.cu"])
+        defines = {}
+        for item in filter(None, os.environ.get("IE_FA_DEFINES", "").split(",")):
+            name, _, value = item.partition("=")
+            defines[name.strip()] = int(value)
+        lib = load_library("attn_tcgen05", ["attention_tcgen05.cu"], defines)
         P, I = c_void_p, c_int
         lib.ie_attention_tcgen05.argtypes = [P] * 9 + [I] * 9 + [c_float, P]
         lib.ie_attention_tcgen05.restype = c_int

@@ -423,7 +423,7 @@ TCGEN05_ATTENTION_CASES = [
     (4, 4, 64, 16, [17, 1, 64, 300], [3, 300, 64, 0]),
     (3, 1, 64, 32, [5, 166], [11, 200]),
     (8, 1, 64, 64, [129, 2], [127, 1000]),
-    (2, 2, 64, 128, [3, 150, 257], [9, 40, 0]),
+    (2, 2, 64, 64, [3, 150, 257], [9, 40, 0]),
     (8, 2, 128, 16, [200], [0]),
     (6, 2, 128, 8, [1, 9, 1, 70, 130], [70, 0, 129, 31, 515]),
     (3, 3, 128, 32, [17, 1, 300], [3, 300, 64]),
@@ -469,6 +469,7 @@ def test_attention_tcgen05_finds_one_far_key_among_hundreds(hd):
 def test_attention_tcgen05_refuses_what_it_cannot_do():
     assert not k().attention_tcgen05_supports(96, 16, None)
     assert not k().attention_tcgen05_supports(128, 128, None)
+    assert not k().attention_tcgen05_supports(64, 128, None)
     assert not k().attention_tcgen05_supports(64, 4, None)
     assert not k().attention_tcgen05_supports(64, 16, 32)
 
