@@ -68,6 +68,11 @@ struct FaParams {
   int q_stride, out_stride, table_stride;
   int n_heads, n_kv_heads, page_size, page_shift, n_work;
   float scale_log2;
+  // q arrives unrotated when these are given: cos / sin tables [positions, HD/2] float32 and each token's position
+  // (rotation in pairs (i, i + HD/2), engine/layers.py:82-115 of the reference)
+  const float* cos_t;
+  const float* sin_t;
+  const int* positions;
 };
 
 __device__ __forceinline__ uint32_t saddr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -342,15 +347,46 @@ __global__ void __launch_bounds__(FA_THREADS, Geo<HD, KT, STAGES>::BLOCKS_PER_SM
       return false;
     };
 
-    // queries -> shared memory in the MMA's swizzle
+    // queries -> shared memory in the MMA's swizzle, rotated on the way if they arrive unrotated
     {
       const bf16* src = p.q + (size_t)(q0 + t) * p.q_stride + head * HD;
+      constexpr int NCH = HD / 8 / SPLIT;                  // 16-byte chunks of the row that this thread stages
+      if (p.cos_t != nullptr && SPLIT == 1) {
+        const int pos = valid ? p.positions[q0 + t] : 0;
+        const float* cr = p.cos_t + (size_t)pos * (HD / 2);
+        const float* sr = p.sin_t + (size_t)pos * (HD / 2);
 #pragma unroll
-      for (int cc = 0; cc < HD / 8 / SPLIT; ++cc) {
-        const int ch = part * (HD / 8 / SPLIT) + cc;
-        uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        if (valid) v = *reinterpret_cast<const uint4*>(src + ch * 8);
-        *reinterpret_cast<uint4*>(gen_base + (ch >> 3) * ATOM_BYTES + sw128(r, ch & 7)) = v;
+        for (int ch = 0; ch < HD / 16; ++ch) {             // chunk ch holds dims 8 ch .., its partners are chunk ch + HD/16
+          uint4 lo = make_uint4(0u, 0u, 0u, 0u), hi = lo;
+          if (valid) {
+            lo = *reinterpret_cast<const uint4*>(src + ch * 8);
+            hi = *reinterpret_cast<const uint4*>(src + HD / 2 + ch * 8);
+            const float4 c0 = *reinterpret_cast<const float4*>(cr + ch * 8), c1 = *reinterpret_cast<const float4*>(cr + ch * 8 + 4);
+            const float4 s0 = *reinterpret_cast<const float4*>(sr + ch * 8), s1 = *reinterpret_cast<const float4*>(sr + ch * 8 + 4);
+            const float cc[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+            const float ss[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+            uint32_t* lw = reinterpret_cast<uint32_t*>(&lo);
+            uint32_t* hw = reinterpret_cast<uint32_t*>(&hi);
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+              const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&lw[w]));
+              const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&hw[w]));
+              lw[w] = fa_pack(a.x * cc[2 * w] - b.x * ss[2 * w], a.y * cc[2 * w + 1] - b.y * ss[2 * w + 1]);
+              hw[w] = fa_pack(b.x * cc[2 * w] + a.x * ss[2 * w], b.y * cc[2 * w + 1] + a.y * ss[2 * w + 1]);
+            }
+          }
+          const int ch_hi = ch + HD / 16;
+          *reinterpret_cast<uint4*>(gen_base + (ch >> 3) * ATOM_BYTES + sw128(r, ch & 7)) = lo;
+          *reinterpret_cast<uint4*>(gen_base + (ch_hi >> 3) * ATOM_BYTES + sw128(r, ch_hi & 7)) = hi;
+        }
+      } else {
+#pragma unroll
+        for (int cc = 0; cc < NCH; ++cc) {
+          const int ch = part * NCH + cc;
+          uint4 v = make_uint4(0u, 0u, 0u, 0u);
+          if (valid) v = *reinterpret_cast<const uint4*>(src + ch * 8);
+          *reinterpret_cast<uint4*>(gen_base + (ch >> 3) * ATOM_BYTES + sw128(r, ch & 7)) = v;
+        }
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> visible to the tensor core
       __syncwarp();
@@ -562,13 +598,16 @@ static int fa_launch(const CUtensorMap& mk, const CUtensorMap& mv, const FaParam
 }
 
 // The work list cuts each request's (token, head-in-group) rows into tiles of 128; n_pool_pages is the
-// number of pages of kpool / vpool ([pages, kv_heads, page_size, hd]).
+// number of pages of kpool / vpool; with cos_t / sin_t / positions q arrives unrotated and is rotated as it is read ([pages, kv_heads, page_size, hd]).
 extern "C" int ie_attention_tcgen05(const void* q, void* out, const void* kpool, const void* vpool,
                                     const int* block_table, const int* q_start, const int* ctx_before,
                                     const int* work_req, const int* work_pair0, int q_stride, int out_stride,
                                     int table_stride, int n_work, int n_heads, int n_kv_heads, int hd, int page_size,
-                                    int n_pool_pages, float scale, cudaStream_t stream) {
+                                    int n_pool_pages, float scale, const float* cos_t, const float* sin_t,
+                                    const int* positions, cudaStream_t stream) {
   if (n_work <= 0) return IE_OK;
+  if ((cos_t == nullptr) != (sin_t == nullptr) || (cos_t && !positions)) return IE_BAD_SIZE;
+  if (cos_t && (FA_SOFTMAX_SPLIT != 1 || (((uintptr_t)cos_t | (uintptr_t)sin_t) & 15))) return IE_BAD_ALIGN;
   if (!ie_attention_tcgen05_supports(hd, page_size, 0)) return IE_BAD_SIZE;
   if (n_kv_heads <= 0 || n_heads % n_kv_heads || n_pool_pages <= 0) return IE_BAD_SIZE;
   if (((uintptr_t)q | (uintptr_t)out | (uintptr_t)kpool | (uintptr_t)vpool) & 15) return IE_BAD_ALIGN;
@@ -587,6 +626,7 @@ extern "C" int ie_attention_tcgen05(const void* q, void* out, const void* kpool,
   p.page_shift = 0;
   while ((1 << p.page_shift) < page_size) ++p.page_shift;
   p.scale_log2 = scale * LOG2E;
+  p.cos_t = cos_t; p.sin_t = sin_t; p.positions = positions;
   if (hd == 64) return fa_launch<64, 64, 4>(mk, mv, p, n_work, n_kv_heads, stream);
   return fa_launch<128, 64, 2>(mk, mv, p, n_work, n_kv_heads, stream);
 }

@@ -219,7 +219,8 @@ __global__ void rope_kv_write_kernel(TA* __restrict__ q, const TA* __restrict__ 
   const float* c = cos_t ? cos_t + (size_t)pos * half : nullptr;
   const float* s = sin_t ? sin_t + (size_t)pos * half : nullptr;
   TA* qrow = q + (size_t)n * q_stride;
-  for (int idx = threadIdx.x; idx < n_heads * half; idx += blockDim.x) {
+  const int q_pairs = (write_kv & 2) ? 0 : n_heads * half;      // bit 1: q is rotated elsewhere
+  for (int idx = threadIdx.x; idx < q_pairs; idx += blockDim.x) {
     const int h = idx / half, i = idx - h * half;
     TA* x = qrow + h * hd;
     const float a = to_f32(x[i]), b = to_f32(x[i + half]);
@@ -227,7 +228,7 @@ __global__ void rope_kv_write_kernel(TA* __restrict__ q, const TA* __restrict__ 
     x[i] = from_f32<TA>(a * cc - b * ss);
     x[i + half] = from_f32<TA>(b * cc + a * ss);
   }
-  if (!write_kv) return;
+  if (!(write_kv & 1)) return;
   const int slot = slot_mapping[n];
   if (slot < 0) return;
   const int page = slot / page_size, off = slot - page * page_size;
@@ -258,10 +259,11 @@ __global__ void rope_kv_write_bf16_vec_kernel(bf16* __restrict__ q, const bf16* 
   const int half = hd >> 1;
   const int groups = half >> 3;                 // groups of eight pairs per head
   const int pos = positions[n];
-  const int slot = write_kv ? slot_mapping[n] : -1;
+  const int slot = (write_kv & 1) ? slot_mapping[n] : -1;
   const int page = slot >= 0 ? slot / page_size : 0, off = slot >= 0 ? slot - page * page_size : 0;
   const int total = (n_heads + n_kv_heads) * groups;
-  for (int idx = threadIdx.x; idx < total; idx += blockDim.x) {
+  const int first = (write_kv & 2) ? n_heads * groups : 0;     // bit 1: q is rotated elsewhere
+  for (int idx = first + threadIdx.x; idx < total; idx += blockDim.x) {
     const int h = idx / groups, i = (idx - h * groups) * 8;
     float cc[8], ss[8];
     if (cos_t) {
@@ -305,6 +307,8 @@ __global__ void rope_kv_write_bf16_vec_kernel(bf16* __restrict__ q, const bf16* 
   }
 }
 
+// write_kv: bit 0: store the rotated key and the value at slot_mapping; bit 1: leave q alone (it is rotated
+// where it is read)
 extern "C" int ie_rope_kv_write(void* q, const void* k, const void* v, int q_stride, int kv_stride,
                                 const float* cos_t, const float* sin_t, const int* positions,
                                 const int* slot_mapping, void* kpool, void* vpool, int n_tokens, int n_heads,

@@ -131,8 +131,9 @@ def residual_add(residual: torch.Tensor, delta: torch.Tensor) -> None:
 def rope_kv_write(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cos: torch.Tensor | None,
                   sin: torch.Tensor | None, positions: torch.Tensor, slot_mapping: torch.Tensor | None,
                   kpool: torch.Tensor | None, vpool: torch.Tensor | None, n_heads: int, n_kv_heads: int,
-                  head_dim: int, page_size: int) -> None:
-    """Rotate q in place; write rotated k and raw v into their page slots (if pools are given).
+                  head_dim: int, page_size: int, rotate_q: bool = True) -> None:
+    """Rotate q in place (unless ``rotate_q`` is off: the attention kernel then rotates it as it reads it);
+    write rotated k and raw v into their page slots (if pools are given).
 
     q, k, v are row-strided views [n, heads*head_dim] (columns of one fused buffer, for instance).
     """
@@ -141,7 +142,8 @@ def rope_kv_write(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cos: torch.
     write = kpool is not None
     _check(core().ie_rope_kv_write(_ptr(q), _ptr(k), _ptr(v), q.stride(0), k.stride(0), _ptr(cos), _ptr(sin),
                                    _ptr(positions), _ptr(slot_mapping), _ptr(kpool), _ptr(vpool), n, n_heads,
-                                   n_kv_heads, head_dim, page_size, 1 if write else 0, dtype_code(q.dtype),
+                                   n_kv_heads, head_dim, page_size, (1 if write else 0) | (0 if rotate_q else 2),
+                                   dtype_code(q.dtype),
                                    _stream()), "rope_kv_write")
 
 
@@ -431,7 +433,7 @@ def attention_tcgen05_library():
             defines[name.strip()] = int(value)
         lib = load_library("attn_tcgen05", ["attention_tcgen05.cu"], defines)
         P, I = c_void_p, c_int
-        lib.ie_attention_tcgen05.argtypes = [P] * 9 + [I] * 9 + [c_float, P]
+        lib.ie_attention_tcgen05.argtypes = [P] * 9 + [I] * 9 + [c_float, P, P, P, P]
         lib.ie_attention_tcgen05.restype = c_int
         lib.ie_attention_tcgen05_supports.argtypes = [I, I, I]
         lib.ie_attention_tcgen05_supports.restype = c_int
@@ -450,16 +452,18 @@ def attention_tcgen05_error() -> int:
 
 
 def attention_tcgen05(q, out, kpool, vpool, block_table, q_start, ctx_before, work_req, work_pair0, n_work,
-                      n_heads, n_kv_heads, head_dim, page_size, scale) -> None:
+                      n_heads, n_kv_heads, head_dim, page_size, scale, cos=None, sin=None, positions=None) -> None:
     """Causal paged attention for prompt portions with tcgen05 tensor cores; bfloat16, head size 64 or 128;
     the work list cuts each request's (token, head-in-group) rows into tiles of 128.  ``kpool``/``vpool``
-    are one layer's pages, [pages, kv_heads, page_size, head_dim], contiguous."""
+    are one layer's pages, [pages, kv_heads, page_size, head_dim], contiguous.  With ``cos``/``sin`` (float32
+    [positions, head_dim/2]) and ``positions`` (int32 per token) q arrives unrotated and is rotated as read."""
     assert q.dtype is torch.bfloat16 and q.stride(1) == 1 and out.stride(1) == 1
     assert kpool.is_contiguous() and vpool.is_contiguous() and kpool.dim() == 4
     _check(attention_tcgen05_library().ie_attention_tcgen05(
         _ptr(q), _ptr(out), _ptr(kpool), _ptr(vpool), _ptr(block_table), _ptr(q_start), _ptr(ctx_before),
         _ptr(work_req), _ptr(work_pair0), q.stride(0), out.stride(0), block_table.stride(0), n_work, n_heads,
-        n_kv_heads, head_dim, page_size, kpool.shape[0], float(scale), _stream()), "attention_tcgen05")
+        n_kv_heads, head_dim, page_size, kpool.shape[0], float(scale), _ptr(cos), _ptr(sin), _ptr(positions),
+        _stream()), "attention_tcgen05")
 
 
 def check_device_errors() -> None:

@@ -118,18 +118,31 @@ class PagedAttention:
         if tables is None:
             self.position.rotate(q, k, ctx)
         cos, sin = tables if tables is not None else (None, None)
+        # a step of prompt portions only, on the tcgen05 kernel: q is rotated where that kernel reads it
+        q_in_kernel = tables is not None and self._portions_only_on_tcgen05(ctx)
         kernels.rope_kv_write(q, k, v, cos, sin, ctx.positions, kvctx.slot_mapping,
                               cache.k if cache.write else None, cache.v if cache.write else None,
-                              s.n_heads, s.n_kv_heads, s.head_dim, ctx.page_size)
-        self._attend(q, out, cache, ctx, kvctx)
+                              s.n_heads, s.n_kv_heads, s.head_dim, ctx.page_size, rotate_q=not q_in_kernel)
+        self._attend(q, out, cache, ctx, kvctx, (cos, sin, ctx.positions) if q_in_kernel else (None, None, None))
         return out
+
+    def _portions_only_on_tcgen05(self, ctx) -> bool:
+        s = self.spec
+        group = s.n_heads // s.n_kv_heads
+        if not (self.rt.act_dtype is torch.bfloat16 and s.head_dim in kernels.MMA_HEAD_DIMS):
+            return False
+        if ctx.max_q_len * group < TCGEN05_MIN_ROWS or ctx.max_q_len * group <= 16:
+            return False
+        if not kernels.attention_tcgen05_supports(s.head_dim, ctx.page_size, s.window):
+            return False
+        return ctx.keys_of_small_requests(group, 16)[0] == 0
 
     def _decode_scratch(self, ctx, n_splits: int) -> torch.Tensor:
         s = self.spec
         n = kernels.attention_decode_scratch_floats(ctx.n_tokens, s.n_heads, n_splits, s.head_dim)
         return self.rt.ws.take("attn_scratch", (n,), torch.float32)   # zero when made; tickets stay zero
 
-    def _attend(self, q, out, cache, ctx, kvctx) -> None:
+    def _attend(self, q, out, cache, ctx, kvctx, rotate=(None, None, None)) -> None:
         s = self.spec
         group = s.n_heads // s.n_kv_heads
         if self.rt.act_dtype is torch.bfloat16 and s.head_dim in kernels.MMA_HEAD_DIMS:
@@ -157,7 +170,7 @@ class PagedAttention:
                 work_req, work_pair0, n_work = ctx.attention_work(group, 128, more_than)
                 kernels.attention_tcgen05(q, out, cache.k, cache.v, kvctx.block_table, ctx.q_start, ctx.ctx_before,
                                           work_req, work_pair0, n_work, s.n_heads, s.n_kv_heads, s.head_dim,
-                                          ctx.page_size, self.scale)
+                                          ctx.page_size, self.scale, *rotate)
             else:
                 rows = 64      # tiles of 128 rows (8 warps) leave one block per SM at this register count: slower
                 work_req, work_pair0, n_work = ctx.attention_work(group, rows, more_than)

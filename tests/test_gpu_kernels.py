@@ -450,6 +450,37 @@ def test_attention_prefill_tcgen05(case):
 
 
 @pytest.mark.parametrize("hd", [64, 128])
+def test_attention_tcgen05_rotates_q_as_it_reads_it(hd):
+    """q arrives unrotated with tables and positions; the result equals attention over q rotated on the host."""
+    H, Hk, ps, act = 6, 2, 16, torch.bfloat16
+    q_lens, ctx_before = [140, 50], [37, 300]
+    c = paged_case(act, H, Hk, hd, ps, q_lens, ctx_before, seed=21 + hd)
+    half = hd // 2
+    g = torch.Generator().manual_seed(3)
+    n_pos = max(a + b for a, b in zip(q_lens, ctx_before))
+    ang = torch.rand(n_pos, half, generator=g) * 6.28
+    cos, sin = ang.cos(), ang.sin()
+    positions = [cb + i for ql, cb in zip(q_lens, ctx_before) for i in range(ql)]
+    q_raw = c["q"]                                              # bfloat16-rounded values
+    qr = q_raw.view(-1, H, hd)
+    cc, ss = cos[positions][:, None, :], sin[positions][:, None, :]
+    a, b = qr[..., :half], qr[..., half:]
+    q_rot = torch.cat([a * cc - b * ss, b * cc + a * ss], dim=-1).to(act).float().view(-1, H * hd)
+    ref = paged_reference(q_rot, c["kd"], c["vd"], q_lens, ctx_before, H, Hk, hd, None)
+    req, pair0 = work_list(q_lens, H // Hk, 128)
+    dev = lambda t: torch.as_tensor(t, dtype=torch.int32).to(DEV)
+    out = torch.full((c["N"], H * hd), float("nan"), device=DEV, dtype=act)
+    qd = q_raw.to(DEV, act)
+    k().attention_tcgen05(qd, out, c["kpool"].to(DEV, act), c["vpool"].to(DEV, act), c["table"].to(DEV),
+                          dev(c["q_start"]), dev(ctx_before), dev(req), dev(pair0), len(req), H, Hk, hd, ps, hd ** -0.5,
+                          cos.to(DEV), sin.to(DEV), dev(positions))
+    torch.cuda.synchronize()
+    assert k().attention_tcgen05_error() == 0
+    assert torch.allclose(out.float().cpu(), ref, **tol(act))
+    assert torch.equal(qd.float().cpu(), q_raw)                 # q itself is left as it came
+
+
+@pytest.mark.parametrize("hd", [64, 128])
 def test_attention_tcgen05_finds_one_far_key_among_hundreds(hd):
     H, Hk, ps, act = 4, 2, 16, torch.bfloat16
     q_lens, ctx_before = [140, 6], [700, 420]
