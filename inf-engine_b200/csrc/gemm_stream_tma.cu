@@ -122,78 +122,77 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// What a block's roles share: the ring of stages (slots `slot_bytes` apart, so that products with different stage
+// shapes can follow one another through the same ring), its barriers, and scratch for the consumers.
+struct BlockCtx {
+  unsigned char* smem;      // dynamic shared memory: the ring, then the staged activations
+  uint32_t ring;            // its shared-memory address
+  uint32_t slot_bytes;      // distance between stages
+  uint32_t x_off;           // offset of the staged activations
+  uint32_t full0, empty0;   // addresses of the barrier arrays
+  int n_stages;
+  float* red;               // [2 or 4][CONSUMER_WARPS][4 * NT][32]
+  float* inv_rms;           // [16]
+  volatile int* failed;
+};
+struct RingPos {
+  int s;
+  uint32_t phase;
+};
+
+// ------------------------------------------------------------- producer (one warp)
+// lane 0 waits for the stage and arms its barrier; then lane r issues the copy of weight row r, so that the copies of
+// a stage are issued side by side rather than one after the other.  nt: units of 8 * nt rows.
+__device__ __forceinline__ bool produce(const TmaParams& p, int nt, const BlockCtx& b, RingPos& pos, int lane) {
+  const int unit_rows = 8 * nt;
+  const int n_units = (p.N + unit_rows - 1) / unit_rows;
+  const int k_stages = p.K / p.ks;
+  const uint32_t w_pitch = (uint32_t)p.ks * 2 + ROW_PAD;
+  bool ok = true;
+  const uint32_t row_bytes = (uint32_t)p.ks * 2;
+  const uint64_t pol = l2_evict_first_policy();
+  for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
+    const int n0 = u * unit_rows;
+    const int rows = min(unit_rows, p.N - n0);
+    const bf16* src = p.W + (size_t)(n0 + (lane < rows ? lane : 0)) * p.ldw;
+    for (int ksi = 0; ksi < k_stages; ++ksi) {
+      const uint32_t bar = b.full0 + 8 * pos.s;
+      if (lane == 0) {
+        ok = mbar_wait(b.empty0 + 8 * pos.s, pos.phase ^ 1);
+        if (ok) mbar_expect_tx(bar, row_bytes * rows);
+      }
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (!ok) break;
+      if (lane < rows) bulk_copy(b.ring + pos.s * b.slot_bytes + lane * w_pitch, src + (size_t)ksi * p.ks, row_bytes, bar, pol);
+      if (++pos.s == b.n_stages) { pos.s = 0; pos.phase ^= 1; }
+    }
+  }
+  return ok;
+}
+
+// ------------------------------------------------------------- consumers (eight warps)
 // NT: 8*NT weight rows per unit (NT n-tiles of the MMA per warp)
 // XS: activations staged in shared memory (true) or read from L2 per stage (false; plain prologue only)
+// first: this product is the kernel's first: its consumers wait for the kernel ahead (after asking for the gain)
 template <int NT, int PRO, int EPI, bool XS>
-// Units of 8 rows (short products: qkv, output) keep within 112 registers, so that the kernel behind them in
-// the stream (decode attention, say) finds room on the SM and starts its own fetches early.
-__global__ void __launch_bounds__(THREADS, NT == 1 ? 2 : 1) gemm_stream_tma_kernel(TmaParams p) {
+__device__ __forceinline__ void consume(const TmaParams& p, const BlockCtx& b, RingPos& pos, bool first, unsigned int trace_id) {
   constexpr int UNIT_ROWS = 8 * NT;
-  extern __shared__ __align__(128) unsigned char smem[];
-  __shared__ __align__(8) unsigned long long bars[2 * MAX_STAGES];   // full[], empty[]
-  __shared__ float red[2][CONSUMER_WARPS][4 * NT][32];
-  __shared__ float inv_rms[16];
-  __shared__ volatile int failed;
-
-  pdl_trigger();
-  TRACE_BEGIN();
-  TRACE(0);                                                  // entry
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n_units = (p.N + UNIT_ROWS - 1) / UNIT_ROWS;
   const int k_stages = p.K / p.ks;
   const uint32_t w_pitch = (uint32_t)p.ks * 2 + ROW_PAD;
-  const uint32_t stage_bytes = UNIT_ROWS * w_pitch;
+  const uint32_t stage_bytes = b.slot_bytes;
   const uint32_t x_pitch = (uint32_t)p.K * 2 + ROW_PAD;
-  const uint32_t ring = smem_addr(smem);
-  const uint32_t xs = ring + p.n_stages * stage_bytes;
-  const uint32_t full0 = smem_addr(&bars[0]), empty0 = smem_addr(&bars[MAX_STAGES]);
-
-  if (tid == 0) {
-    failed = 0;
-    for (int s = 0; s < p.n_stages; ++s) {
-      mbar_init(full0 + 8 * s, 1);
-      mbar_init(empty0 + 8 * s, CONSUMER_WARPS);
-    }
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  __syncthreads();
-
-  if (warp == CONSUMER_WARPS) {
-    // ------------------------------------------------------------- producer
-    // lane 0 waits for the stage and arms its barrier; then lane r issues the copy of weight row r,
-    // so that the copies of a stage are issued side by side rather than one after the other
-    int s = 0;
-    uint32_t phase = 0;
-    bool ok = true;
-    const uint32_t row_bytes = (uint32_t)p.ks * 2;
-    const uint64_t pol = l2_evict_first_policy();
-    for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
-      const int n0 = u * UNIT_ROWS;
-      const int rows = min(UNIT_ROWS, p.N - n0);
-      const bf16* src = p.W + (size_t)(n0 + (lane < rows ? lane : 0)) * p.ldw;
-      for (int ksi = 0; ksi < k_stages; ++ksi) {
-        const uint32_t bar = full0 + 8 * s;
-        if (lane == 0) {
-          ok = mbar_wait(empty0 + 8 * s, phase ^ 1);
-          if (ok) mbar_expect_tx(bar, row_bytes * rows);
-        }
-        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-        if (!ok) break;
-        if (lane < rows) bulk_copy(ring + s * stage_bytes + lane * w_pitch, src + (size_t)ksi * p.ks, row_bytes, bar, pol);
-        if (++s == p.n_stages) { s = 0; phase ^= 1; }
-      }
-    }
-    if (!ok && lane == 0) {
-      atomicExch(&g_stream_error, 1);
-      failed = 1;
-      // copies already issued land in this block's shared memory: stay a bounded while before leaving
-      for (int i = 0; i < 4096; ++i) __nanosleep(64);
-    }
-    pdl_wait();
-    return;
-  }
-
-  // --------------------------------------------------------------- consumers
+  const uint32_t ring = b.ring;
+  const uint32_t xs = ring + b.x_off;
+  const uint32_t full0 = b.full0, empty0 = b.empty0;
+  unsigned char* const smem = b.smem;
+  volatile int& failed = *b.failed;
+  float* const inv_rms = b.inv_rms;
+  float (*red)[CONSUMER_WARPS][4 * NT][32] = reinterpret_cast<float (*)[CONSUMER_WARPS][4 * NT][32]>(b.red);
+  int& s = pos.s;
+  uint32_t& phase = pos.phase;
+  (void)trace_id;
   TRACE(1);                                                  // barriers set up
   // The norm's gain does not depend on the kernel ahead, and it is cold (read once a step, long evicted): it
   // comes from HBM, behind the weights that every producer is streaming.  Ask for it before waiting.
@@ -206,13 +205,13 @@ __global__ void __launch_bounds__(THREADS, NT == 1 ? 2 : 1) gemm_stream_tma_kern
         asm volatile("ld.global.nc.v2.u32 {%0,%1}, [%2];" : "=r"(gpre[i].x), "=r"(gpre[i].y)
                      : "l"((const bf16*)p.gain + lane * 4 + i * 128));
   }
-  pdl_wait();
+  if (first) pdl_wait();
   TRACE(2);                                                  // the kernel ahead has finished
   const int g = lane >> 2, t = lane & 3;
   // activations -> shared memory, once per block (plain activations of a long K stay in L2 instead:
   // they would crowd the ring out of shared memory)
   if (XS) {
-    unsigned char* xsm = smem + p.n_stages * stage_bytes;
+    unsigned char* xsm = smem + b.x_off;
     for (int m = warp; m < p.x_rows; m += CONSUMER_WARPS) {
       bf16* dst = reinterpret_cast<bf16*>(xsm + (size_t)m * x_pitch);
       if (m >= p.M) {
@@ -279,8 +278,6 @@ __global__ void __launch_bounds__(THREADS, NT == 1 ? 2 : 1) gemm_stream_tma_kern
   const int kw = warp * (p.ks / CONSUMER_WARPS);        // this warp's k offset inside a stage
   const int chunks = p.ks / (CONSUMER_WARPS * 32);      // 32-wide chunks per warp per stage
   const bool two = p.x_rows > 8;
-  int s = 0;
-  uint32_t phase = 0;
   int parity = 0;
   bool dead = false;   // after a timed-out wait a warp stops waiting and computing but still meets every barrier
   for (int u = blockIdx.x; u < n_units; u += gridDim.x) {
@@ -301,8 +298,8 @@ __global__ void __launch_bounds__(THREADS, NT == 1 ? 2 : 1) gemm_stream_tma_kern
 #pragma unroll
         for (int u = 0; u < (XS ? 1 : 8); ++u) {
           const int c = min(u, chunks - 1);
-          xg0[u] = *reinterpret_cast<const uint4*>(xa + c * 32);
-          xg1[u] = two ? *reinterpret_cast<const uint4*>(xb + c * 32) : make_uint4(0u, 0u, 0u, 0u);
+          xg0[u] = __ldcg(reinterpret_cast<const uint4*>(xa + c * 32));
+          xg1[u] = two ? __ldcg(reinterpret_cast<const uint4*>(xb + c * 32)) : make_uint4(0u, 0u, 0u, 0u);
           if (!va) xg0[u] = make_uint4(0u, 0u, 0u, 0u);
           if (!vb) xg1[u] = make_uint4(0u, 0u, 0u, 0u);
         }
@@ -343,7 +340,7 @@ __global__ void __launch_bounds__(THREADS, NT == 1 ? 2 : 1) gemm_stream_tma_kern
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(empty0 + 8 * s);
-      if (++s == p.n_stages) { s = 0; phase ^= 1; }
+      if (++s == b.n_stages) { s = 0; phase ^= 1; }
     }
     // partial sums of the four warps, added in warp order
 #pragma unroll
@@ -390,6 +387,60 @@ __global__ void __launch_bounds__(THREADS, NT == 1 ? 2 : 1) gemm_stream_tma_kern
     parity ^= 1;
   }
   TRACE(6);                                                  // last unit stored
+}
+
+// One product per launch.
+template <int NT, int PRO, int EPI, bool XS>
+// Units of 8 rows (short products: qkv, output) keep within 112 registers, so that the kernel behind them in
+// the stream (decode attention, say) finds room on the SM and starts its own fetches early.
+__global__ void __launch_bounds__(THREADS, NT == 1 ? 2 : 1) gemm_stream_tma_kernel(TmaParams p) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ __align__(8) unsigned long long bars[2 * MAX_STAGES];   // full[], empty[]
+  __shared__ float red[2][CONSUMER_WARPS][4 * NT][32];
+  __shared__ float inv_rms[16];
+  __shared__ volatile int failed;
+
+  pdl_trigger();
+  TRACE_BEGIN();
+  TRACE(0);                                                  // entry
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  BlockCtx b;
+  b.smem = smem;
+  b.ring = smem_addr(smem);
+  b.slot_bytes = (uint32_t)(8 * NT) * ((uint32_t)p.ks * 2 + ROW_PAD);
+  b.x_off = p.n_stages * b.slot_bytes;
+  b.full0 = smem_addr(&bars[0]);
+  b.empty0 = smem_addr(&bars[MAX_STAGES]);
+  b.n_stages = p.n_stages;
+  b.red = &red[0][0][0][0];
+  b.inv_rms = inv_rms;
+  b.failed = &failed;
+  if (tid == 0) {
+    failed = 0;
+    for (int s = 0; s < p.n_stages; ++s) {
+      mbar_init(b.full0 + 8 * s, 1);
+      mbar_init(b.empty0 + 8 * s, CONSUMER_WARPS);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  RingPos pos = {0, 0};
+  if (warp == CONSUMER_WARPS) {
+    const bool ok = produce(p, NT, b, pos, lane);
+    if (!ok && lane == 0) {
+      atomicExch(&g_stream_error, 1);
+      failed = 1;
+      // copies already issued land in this block's shared memory: stay a bounded while before leaving
+      for (int i = 0; i < 4096; ++i) __nanosleep(64);
+    }
+    pdl_wait();
+    return;
+  }
+#ifdef IE_STREAM_TRACE
+  consume<NT, PRO, EPI, XS>(p, b, pos, true, trace_id);
+#else
+  consume<NT, PRO, EPI, XS>(p, b, pos, true, 0u);
+#endif
 }
 
 template <int NT, int PRO, int EPI, bool XS>
@@ -467,12 +518,16 @@ extern "C" int ie_gemm_stream_tma(const void* A, const void* W, void* C, const v
   p.M = M; p.N = N; p.K = K; p.lda = lda; p.ldw = ldw; p.ldc = ldc;
   p.gain_is_f32 = gain_dtype == IE_F32; p.eps = eps;
   // units of 16 rows when that still gives every SM several units; a stage is 8 KB..16 KB per 8 rows
-  const int nt = (N >= 16 * 4 * n_sms) ? 2 : 1;
-  const int unit_rows = 8 * nt;
   p.x_rows = M > 8 ? 16 : 8;
   size_t x_bytes = (size_t)p.x_rows * ((size_t)K * 2 + ROW_PAD);
   p.x_in_smem = x_bytes <= X_SMEM_LIMIT ? 1 : 0;
   if (!p.x_in_smem) x_bytes = 0;
+  // Activations that stay in L2 are read again for every unit (all SMs, the same bytes): with a long K that is as
+  // much traffic as the weights.  Units of 16 rows halve it; the longest block's share of the weights stays what
+  // it was while there are at least about as many such units as SMs.
+  int nt = (N >= 16 * 4 * n_sms) ? 2 : 1;
+  if (!p.x_in_smem && (N + 15) / 16 >= (n_sms * 3) / 4) nt = 2;
+  const int unit_rows = 8 * nt;
   const int ks_try[4] = {2048, 1024, 512, 256};
   // A product that keeps an SM busy for long wants a deep ring (HBM answers after about 2 us, so about
   // 100 KB per SM must be on its way).  A short one gains more from sharing the SM with the kernel behind
