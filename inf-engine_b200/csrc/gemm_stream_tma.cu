@@ -27,8 +27,14 @@
 
 namespace {
 
-enum { PRO_PLAIN = 0, PRO_NORM = 1 };
-enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_RESIDUAL = 2, EPI_SILU_MUL = 3 };
+// Prologues: PLAIN bfloat16 activations; NORM float32 residual rows, RMSNorm inside the kernel; PRENORMED bfloat16
+// rows that the product ahead has already multiplied by this norm's gain, with that product's per-block sums of
+// squares (the 1/rms is formed from them here and applied to the sums as in NORM).
+// Epilogues: ...; RESIDUAL_NORMOUT is RESIDUAL that also prepares the next product's PRENORMED input: for the norm that
+// comes next it writes bfloat16(new residual * gain) and its block's sums of squares of the new residual rows.
+enum { PRO_PLAIN = 0, PRO_NORM = 1, PRO_PRENORMED = 2 };
+enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_RESIDUAL = 2, EPI_SILU_MUL = 3, EPI_RESIDUAL_NORMOUT = 4 };
+constexpr int SSQ_SLOT = 16;         // floats per block in the sums-of-squares array (one per activation row)
 
 constexpr int CONSUMER_WARPS = 8;
 constexpr int CONSUMER_THREADS = CONSUMER_WARPS * 32;
@@ -72,6 +78,14 @@ struct TmaParams {
   int n_stages;
   int x_rows;             // 8 or 16 activation rows (one MMA tile of tokens)
   int x_in_smem;          // activations staged in shared memory once per block (else read from L2 per chunk)
+  // RESIDUAL_NORMOUT writes, PRENORMED reads:
+  bf16* xg_out;           // [M, ld_xg] bfloat16(new residual * gain_next)
+  const void* gain_next;  // gain of the norm that comes next
+  int gain_next_is_f32;
+  int ld_xg;
+  float* ssq_out;         // [grid, SSQ_SLOT] this block's sums of squares of the new residual rows
+  const float* ssq_in;    // [ssq_blocks, SSQ_SLOT] the sums of the product ahead (PRENORMED)
+  int ssq_blocks;
 };
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -218,17 +232,32 @@ __device__ __forceinline__ void consume(const TmaParams& p, const BlockCtx& b, R
         for (int k = lane * 8; k < p.K; k += 256) *reinterpret_cast<uint4*>(dst + k) = make_uint4(0u, 0u, 0u, 0u);
         continue;
       }
-      if (PRO == PRO_PLAIN) {
+      // PRENORMED: the per-block sums of squares of the product ahead are asked for first and added up (in a
+      // fixed order) after the row has been copied, so that both come back in one trip to L2
+      float part[8];
+      if (PRO == PRO_PRENORMED) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          part[j] = (j * 32 + lane < p.ssq_blocks) ? __ldcg(p.ssq_in + (size_t)(j * 32 + lane) * SSQ_SLOT + m) : 0.f;
+      }
+      if (PRO == PRO_PLAIN || PRO == PRO_PRENORMED) {
         const bf16* src = (const bf16*)p.A + (size_t)m * p.lda;
         // read-only loads, eight rounds in flight: staging a row is a matter of trips to L2
         for (int kb = lane * 8; kb < p.K; kb += 2048) {
           uint4 v[8];
 #pragma unroll
           for (int i = 0; i < 8; ++i)
-            if (kb + i * 256 < p.K) v[i] = __ldg(reinterpret_cast<const uint4*>(src + kb + i * 256));
+            if (kb + i * 256 < p.K) v[i] = __ldcg(reinterpret_cast<const uint4*>(src + kb + i * 256));
 #pragma unroll
           for (int i = 0; i < 8; ++i)
             if (kb + i * 256 < p.K) *reinterpret_cast<uint4*>(dst + kb + i * 256) = v[i];
+        }
+        if (PRO == PRO_PRENORMED) {
+          float ssq = 0.f;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) ssq += part[j];
+          ssq = warp_sum(ssq);
+          if (lane == 0) inv_rms[m] = 1.f / sqrtf(ssq / (float)p.K + p.eps);
         }
       } else {
         const int row = p.row_index ? p.row_index[m] : m;
@@ -279,6 +308,7 @@ __device__ __forceinline__ void consume(const TmaParams& p, const BlockCtx& b, R
   const int chunks = p.ks / (CONSUMER_WARPS * 32);      // 32-wide chunks per warp per stage
   const bool two = p.x_rows > 8;
   int parity = 0;
+  float ssq_mine = 0.f;   // RESIDUAL_NORMOUT: squares of the new residual values this thread has stored (one row m per thread)
   bool dead = false;   // after a timed-out wait a warp stops waiting and computing but still meets every barrier
   for (int u = blockIdx.x; u < n_units; u += gridDim.x) {
     // two accumulators per n-tile: the two MMAs of a chunk do not wait for each other
@@ -361,7 +391,7 @@ __device__ __forceinline__ void consume(const TmaParams& p, const BlockCtx& b, R
           v0 += red[parity][w4][nt * 4 + h * 2][ln];
           v1 += red[parity][w4][nt * 4 + h * 2 + 1][ln];
         }
-        if (PRO == PRO_NORM) {
+        if (PRO != PRO_PLAIN) {
           v0 *= inv_rms[m];
           v1 *= inv_rms[m];
         }
@@ -378,6 +408,17 @@ __device__ __forceinline__ void consume(const TmaParams& p, const BlockCtx& b, R
           float* c = (float*)p.C + (size_t)m * p.ldc + n;
           c[0] += v0;
           if (has1) c[1] += v1;
+        } else if (EPI == EPI_RESIDUAL_NORMOUT) {
+          float* c = (float*)p.C + (size_t)m * p.ldc + n;
+          const float r0 = c[0] + v0, r1 = has1 ? c[1] + v1 : 0.f;
+          c[0] = r0;
+          if (has1) c[1] = r1;
+          ssq_mine += r0 * r0 + r1 * r1;
+          const float g0 = p.gain_next_is_f32 ? ((const float*)p.gain_next)[n] : __bfloat162float(((const bf16*)p.gain_next)[n]);
+          const float g1 = !has1 ? 0.f : (p.gain_next_is_f32 ? ((const float*)p.gain_next)[n + 1] : __bfloat162float(((const bf16*)p.gain_next)[n + 1]));
+          bf16* xg = p.xg_out + (size_t)m * p.ld_xg + n;
+          if (has1 && ((((uintptr_t)xg) & 3) == 0)) *reinterpret_cast<uint32_t*>(xg) = pack2(r0 * g0, r1 * g1);
+          else { xg[0] = __float2bfloat16_rn(r0 * g0); if (has1) xg[1] = __float2bfloat16_rn(r1 * g1); }
         } else {
           const float sg = 1.f / (1.f + expf(-v0));
           ((bf16*)p.C)[(size_t)m * p.ldc + (n >> 1)] = __float2bfloat16_rn((v0 * sg) * v1);
@@ -385,6 +426,25 @@ __device__ __forceinline__ void consume(const TmaParams& p, const BlockCtx& b, R
       }
     }
     parity ^= 1;
+  }
+  if (EPI == EPI_RESIDUAL_NORMOUT) {
+    // the block's sums of squares, row by row, added in a fixed order: the four threads of a row's quad, then the
+    // n-tiles; red is free (the last unit's sums were read before its consumers passed the barrier below)
+    float sq = ssq_mine;
+    sq += __shfl_xor_sync(0xffffffffu, sq, 1);
+    sq += __shfl_xor_sync(0xffffffffu, sq, 2);
+    consumer_sync();
+    float* rows = &red[0][0][0][0];                          // [NT][16]
+    if (tid < 64 * NT && (lane & 3) == 0) rows[(tid >> 6) * 16 + (lane >> 2) + ((tid >> 5) & 1) * 8] = sq;
+    consumer_sync();
+    if (tid < SSQ_SLOT) {
+      float total = rows[tid];
+      if (NT == 2) total += rows[16 + tid];
+      p.ssq_out[(size_t)blockIdx.x * SSQ_SLOT + tid] = total;
+      // the reader adds ssq_blocks slots up: those of blocks that this launch does not have are zero
+      if (blockIdx.x == 0)
+        for (int j = gridDim.x; j < p.ssq_blocks; ++j) p.ssq_out[(size_t)j * SSQ_SLOT + tid] = 0.f;
+    }
   }
   TRACE(6);                                                  // last unit stored
 }
@@ -480,7 +540,7 @@ constexpr size_t X_SMEM_LIMIT = 72 * 1024;
 extern "C" int ie_gemm_stream_tma_supports(int M, int N, int K, int pro) {
   if (M <= 0 || M > 16 || N <= 0 || K <= 0 || (K % 256)) return 0;
   const size_t x_bytes = (size_t)(M > 8 ? 16 : 8) * ((size_t)K * 2 + ROW_PAD);
-  if (pro == PRO_NORM) return x_bytes <= X_SMEM_LIMIT ? 1 : 0;
+  if (pro == PRO_NORM || pro == PRO_PRENORMED) return x_bytes <= X_SMEM_LIMIT ? 1 : 0;
   return 1;
 }
 
@@ -505,9 +565,15 @@ extern "C" int ie_gemm_stream_trace_read(unsigned long long* out, int max_launch
 }
 #endif
 
+// pro 2 (PRENORMED): A is the bfloat16 [M, lda] that the product ahead wrote (its xg), ssq its sums of squares
+//   ([ssq_blocks, 16] float32), eps the norm's; gain unused.
+// epi 4 (RESIDUAL_NORMOUT): C float32 += product, and for the norm that comes next: xg [M, ld_xg] = bfloat16(C * gain_next)
+//   and ssq [ssq_blocks, 16] = per-block sums of squares of the new rows of C (ssq_blocks >= the SMs used; N == the
+//   width of C: the whole row passes through this launch).
 extern "C" int ie_gemm_stream_tma(const void* A, const void* W, void* C, const void* gain, int gain_dtype,
                                   const int* row_index, int M, int N, int K, int lda, int ldw, int ldc, float eps,
-                                  int pro, int epi, int n_sms, cudaStream_t stream) {
+                                  int pro, int epi, int n_sms, void* xg, int ld_xg, const void* gain_next,
+                                  int gain_next_dtype, float* ssq, int ssq_blocks, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return IE_OK;
   if (!ie_gemm_stream_tma_supports(M, N, K, pro) || (lda & 7) || (ldw & 7)) return IE_BAD_SIZE;
   if (((uintptr_t)A | (uintptr_t)W) & 15) return IE_BAD_ALIGN;
@@ -517,6 +583,12 @@ extern "C" int ie_gemm_stream_tma(const void* A, const void* W, void* C, const v
   p.A = A; p.W = (const bf16*)W; p.C = C; p.gain = gain; p.row_index = row_index;
   p.M = M; p.N = N; p.K = K; p.lda = lda; p.ldw = ldw; p.ldc = ldc;
   p.gain_is_f32 = gain_dtype == IE_F32; p.eps = eps;
+  p.xg_out = (bf16*)xg; p.ld_xg = ld_xg; p.gain_next = gain_next; p.gain_next_is_f32 = gain_next_dtype == IE_F32;
+  p.ssq_out = ssq; p.ssq_in = ssq; p.ssq_blocks = ssq_blocks;
+  if (epi == EPI_RESIDUAL_NORMOUT &&
+      (!xg || !gain_next || !ssq || ssq_blocks < n_sms || (ld_xg & 1) || (((uintptr_t)xg | (uintptr_t)ssq) & 3)))
+    return IE_BAD_SIZE;
+  if (pro == PRO_PRENORMED && (!ssq || ssq_blocks <= 0 || ssq_blocks > 256)) return IE_BAD_SIZE;
   // units of 16 rows when that still gives every SM several units; a stage is 8 KB..16 KB per 8 rows
   p.x_rows = M > 8 ? 16 : 8;
   size_t x_bytes = (size_t)p.x_rows * ((size_t)K * 2 + ROW_PAD);
@@ -567,7 +639,14 @@ extern "C" int ie_gemm_stream_tma(const void* A, const void* W, void* C, const v
     if (epi == EPI_SILU_MUL) return launch_tma<PRO_NORM, EPI_SILU_MUL>(p, nt, n_sms, smem, stream);
     return IE_BAD_DTYPE;
   }
+  if (pro == PRO_PRENORMED) {
+    if (epi == EPI_BF16) return launch_tma<PRO_PRENORMED, EPI_BF16>(p, nt, n_sms, smem, stream);
+    if (epi == EPI_F32) return launch_tma<PRO_PRENORMED, EPI_F32>(p, nt, n_sms, smem, stream);
+    if (epi == EPI_SILU_MUL) return launch_tma<PRO_PRENORMED, EPI_SILU_MUL>(p, nt, n_sms, smem, stream);
+    return IE_BAD_DTYPE;
+  }
   if (pro == PRO_PLAIN) {
+    if (epi == EPI_RESIDUAL_NORMOUT) return launch_tma<PRO_PLAIN, EPI_RESIDUAL_NORMOUT>(p, nt, n_sms, smem, stream);
     if (epi == EPI_BF16) return launch_tma<PRO_PLAIN, EPI_BF16>(p, nt, n_sms, smem, stream);
     if (epi == EPI_F32) return launch_tma<PRO_PLAIN, EPI_F32>(p, nt, n_sms, smem, stream);
     if (epi == EPI_RESIDUAL) return launch_tma<PRO_PLAIN, EPI_RESIDUAL>(p, nt, n_sms, smem, stream);

@@ -54,6 +54,10 @@ class StepContext:
         self.max_q_len = 0
         self.max_seq_len = 0
         self.keys_cap = 0          # no request of the step holds more keys than this (sizes split-key grids)
+        # scratch for the parts while the step runs (see parts/linear.py: a norm handed over between products)
+        self.handover = None
+        self.upcoming_norm = None
+        self.norm_after_block = None
 
     def attention_work(self, group: int, rows: int, more_than: int = 0):
         """Work list for attention kernels that tile (token, head-in-group) pairs

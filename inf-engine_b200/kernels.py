@@ -306,7 +306,8 @@ def attention_decode_fused(q, k_new, v_new, out, kpool, vpool, block_table, q_st
 # ----------------------------------------------- weight-streaming product for few rows
 STREAM_MAX_ROWS = 64        # what the kernel takes
 STREAM_BEST_ROWS = 16       # beyond this the library product is faster (activations are re-read per block)
-_EPI = {"bf16": 0, "f32": 1, "residual": 2, "silu_mul": 3}
+_EPI = {"bf16": 0, "f32": 1, "residual": 2, "silu_mul": 3, "residual_normout": 4}
+SSQ_SLOT = 16               # floats per block in a sums-of-squares array
 _stream_lib = None
 
 
@@ -322,7 +323,7 @@ def stream_library():
         P, I, F = c_void_p, c_int, c_float
         lib.ie_gemm_stream.argtypes = [P, P, P, P, I, P, I, I, I, I, I, I, F, I, I, I, P]
         lib.ie_gemm_stream.restype = c_int
-        lib.ie_gemm_stream_tma.argtypes = [P, P, P, P, I, P, I, I, I, I, I, I, F, I, I, I, P]
+        lib.ie_gemm_stream_tma.argtypes = [P, P, P, P, I, P, I, I, I, I, I, I, F, I, I, I, P, I, P, I, P, I, P]
         lib.ie_gemm_stream_tma.restype = c_int
         lib.ie_gemm_stream_tma_supports.argtypes = [I, I, I, I]
         lib.ie_gemm_stream_tma_supports.restype = c_int
@@ -348,26 +349,46 @@ def stream_error() -> int:
 
 def gemm_stream(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, m: int, epi: str = "bf16",
                 gain: torch.Tensor | None = None, eps: float = 0.0, row_index: torch.Tensor | None = None,
-                nt: int | None = None) -> None:
+                nt: int | None = None, prenormed=None, normout=None) -> None:
     """c = a @ w^T for m <= 64 rows, bfloat16 weights, reading w once at HBM speed.
 
     With ``gain`` the input ``a`` is the float32 residual stream (rows gathered by ``row_index`` if given)
     and RMSNorm with that gain and ``eps`` is applied inside the kernel.  ``epi``: "bf16" or "f32" store,
     "residual" adds into the float32 ``c``, "silu_mul" takes w's rows as alternating gate/up and writes
-    silu(gate)*up, half as wide."""
+    silu(gate)*up, half as wide.
+
+    Two products can hand a norm over between them.  ``normout=(xg, gain_next, ssq)`` with epi "residual":
+    besides adding into ``c`` the kernel writes ``xg`` = bfloat16(new c * gain_next) and, per block, the sums of
+    squares of the new rows into ``ssq`` ([SMs, SSQ_SLOT] float32).  ``prenormed=(xg, ssq)`` with ``eps``: ``a`` is
+    ignored, the input is ``xg`` and the 1/rms comes from ``ssq``: RMSNorm without reading the residual again."""
     n, k = w.shape
     assert w.dtype is torch.bfloat16 and w.stride(1) == 1 and a.stride(-1) == 1 and c.stride(-1) == 1
+    lib = stream_library()
+    if prenormed is not None or normout is not None:
+        pro = 2 if prenormed is not None else 0
+        xg, ssq = (prenormed if prenormed is not None else (normout[0], normout[2]))
+        gain_next = normout[1] if normout is not None else None
+        src = xg if prenormed is not None else a
+        assert src.dtype is torch.bfloat16 and xg.dtype is torch.bfloat16 and ssq.dtype is torch.float32
+        assert nt is None and lib.ie_gemm_stream_tma_supports(m, n, k, pro)
+        code = _EPI["residual_normout"] if normout is not None else _EPI[epi]
+        _check(lib.ie_gemm_stream_tma(_ptr(src), _ptr(w), _ptr(c), None, 0, None, m, n, k, src.stride(0), w.stride(0),
+                                      c.stride(0), float(eps), pro, code, sm_count(), _ptr(xg), xg.stride(0),
+                                      _ptr(gain_next), dtype_code(gain_next.dtype) if gain_next is not None else 0,
+                                      _ptr(ssq), ssq.shape[0], _stream()),
+               f"gemm_stream_tma(m={m}, n={n}, k={k}, {epi}, handed-over norm)")
+        return
     if gain is None:
         assert a.dtype is torch.bfloat16
     else:
         assert a.dtype is torch.float32 and gain.shape == (k,)
-    lib = stream_library()
     if nt is None and lib.ie_gemm_stream_tma_supports(m, n, k, 0 if gain is None else 1):
         # persistent bulk-copy kernel: one block per SM, weights through a ring of shared memory
         _check(lib.ie_gemm_stream_tma(_ptr(a), _ptr(w), _ptr(c), _ptr(gain),
                                       dtype_code(gain.dtype) if gain is not None else 0, _ptr(row_index), m, n, k,
                                       a.stride(0), w.stride(0), c.stride(0), float(eps),
-                                      0 if gain is None else 1, _EPI[epi], sm_count(), _stream()),
+                                      0 if gain is None else 1, _EPI[epi], sm_count(), None, 0, None, 0, None, 0,
+                                      _stream()),
                f"gemm_stream_tma(m={m}, n={n}, k={k}, {epi})")
         return
     if nt is None:

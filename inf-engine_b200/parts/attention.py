@@ -19,7 +19,7 @@ import torch
 from .. import kernels
 from ..cache.manager import CacheRequirement
 from ..weights.loader import ExpectedTensor
-from .linear import Linear
+from .linear import Linear, stream_into_residual, stream_normed
 from .registry import build_position, position_class, register_mixer
 
 
@@ -81,11 +81,10 @@ class PagedAttention:
         residual sum in the output product's epilogue."""
         rt = self.rt
         n = residual.shape[0]
-        gain, eps = norm.fusable_rms()
         qkv = rt.ws.take("attn_qkv", (n, self.q_width + 2 * self.kv_width), rt.act_dtype)
-        self.qkv.stream(residual, qkv, n, "bf16", gain, eps)
+        stream_normed(self.qkv, residual, qkv, n, "bf16", norm, ctx)
         out = self._rotate_write_attend(qkv, ctx, cache)
-        self.o.stream(out, residual, n, "residual")
+        stream_into_residual(self.o, out, residual, n, ctx, rt)
 
     def forward(self, x: torch.Tensor, ctx, cache: CacheView) -> torch.Tensor:
         s, rt = self.spec, self.rt

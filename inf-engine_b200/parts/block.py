@@ -38,19 +38,31 @@ class PreNormBlock:
         n = ctx.n_tokens
         # a part may offer forward_fused(residual, norm, ...): it applies the norm and adds its own
         # result into the residual inside its kernels (worth it for the few rows of a decode step)
+        # ctx.upcoming_norm tells a fused part which norm follows its product into the residual (it may prepare
+        # that norm's input); ctx.handover is what the part before prepared, void as soon as the residual changes
+        after_block = getattr(ctx, "norm_after_block", None)
+        ff_fuses = _fuses(self.feedforward, n, self.ff_norm)
         if _fuses(self.mixer, n, self.mixer_norm):
             if pending is not None:
                 kernels.residual_add(residual, pending)
+                ctx.handover = None
+            ctx.upcoming_norm = self.ff_norm if ff_fuses else None
             self.mixer.forward_fused(residual, self.mixer_norm, ctx, cache)
             a = None
         else:
+            ctx.handover = None
             h = self.mixer_norm.add_norm(residual, pending)
             a = self.mixer.forward(h, ctx, cache)
-        if _fuses(self.feedforward, n, self.ff_norm):
+        if ff_fuses:
             if a is not None:
                 kernels.residual_add(residual, a)
+                ctx.handover = None
+            ctx.upcoming_norm = after_block
             self.feedforward.forward_fused(residual, self.ff_norm, ctx)
+            ctx.upcoming_norm = None
             return residual, None
+        ctx.handover = None
+        ctx.upcoming_norm = None
         h = self.ff_norm.add_norm(residual, a)
         m = self.feedforward.forward(h, ctx)
         return residual, m

@@ -11,7 +11,7 @@ import torch
 
 from .. import kernels
 from ..weights.loader import ExpectedTensor
-from .linear import Linear
+from .linear import Linear, stream_into_residual, stream_normed
 from .registry import register_feedforward
 
 
@@ -45,10 +45,9 @@ class GatedMLP:
         the first product's prologue, the activation in its epilogue, the sum in the second's epilogue."""
         n = residual.shape[0]
         s, ws = self.spec, self.rt.ws
-        gain, eps = norm.fusable_rms()
         h = ws.take("ff_hidden", (n, s.intermediate), torch.bfloat16)
-        self.gate_up.stream(residual, h, n, "silu_mul", gain, eps)
-        self.down.stream(h, residual, n, "residual")
+        stream_normed(self.gate_up, residual, h, n, "silu_mul", norm, ctx)
+        stream_into_residual(self.down, h, residual, n, ctx, self.rt)
 
     TCGEN05_MIN_ROWS = 128     # below one tile of rows the library product is the better choice
 

@@ -74,3 +74,46 @@ def _mm_f32_out(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
         torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
     else:
         kernels.gemm_simt(x, w, out)
+
+
+# ------------------------------------------------------------------ a norm handed over between two products
+# In a decode step a product that adds into the residual stream (the mixer's output projection, the feed-forward's
+# second product) is followed by a product of the NORMALISED residual (gate/up, the next block's qkv, the head).
+# The first can prepare the second's input while the new residual values pass through its hands: bfloat16(residual
+# * gain of the norm that comes next) and the sums of squares of the rows.  The second then reads 32 KB of bfloat16
+# instead of the float32 rows and the gain, and spends no time on the norm.  ``ctx.upcoming_norm`` (set by whoever
+# knows the order: the block, the model) names the norm that comes next; ``ctx.handover`` carries what was prepared
+# and is used only by a product whose norm is that very one.
+class NormHandover:
+    def __init__(self, gain, eps, xg, ssq):
+        self.gain, self.eps, self.xg, self.ssq = gain, eps, xg, ssq
+
+
+def stream_into_residual(linear: Linear, x: torch.Tensor, residual: torch.Tensor, n: int, ctx, rt) -> None:
+    """residual += x W^T through the streaming kernel; prepares the handover for ``ctx.upcoming_norm`` if it can."""
+    nxt = getattr(ctx, "upcoming_norm", None)
+    ctx.handover = None
+    if (nxt is not None and hasattr(nxt, "fusable_rms") and n <= 16 and linear.out_features == residual.shape[1]
+            and residual.is_contiguous()):
+        gain, eps = nxt.fusable_rms()
+        if gain.dtype in (torch.bfloat16, torch.float32) and linear.out_features % 256 == 0:
+            xg = rt.ws.take("handover_xg", (n, residual.shape[1]), torch.bfloat16)
+            ssq = rt.ws.take("handover_ssq", (kernels.sm_count(), kernels.SSQ_SLOT), torch.float32)
+            kernels.gemm_stream(x, linear.weight, residual, n, "residual", normout=(xg, gain, ssq))
+            ctx.handover = NormHandover(gain, eps, xg, ssq)
+            return
+    linear.stream(x, residual, n, "residual")
+
+
+def stream_normed(linear: Linear, residual: torch.Tensor, out: torch.Tensor, n: int, epi: str, norm, ctx) -> torch.Tensor:
+    """out = epilogue(norm(residual) W^T) through the streaming kernel: from a handover prepared for this very norm
+    (all rows, in order), else with the RMSNorm prologue."""
+    gain, eps = norm.fusable_rms()
+    h = getattr(ctx, "handover", None)
+    ctx.handover = None
+    if (h is not None and h.gain is gain and h.eps == eps and h.xg.shape[0] == n
+            and kernels.stream_library().ie_gemm_stream_tma_supports(n, linear.out_features, linear.in_features, 2)):
+        kernels.gemm_stream(h.xg, linear.weight, out, n, epi, eps=eps, prenormed=(h.xg, h.ssq))
+        return out
+    return linear.stream(residual, out, n, epi, gain, eps)
+

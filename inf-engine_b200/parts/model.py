@@ -11,7 +11,7 @@ import torch
 from .. import kernels
 from ..cache.manager import CacheManager, CacheRequirement
 from .attention import CacheView
-from .linear import Linear
+from .linear import Linear, stream_normed
 from .registry import build_block, build_norm
 
 
@@ -68,8 +68,14 @@ class DecoderModel:
         residual = rt.ws.take("residual", (n, spec.hidden), torch.float32)
         kernels.embed_gather(ctx.token_ids, self.embedding, residual)
         pending = None
+        ctx.handover = None
+        last = len(spec.schedule) - 1
         for i, e in enumerate(spec.schedule):
+            # the norm that the residual meets after this block: the next block's first, or the final one
+            nxt = self.layers[spec.schedule[i + 1].layer] if i < last else None
+            ctx.norm_after_block = getattr(nxt, "mixer_norm", None) if nxt is not None else self.final_norm
             residual, pending = self.layers[e.layer].forward(residual, pending, ctx, self._views[i])
+        ctx.norm_after_block = None
         m = ctx.n_logits
         if m == 0:
             return None
@@ -78,6 +84,10 @@ class DecoderModel:
             # final norm on the gathered rows inside the head product
             if pending is not None:
                 kernels.residual_add(residual, pending)
+                ctx.handover = None
+            if m == n and getattr(ctx, "handover", None) is not None:
+                # every row is wanted (a decode step): the last block may have prepared the final norm's input
+                return stream_normed(self.head, residual, logits, m, "f32", self.final_norm, ctx)
             gain, eps = self.final_norm.fusable_rms()
             return self.head.stream(residual, logits, m, "f32", gain, eps, row_index=ctx.logit_rows)
         h = self.final_norm.gather_norm(residual, pending, ctx.logit_rows, m)

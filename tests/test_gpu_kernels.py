@@ -217,6 +217,45 @@ def test_gemm_stream_bulk_copy_kernel(M, N, K):
     assert kernels.stream_error() == 0
 
 
+@pytest.mark.parametrize("M,hidden,inter", [(8, 2048, 8192), (3, 1024, 2048), (13, 512, 1024)])
+def test_norm_handed_over_between_streaming_products(M, hidden, inter):
+    """residual += h W_down^T with the next norm's input prepared on the way (bfloat16(residual * gain) and per-block
+    sums of squares), then a product that takes that input instead of normalising the residual itself: both against
+    float32 arithmetic, and the second against the same product with the RMSNorm prologue."""
+    from inf_engine_b200 import kernels
+    torch.manual_seed(hidden + M)
+    bf = torch.bfloat16
+    res0 = torch.randn(M, hidden, device=DEV)
+    hmid = torch.randn(M, inter, device=DEV).to(bf)
+    wd = (torch.randn(hidden, inter, device=DEV) * 0.03).to(bf)
+    wq = (torch.randn(3 * 256, hidden, device=DEV) * 0.03).to(bf)
+    eps = 1e-5
+    for gain_dtype in (bf, torch.float32):
+        gain = (1 + 0.1 * torch.randn(hidden, device=DEV)).to(gain_dtype)
+        res = res0.clone()
+        xg = torch.full((M, hidden), float("nan"), device=DEV, dtype=bf)
+        ssq = torch.full((kernels.sm_count(), kernels.SSQ_SLOT), float("nan"), device=DEV)
+        kernels.gemm_stream(hmid, wd, res, M, "residual", normout=(xg, gain, ssq))
+        want_res = res0.cpu() + hmid.float().cpu() @ wd.float().cpu().T
+        assert float((res.cpu() - want_res).abs().max()) <= 2e-3 * max(1.0, float(want_res.abs().max()))
+        # what was prepared: bfloat16(residual * gain), and sums of squares that add up to the rows' own
+        assert torch.equal(xg.float().cpu(), (res.cpu() * gain.float().cpu()).to(bf).float())
+        total = ssq[:, :M].sum(dim=0).cpu()
+        assert torch.allclose(total, (res.cpu() ** 2).sum(dim=1), rtol=1e-5)
+        assert torch.isfinite(ssq).all() and float(ssq[:, M:].abs().max()) == 0.0
+        # the product that takes it, against the one that normalises for itself
+        out_a = torch.empty(M, wq.shape[0], device=DEV, dtype=bf)
+        out_b = torch.empty_like(out_a)
+        kernels.gemm_stream(xg, wq, out_a, M, "bf16", eps=eps, prenormed=(xg, ssq))
+        kernels.gemm_stream(res, wq, out_b, M, "bf16", gain, eps)
+        ref = plain_llama.rms_norm(res.cpu(), gain.float().cpu(), eps) @ wq.float().cpu().T
+        scale = max(1.0, float(ref.abs().max()))
+        assert float((out_a.float().cpu() - ref).abs().max()) <= 2e-2 * scale
+        assert float((out_a.float() - out_b.float()).abs().max()) <= 1.6e-2 * scale      # a bfloat16 step of the result at most
+    torch.cuda.synchronize()
+    assert kernels.stream_error() == 0
+
+
 @pytest.mark.parametrize("M,N,K,bn", [(128, 256, 64, 256), (100, 200, 128, 128), (333, 1000, 512, 128),
                                       (700, 1306, 192, 256), (2048, 3072, 2048, 256)])
 def test_gemm_tcgen05_against_float32(M, N, K, bn):
