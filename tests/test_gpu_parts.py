@@ -257,3 +257,212 @@ def test_a_toy_mixer_with_its_own_state_is_registered_built_and_stepped(dtype):
         assert torch.allclose(lg, ref_a, **t)
     finally:
         MIXERS.pop("toy_decay")
+
+
+# ------------------------------------------------------- more toy parts
+def _two_layer_model(dtype, toy_block_of, seed, fix=None):
+    """TINY_A with its second layer replaced by ``toy_block_of(base layer)``: (runner, float32 weights)."""
+    from inf_engine_b200 import ModelRunner
+    from inf_engine_b200.config import ScheduleEntry, parse_config_dict
+    from inf_engine_b200.parts import expected_tensors
+    from inf_engine_b200.weights import kept_dtype, random_tensors
+    from helpers import TINY_A
+
+    cfg = parse_config_dict(TINY_A)
+    base = cfg.model_spec()
+    spec = dataclasses.replace(base, layers=(base.layers[0], toy_block_of(base.layers[1])),
+                               schedule=(ScheduleEntry(0), ScheduleEntry(1)))
+    cpu = random_tensors(expected_tensors(spec), seed=seed, std=0.05)
+    if fix is not None:
+        fix(cpu)
+    tensors = {n: t.to(DEV, kept_dtype(t.dtype, dtype)) for n, t in cpu.items()}
+    r = ModelRunner(cfg, tensors, dtype, page_size=16, n_pages=16, max_requests=3, spec=spec)
+    return r, {n: t.float() for n, t in cpu.items()}
+
+
+def _stepped_in_cuts(r, a, b):
+    """Request a in portions (then token by token), b whole beside a's first portion: every logit of both."""
+    from inf_engine_b200 import StepEntry
+    got_a, got_b = [], []
+    r.open("a"); r.open("b")
+    pa = pb = 0
+    for na, nb in [(7, len(b)), (2, 0), (len(a) - 12, 0), (1, 0), (1, 0), (1, 0)]:
+        es = [StepEntry("a", a[pa:pa + na], list(range(na)))]
+        if nb:
+            es.append(StepEntry("b", b[pb:pb + nb], list(range(nb))))
+        lg = r.step(es).cpu()
+        got_a.append(lg[:na].clone()); got_b.append(lg[na:].clone())
+        pa += na; pb += nb
+    assert pa == len(a) and pb == len(b)
+    return torch.cat(got_a), torch.cat(got_b)
+
+
+def _logit_tol(dtype):
+    return dict(atol=2e-5, rtol=1e-5) if dtype is torch.float32 else dict(atol=4e-2, rtol=4e-2)
+
+
+@dataclass(frozen=True)
+class ToyRoutedSpec:
+    """Each token goes to the one expert its router logit is largest for: out = p * W_out[e] relu(W_in[e] x),
+    p the softmax weight of that expert."""
+
+    kind: str
+    hidden: int
+    inner: int
+    n_experts: int
+    router: str
+    w_in: str
+    w_out: str
+
+
+class ToyRoutedFeedForward:
+    @staticmethod
+    def expected_tensors(spec):
+        from inf_engine_b200.weights import ExpectedTensor
+        return {spec.router: ExpectedTensor((spec.n_experts, spec.hidden)),
+                spec.w_in: ExpectedTensor((spec.n_experts, spec.inner, spec.hidden)),
+                spec.w_out: ExpectedTensor((spec.n_experts, spec.hidden, spec.inner))}
+
+    def __init__(self, spec, tensors, rt):
+        self.spec = spec
+        self.router, self.w_in, self.w_out = tensors[spec.router], tensors[spec.w_in], tensors[spec.w_out]
+
+    def forward(self, x, ctx):
+        logits = x.float() @ self.router.float().T                      # router logits in 32-bit
+        p, e = torch.softmax(logits, dim=-1).max(dim=-1)
+        out = torch.zeros_like(x)
+        for i in range(self.spec.n_experts):
+            rows = (e == i).nonzero().flatten()
+            h = torch.relu(x[rows] @ self.w_in[i].to(x.dtype).T)
+            out[rows] = (p[rows, None] * (h @ self.w_out[i].to(x.dtype).T).float()).to(x.dtype)
+        return out
+
+
+def _plain_routed(h, w):
+    logits = h @ w["toy.router"].T
+    p, e = torch.softmax(logits, dim=-1).max(dim=-1)
+    out = torch.stack([p[t] * (w["toy.w_out"][e[t]] @ torch.relu(w["toy.w_in"][e[t]] @ h[t])) for t in range(len(h))])
+    top2 = logits.topk(2, dim=-1).values
+    return out, float((top2[:, 0] - top2[:, 1]).min())
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_toy_feedforward_with_routing_beside_the_dense_one(dtype):
+    """Layer 0 keeps the dense feed-forward (and fuses its norm on short steps), layer 1 routes: the block takes
+    either, and the hand-over of a prepared norm stops where a part does not take part in it."""
+    from inf_engine_b200.parts import FEEDFORWARDS, register_feedforward
+    from helpers import TINY_A
+
+    register_feedforward("toy_routed", ToyRoutedFeedForward)
+    try:
+        toy = ToyRoutedSpec("toy_routed", 64, 40, 3, "toy.router", "toy.w_in", "toy.w_out")
+
+        def sharpen(cpu):               # router rows far apart, so that rounding does not move a token to another expert
+            cpu["toy.router"] = (cpu["toy.router"].float() * 40).to(cpu["toy.router"].dtype)
+
+        r, w = _two_layer_model(dtype, lambda blk: dataclasses.replace(blk, feedforward=toy), seed=6, fix=sharpen)
+        assert "model.layers.1.mlp.gate_proj.weight" not in w and w["toy.w_in"].shape == (3, 40, 64)
+
+        margins = []
+
+        def plain(toks):
+            x = w["model.embed_tokens.weight"][torch.tensor(toks)]
+            x = plain_llama.block(x, w, "model.layers.0.", TINY_A, *plain_llama.rope_tables(TINY_A, len(toks)))
+            h = plain_llama.rms_norm(x, w["model.layers.1.input_layernorm.weight"], 1e-5)
+            x = x + plain_llama.attention(h, *(w[f"model.layers.1.self_attn.{p}_proj.weight"] for p in "qkvo"),
+                                          TINY_A, *plain_llama.rope_tables(TINY_A, len(toks)))
+            h = plain_llama.rms_norm(x, w["model.layers.1.post_attention_layernorm.weight"], 1e-5)
+            routed, margin = _plain_routed(h, w)
+            margins.append(margin)
+            x = x + routed
+            return plain_llama.rms_norm(x, w["model.norm.weight"], 1e-5) @ w["model.embed_tokens.weight"].T
+
+        a, b = random_tokens(256, 40, 1), random_tokens(256, 23, 2)
+        ref_a, ref_b = plain(a), plain(b)
+        assert min(margins) > 0.25, "the test's tokens must not sit on the edge between two experts"
+        got_a, got_b = _stepped_in_cuts(r, a, b)
+        assert torch.allclose(got_a, ref_a, **_logit_tol(dtype)) and torch.allclose(got_b, ref_b, **_logit_tol(dtype))
+    finally:
+        FEEDFORWARDS.pop("toy_routed")
+
+
+@dataclass(frozen=True)
+class ToyDecayPositionSpec:
+    """Not a table rotation: q of a head is scaled by exp(-rate * position) and k by exp(+rate * position), so a
+    score carries exp(-rate * distance).  One learned rate per kv head."""
+
+    kind: str
+    n_kv_heads: int
+    head_dim: int
+    rates: str
+
+
+class ToyDecayPosition:
+    @staticmethod
+    def expected_tensors(spec):
+        from inf_engine_b200.weights import ExpectedTensor
+        return {spec.rates: ExpectedTensor((spec.n_kv_heads,))}
+
+    def __init__(self, spec, tensors, rt):
+        self.spec, self.rates = spec, tensors[spec.rates].float()
+
+    def rotary_tables(self):
+        return None
+
+    def rotate(self, q, k, ctx):
+        n, c, hd = q.shape[0], self.spec.n_kv_heads, self.spec.head_dim
+        f = torch.exp(self.rates[None, :] * ctx.positions[:n, None].float())            # [n, kv heads]
+        kk = k.view(n, c, hd)
+        kk.copy_((kk.float() * f[:, :, None]).to(k.dtype))
+        qq = q.view(n, c, -1, hd)                                                       # heads of a group together
+        qq.copy_((qq.float() / f[:, :, None, None]).to(q.dtype))
+
+
+def _plain_decay_attention(h, w, prefix, config, rates):
+    T = h.shape[0]
+    H, C, hd = config["num_attention_heads"], config["num_key_value_heads"], config["head_dim"]
+    q = (h @ w[prefix + "q_proj.weight"].T).view(T, H, hd).transpose(0, 1)
+    k = (h @ w[prefix + "k_proj.weight"].T).view(T, C, hd).transpose(0, 1).repeat_interleave(H // C, dim=0)
+    v = (h @ w[prefix + "v_proj.weight"].T).view(T, C, hd).transpose(0, 1).repeat_interleave(H // C, dim=0)
+    i, j = torch.arange(T)[:, None], torch.arange(T)[None, :]
+    decay = torch.exp(-rates.repeat_interleave(H // C)[:, None, None] * (i - j)[None].float())
+    scores = (q @ k.transpose(1, 2)) * decay * hd ** -0.5
+    scores = scores.masked_fill(~(j <= i)[None], float("-inf"))
+    out = (torch.softmax(scores, dim=-1) @ v).transpose(0, 1).reshape(T, H * hd)
+    return out @ w[prefix + "o_proj.weight"].T
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_toy_position_encoding_with_a_learned_tensor(dtype):
+    """Layer 0 rotates by tables, layer 1 uses an encoding that is no rotation and owns a tensor of the
+    checkpoint: the attention part takes either, chosen by the layer's spec."""
+    from inf_engine_b200.parts import POSITIONS, register_position
+    from helpers import TINY_A
+
+    register_position("toy_decay_position", ToyDecayPosition)
+    try:
+        pos = ToyDecayPositionSpec("toy_decay_position", 2, 16, "toy.pos.rates")
+        rates = torch.tensor([0.03, 0.008])
+
+        def set_rates(cpu):
+            cpu["toy.pos.rates"] = rates.clone()                     # stored in 32-bit: stays so
+
+        r, w = _two_layer_model(
+            dtype, lambda blk: dataclasses.replace(blk, mixer=dataclasses.replace(blk.mixer, position=pos)),
+            seed=8, fix=set_rates)
+
+        def plain(toks):
+            x = w["model.embed_tokens.weight"][torch.tensor(toks)]
+            x = plain_llama.block(x, w, "model.layers.0.", TINY_A, *plain_llama.rope_tables(TINY_A, len(toks)))
+            h = plain_llama.rms_norm(x, w["model.layers.1.input_layernorm.weight"], 1e-5)
+            x = x + _plain_decay_attention(h, w, "model.layers.1.self_attn.", TINY_A, rates)
+            h = plain_llama.rms_norm(x, w["model.layers.1.post_attention_layernorm.weight"], 1e-5)
+            x = x + plain_llama.swiglu(h, *(w[f"model.layers.1.mlp.{p}_proj.weight"] for p in ("gate", "up", "down")))
+            return plain_llama.rms_norm(x, w["model.norm.weight"], 1e-5) @ w["model.embed_tokens.weight"].T
+
+        a, b = random_tokens(256, 40, 3), random_tokens(256, 23, 4)
+        ref_a, ref_b = plain(a), plain(b)
+        got_a, got_b = _stepped_in_cuts(r, a, b)
+        assert torch.allclose(got_a, ref_a, **_logit_tol(dtype)) and torch.allclose(got_b, ref_b, **_logit_tol(dtype))
+    finally:
+        POSITIONS.pop("toy_decay_position")
