@@ -34,6 +34,12 @@ class PreNormBlock:
         self.ff_norm = build_norm(spec.ff_norm, tensors, rt)
         self.feedforward = build_feedforward(spec.feedforward, tensors, rt)
 
+    @property
+    def graph_safe(self) -> bool:
+        """Whether a step through this block may be captured as a CUDA graph: every part says that it reads the
+        batch's numbers on the device only and never waits for the device (a part that says nothing does not)."""
+        return all(getattr(p, "graph_safe", False) for p in (self.mixer, self.feedforward))
+
     def forward(self, residual, pending, ctx, cache):
         n = ctx.n_tokens
         # a part may offer forward_fused(residual, norm, ...): it applies the norm and adds its own

@@ -17,6 +17,8 @@ from .registry import register_feedforward
 
 @register_feedforward("gated_mlp")
 class GatedMLP:
+    graph_safe = True
+
     @staticmethod
     def expected_tensors(spec):
         return {

@@ -29,7 +29,8 @@ class DecoderModel:
                 raise ValueError(f"schedule entry {i} names layer {e.layer}, the model has {len(self.layers)}")
             if e.cache_from is not None and not (0 <= e.cache_from < i and spec.schedule[e.cache_from].cache_from is None):
                 raise ValueError(f"schedule entry {i} must read the cache of an earlier entry that owns one")
-        self.graph_safe = all(getattr(self.layers[e.layer].mixer, "graph_safe", False) for e in spec.schedule)
+        # a decode step is captured as a graph only if every block that runs says it may be
+        self.graph_safe = all(getattr(self.layers[e.layer], "graph_safe", False) for e in spec.schedule)
         self._views: list[CacheView] | None = None
 
     # ------------------------------------------------------------------ cache

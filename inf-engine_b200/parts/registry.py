@@ -18,7 +18,9 @@ Mixer           expected_tensors(spec); __init__(spec, tensors, rt)
                     cache is a CacheView: the pools or the state of this run, and whether to write
                 graph_safe: bool   (True when forward reads batch metadata on the device only)
 FeedForward     expected_tensors(spec); __init__(spec, tensors, rt); forward(x, ctx) -> [N, hidden]
+                graph_safe: bool   (as for a mixer; a part that does not say so keeps decode steps out of graphs)
 Block           expected_tensors(spec); __init__(spec, tensors, rt)
+                graph_safe: bool   (every part of it is)
                 forward(residual, pending, ctx, cache) -> (residual, pending)
                     ``pending`` is a delta not yet added to the residual, so that the next norm
                     can fuse the sum

@@ -362,6 +362,7 @@ def test_a_toy_feedforward_with_routing_beside_the_dense_one(dtype):
 
         r, w = _two_layer_model(dtype, lambda blk: dataclasses.replace(blk, feedforward=toy), seed=6, fix=sharpen)
         assert "model.layers.1.mlp.gate_proj.weight" not in w and w["toy.w_in"].shape == (3, 40, 64)
+        assert not r.model.graph_safe                  # the toy part does not say that it is: no captured decode steps
 
         margins = []
 
@@ -450,6 +451,7 @@ def test_a_toy_position_encoding_with_a_learned_tensor(dtype):
         r, w = _two_layer_model(
             dtype, lambda blk: dataclasses.replace(blk, mixer=dataclasses.replace(blk.mixer, position=pos)),
             seed=8, fix=set_rates)
+        assert r.model.graph_safe                      # the encoding works on the device only: decode steps are graphs
 
         def plain(toks):
             x = w["model.embed_tokens.weight"][torch.tensor(toks)]
