@@ -54,7 +54,9 @@ def _ptr(t: torch.Tensor | None) -> int | None:
 
 
 def _stream() -> int:
-    return torch.cuda.current_stream().cuda_stream
+    # the raw handle of the current stream of the current device, without building a Stream object: a step makes
+    # a hundred launches, and the object cost more host time than everything else around a launch
+    return torch._C._cuda_getCurrentRawStream(torch._C._cuda_getDevice())
 
 
 _core = None

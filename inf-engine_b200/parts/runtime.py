@@ -19,9 +19,21 @@ class Workspace:
     def __init__(self, device: torch.device):
         self.device = device
         self._buffers: dict[str, torch.Tensor] = {}
+        self._views: dict[tuple, torch.Tensor] = {}     # (name, shape, dtype) -> the view handed out last time
         self.frozen = False
 
     def take(self, name: str, shape: tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
+        key = (name, shape, dtype)
+        view = self._views.get(key)
+        if view is not None:
+            return view
+        view = self._take(name, shape, dtype)
+        if len(self._views) > 4096:
+            self._views.clear()
+        self._views[key] = view
+        return view
+
+    def _take(self, name: str, shape: tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
         n = 1
         for s in shape:
             n *= int(s)
@@ -36,6 +48,7 @@ class Workspace:
             cap = 1 << (cap - 1).bit_length() if cap < (1 << 20) else -(-cap // (1 << 20)) * (1 << 20)
             buf = torch.zeros(cap, dtype=torch.uint8, device=self.device)   # some kernels keep counters that start at zero
             self._buffers[name] = buf
+            self._views = {k: v for k, v in self._views.items() if k[0] != name}   # views of the buffer it replaces
         return buf[:nbytes].view(dtype).view(shape)
 
     def reserved_bytes(self) -> int:
