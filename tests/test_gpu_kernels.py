@@ -553,6 +553,9 @@ DECODE_CASES = [
     (4, 1, 128, 16, [1, 3], [333, 50], None, 96),
     (16, 1, 128, 32, [1], [900], None, 128),
     (8, 2, 64, 16, [1, 1, 2], [90, 41, 400], 37, 64),
+    # long contexts: more blocks per stream than one round of the last block's merge takes
+    (8, 2, 64, 16, [1, 1], [9000, 5], None, 64),
+    (4, 1, 128, 16, [1, 2], [7, 6100], None, 64),
 ]
 
 
@@ -585,6 +588,7 @@ FUSED_DECODE_CASES = [
     (4, 4, 64, 16, [3, 1000], 37, 256, True, True),
     (8, 2, 64, 16, [64, 200], None, 64, False, True),
     (8, 2, 64, 16, [64, 200], None, 64, True, False),
+    (8, 2, 64, 16, [6000, 100], None, 64, True, True),
 ]
 
 
