@@ -467,6 +467,9 @@ TCGEN05_ATTENTION_CASES = [
     (6, 2, 128, 8, [1, 9, 1, 70, 130], [70, 0, 129, 31, 515]),
     (3, 3, 128, 32, [17, 1, 300], [3, 300, 64]),
     (4, 1, 128, 64, [129, 2, 40], [127, 1000, 0]),
+    # long: the rings of stages and of S buffers go round many times
+    (4, 2, 64, 16, [2500, 40], [0, 3000]),
+    (2, 1, 128, 16, [1500], [1200]),
 ]
 
 
