@@ -352,3 +352,40 @@ def test_command_line(tmp_path):
     assert got[0] == plain_llama.greedy_generate(weights, config, [5, 17, 3], 6)
     assert got[1] == plain_llama.greedy_generate(weights, config, [9, 9, 9, 9], 6)
     assert json.loads(stats.read_text())["new_tokens"] == 12
+
+
+@pytest.mark.parametrize("preset,layers", [("llama-3.2-1b", 2), ("llama-3.2-3b", 1)])
+def test_full_width_layers_in_bfloat16_against_the_32bit_path(tmp_path, preset, layers):
+    """The real widths (hidden 2,048 / 3,072, heads of 64 / 128, vocabulary 128,256) take the kernels' large-size
+    paths, which the tiny models never reach: the tensor-core products and attention of a long prompt, the streaming
+    products and the split-key attention of decode steps inside captured graphs, and a mixed step.  The plain
+    implementation is too slow at this size; the 32-bit path of the engine, which the tiny models tie to it, stands
+    in as the reference."""
+    from inf_engine_b200.config import get_preset
+    from inf_engine_b200.weights import write_random_model
+
+    cfg = dataclasses.replace(get_preset(preset), num_hidden_layers=layers)
+    d = tmp_path / "wide"
+    write_random_model(cfg, 11, d)
+    V = cfg.vocab_size
+    a, b = random_tokens(V, 300, 1), random_tokens(V, 150, 2)
+    tail = random_tokens(V, 4, 3)
+
+    def run(dtype):
+        r = runner_for(d, dtype, page_size=16, n_pages=64, max_requests=4)
+        out = []
+        r.open("a")
+        out.append(r.step([entry("a", a, [len(a) - 2, len(a) - 1])]).cpu().clone())       # a long prompt, whole
+        for t in tail[:2]:                                                                 # decode steps of one
+            out.append(r.step([entry("a", [t])]).cpu().clone())
+        r.open("b")
+        out.append(r.step([entry("a", [tail[2]]), entry("b", b[:100], [99])]).cpu().clone())   # mixed
+        out.append(r.step([entry("a", [tail[3]]), entry("b", b[100:], [49])]).cpu().clone())
+        for t in (7, 8):                                                                   # decode steps of two
+            out.append(r.step([entry("a", [t]), entry("b", [t + 1])]).cpu().clone())
+        return torch.cat(out)
+
+    ref = run("float32")
+    got = run("bfloat16")
+    assert_close(got, ref, "bfloat16", f"{preset} widths, {layers} layers")
+    assert (got.argmax(-1) == ref.argmax(-1)).float().mean() >= 0.75      # mostly the same next token
