@@ -41,6 +41,8 @@ struct MmaAttnParams {
   float* part_ml;  // decode: [n_tokens*n_heads, n_blocks, 2]
   int* tickets;    // decode: [n_requests * n_kv_heads], zero between launches
   int n_blocks;    // decode: blocks per (request, kv head) = partial results per row
+  int cluster_merge;  // decode: the blocks of a (request, kv head) are one thread-block cluster and add up through
+                      // distributed shared memory instead of through global memory and a ticket
   int q_stride, out_stride, table_stride;
   int n_heads, n_kv_heads, page_size, window;
   int page_shift;  // log2(page_size) when it is a power of two, else -1
@@ -492,9 +494,11 @@ __device__ __forceinline__ unsigned long long trace_now() {
 // A warp keeps up to DC_STAGES key tiles in flight (a decode step is a matter of latency: few bytes per
 // warp, all of them wanted as early as possible).  The warps of a block add their partial results up
 // through shared memory, in ascending order of the splits.  A (request, kv head) that one block covers
-// is finished there; otherwise each block writes one partial result and takes a ticket, and the block
-// that takes the last ticket adds the blocks up, again in ascending order: the result does not depend
-// on which block that is.
+// is finished there.  Otherwise, with up to 8 blocks per (request, kv head), these blocks are launched as one
+// thread-block cluster: each leaves its result in its own shared memory, and after a cluster barrier the first
+// of them adds the blocks up in ascending order, reading the others' shared memory.  With more blocks each
+// writes one partial result to global memory and takes a ticket, and the block that takes the last ticket adds
+// the blocks up, again in ascending order: the result does not depend on which block that is, nor on the path.
 #ifndef IE_DC_WARPS
 #define IE_DC_WARPS (HD <= 64 ? 6 : 3)   // 96 KB of tiles per block: two blocks share an SM
 #endif
@@ -510,6 +514,27 @@ constexpr int DC_KT = IE_DC_KT;
 constexpr int DC_STAGES = IE_DC_STAGES;
 constexpr int DC_STAGE_BYTES = 2 * DC_KT * HD * 2;
 constexpr int DC_WARP_BYTES = DC_STAGES * DC_STAGE_BYTES;
+constexpr int DC_RESULT_BYTES = (16 * HD + 32) * 4;   // a block's result for the cluster: [16][HD] sums, [16][2] (max, sum)
+constexpr int DC_SMEM_BYTES = DC_WARPS * DC_WARP_BYTES + DC_RESULT_BYTES;
+
+__device__ __forceinline__ void cluster_barrier() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cluster_map(uint32_t local_addr, uint32_t rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+  return remote;
+}
+__device__ __forceinline__ float ld_cluster_f32(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ float2 ld_cluster_f32x2(uint32_t addr) {
+  float2 v;
+  asm volatile("ld.shared::cluster.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr) : "memory");
+  return v;
+}
 
 __device__ __forceinline__ void cp_async_wait_pending(int pending) {
   switch (pending) {
@@ -558,7 +583,17 @@ __global__ void __launch_bounds__(DC_THREADS, HD <= 64 ? 3 : 2) attention_decode
   // A block without keys leaves at once and frees its slot.  It need not wait for the kernel ahead:
   // block 0 of every (request, kv head) always has keys and waits, so this kernel still ends after it.
   // (a request with more than 16 rows is not this kernel's: in a mixed step the prefill kernel takes it)
-  if ((int)blockIdx.x < b_first || (int)blockIdx.x > b_last || n_pairs <= 0 || n_pairs > 16) return;
+  if (n_pairs <= 0 || n_pairs > 16) return;                   // all blocks of this (request, kv head) alike
+  // whether the blocks add up inside their cluster: the same answer in every block of the cluster, and every one
+  // of them, with keys or without, then meets both cluster barriers below
+  const bool merge_in_cluster = p.cluster_merge != 0 && n_active_blocks > 1;
+  if ((int)blockIdx.x < b_first || (int)blockIdx.x > b_last) {
+    if (merge_in_cluster) {
+      cluster_barrier();
+      cluster_barrier();
+    }
+    return;
+  }
 
   float o[NT_O][4];
 #pragma unroll
@@ -678,6 +713,10 @@ __global__ void __launch_bounds__(DC_THREADS, HD <= 64 ? 3 : 2) attention_decode
     if (n_active_blocks == 1) {
       const float inv = den > 0.f ? 1.f / den : 0.f;
       p.out[(size_t)(q0 + t) * p.out_stride + (c * group + (pr - t * group)) * HD + d] = __float2bfloat16(acc * inv);
+    } else if (merge_in_cluster) {
+      float* res = reinterpret_cast<float*>(smem + DC_WARPS * DC_WARP_BYTES);
+      res[pr * HD + d] = acc;
+      if (d == 0) *reinterpret_cast<float2*>(res + 16 * HD + pr * 2) = make_float2(M, den);
     } else {
       p.part_o[(row * p.n_blocks + blk) * HD + d] = acc;
       if (d == 0) *reinterpret_cast<float2*>(p.part_ml + (row * p.n_blocks + blk) * 2) = make_float2(M, den);
@@ -685,6 +724,42 @@ __global__ void __launch_bounds__(DC_THREADS, HD <= 64 ? 3 : 2) attention_decode
   }
   TRACE(7);                                                  // block's result written (output or partial)
   if (n_active_blocks == 1) return;
+
+  if (merge_in_cluster) {
+    // ---- the cluster of this (request, kv head): its first block with keys adds the blocks up, in ascending
+    // order and with the arithmetic of the ticket path below, from the others' shared memory
+    cluster_barrier();
+    if ((int)blockIdx.x == b_first) {
+      const uint32_t res = smem_u32(smem + DC_WARPS * DC_WARP_BYTES);
+      for (int idx = threadIdx.x; idx < n_out; idx += DC_THREADS) {
+        const int pr = idx / HD, d = idx - pr * HD;
+        const int t = pr / group;
+        float2 mlv[8];
+        float v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const uint32_t peer = cluster_map(res, (uint32_t)(b_first + min(u, n_active_blocks - 1)));   // rank == blockIdx.x
+          mlv[u] = ld_cluster_f32x2(peer + (16 * HD + pr * 2) * 4);
+          v[u] = ld_cluster_f32(peer + (pr * HD + d) * 4);
+        }
+        float M = -INFINITY, acc = 0.f, den = 0.f;
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          if (u < n_active_blocks) M = fmaxf(M, mlv[u].x);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const bool real = u < n_active_blocks && mlv[u].x > -INFINITY;
+          const float f = real ? fast_exp2(mlv[u].x - M) : 0.f;
+          acc += f * v[u];
+          den += f * mlv[u].y;
+        }
+        const float inv = den > 0.f ? 1.f / den : 0.f;
+        p.out[(size_t)(q0 + t) * p.out_stride + (c * group + (pr - t * group)) * HD + d] = __float2bfloat16(acc * inv);
+      }
+    }
+    cluster_barrier();                                         // nobody leaves while the first block still reads
+    return;
+  }
 
   // ---- ticket of this (request, kv head): the last block to arrive adds the blocks up
   __shared__ int s_ticket;
@@ -758,6 +833,7 @@ static void fill(MmaAttnParams& p, const void* q, void* out, const void* kpool, 
   p.q = (const bf16*)q; p.out = (bf16*)out; p.kpool = (const bf16*)kpool; p.vpool = (const bf16*)vpool;
   p.block_table = block_table; p.q_start = q_start; p.ctx_before = ctx_before;
   p.work_req = nullptr; p.work_pair0 = nullptr; p.part_o = nullptr; p.part_ml = nullptr; p.tickets = nullptr;
+  p.cluster_merge = 0;
   p.q_stride = q_stride; p.out_stride = out_stride; p.table_stride = table_stride;
   p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.page_size = page_size; p.window = window;
   p.n_splits = 0; p.split_keys = 0; p.n_blocks = 0; p.scale_log2 = scale * LOG2E;
@@ -839,15 +915,22 @@ static int decode_launch(MmaAttnParams& p, float* scratch, int n_requests, int n
   p.tickets = reinterpret_cast<int*>(scratch);
   p.part_o = scratch + IE_DECODE_TICKET_WORDS;
   p.part_ml = p.part_o + (size_t)n_tokens * n_heads * p.n_blocks * HD;
-  const int smem = DC_WARPS * DC_WARP_BYTES;
+  const int smem = DC_SMEM_BYTES;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
+  // 2 to 8 blocks per (request, kv head): one cluster along x (IE_DECODE_NO_CLUSTER=1: the ticket path, to compare)
+  static int no_cluster = -1;
+  if (no_cluster < 0) {
+    const char* e = getenv("IE_DECODE_NO_CLUSTER");
+    no_cluster = (e && e[0] == '1') ? 1 : 0;
+  }
+  p.cluster_merge = (!no_cluster && p.n_blocks >= 2 && p.n_blocks <= 8) ? 1 : 0;
   dim3 grid(p.n_blocks, n_kv_heads, n_requests);
-  return launch_k(attention_decode_kernel, grid, DC_THREADS, smem, stream, p);
+  return launch_k_cluster(attention_decode_kernel, p.cluster_merge ? p.n_blocks : 1, grid, DC_THREADS, smem, stream, p);
 }
 
 extern "C" int ie_attention_decode(const void* q, void* out, const void* kpool, const void* vpool,

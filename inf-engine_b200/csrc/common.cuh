@@ -98,18 +98,30 @@ static inline bool pdl_enabled() {
   return on == 1;
 }
 
+// cluster_x > 1: consecutive blocks along x form thread-block clusters of that size (grid.x a multiple of it)
 static inline int launch_raw(const void* kernel, dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
-                             void** args) {
+                             void** args, int cluster_x = 1) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchAttribute attr[2];
+  int n = 0;
+  if (pdl_enabled()) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  if (cluster_x > 1) {
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = (unsigned)cluster_x;
+    attr[n].val.clusterDim.y = 1;
+    attr[n].val.clusterDim.z = 1;
+    ++n;
+  }
   cfg.attrs = attr;
-  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  cfg.numAttrs = n;
   return (int)cudaLaunchKernelExC(&cfg, kernel, args);
 }
 
@@ -127,4 +139,15 @@ static inline int launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size
   void* ptrs[sizeof...(KArgs) ? sizeof...(KArgs) : 1];
   tuple_pointers(vals, ptrs, std::index_sequence_for<KArgs...>{});
   return launch_raw((const void*)kernel, grid, block, smem, stream, ptrs);
+}
+
+// the same with clusters of cluster_x blocks along x
+template <typename... KArgs, typename... Args>
+static inline int launch_k_cluster(void (*kernel)(KArgs...), int cluster_x, dim3 grid, dim3 block, size_t smem,
+                                   cudaStream_t stream, Args... args) {
+  static_assert(sizeof...(KArgs) == sizeof...(Args), "kernel argument count");
+  std::tuple<KArgs...> vals{static_cast<KArgs>(args)...};
+  void* ptrs[sizeof...(KArgs) ? sizeof...(KArgs) : 1];
+  tuple_pointers(vals, ptrs, std::index_sequence_for<KArgs...>{});
+  return launch_raw((const void*)kernel, grid, block, smem, stream, ptrs, cluster_x);
 }
