@@ -415,6 +415,8 @@ def tcgen05_library():
         P, I = c_void_p, c_int
         lib.ie_gemm_tcgen05.argtypes = [P, P, P, I, I, I, I, I, I, I, I, I, P]
         lib.ie_gemm_tcgen05.restype = c_int
+        lib.ie_gemm_tcgen05_pair.argtypes = [P, P, P, I, I, I, I, I, I, I, I, P]
+        lib.ie_gemm_tcgen05_pair.restype = c_int
         lib.ie_gemm_tcgen05_supports.argtypes = [I, I, I, I, I]
         lib.ie_gemm_tcgen05_supports.restype = c_int
         lib.ie_gemm_tcgen05_error.restype = c_int
@@ -431,14 +433,21 @@ def gemm_tcgen05_error() -> int:
     return int(tcgen05_library().ie_gemm_tcgen05_error())
 
 
-def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epi: str = "bf16", bn: int = 256) -> None:
+def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epi: str = "bf16", bn: int = 256,
+                 pair: bool = False) -> None:
     """c = a @ w^T on the fifth-generation tensor cores (TMA operands, accumulator in tensor memory).
 
     ``epi``: "bf16" store, "residual" adds into the float32 ``c``, "silu_mul" takes w's rows as alternating
-    gate/up and writes silu(gate)*up, half as wide."""
+    gate/up and writes silu(gate)*up, half as wide.  ``pair``: two SMs share a tile of 256 x 256
+    (``tcgen05.mma.cta_group::2``), each loading half of the weight tile."""
     m, k = a.shape
     n = w.shape[0]
     assert a.dtype is torch.bfloat16 and w.dtype is torch.bfloat16 and a.stride(1) == 1 and w.stride(1) == 1
+    if pair:
+        _check(tcgen05_library().ie_gemm_tcgen05_pair(_ptr(a), _ptr(w), _ptr(c), m, n, k, a.stride(0), w.stride(0),
+                                                      c.stride(0), _EPI[epi], sm_count(), _stream()),
+               f"gemm_tcgen05_pair(m={m}, n={n}, k={k}, {epi})")
+        return
     _check(tcgen05_library().ie_gemm_tcgen05(_ptr(a), _ptr(w), _ptr(c), m, n, k, a.stride(0), w.stride(0), c.stride(0),
                                              _EPI[epi], bn, sm_count(), _stream()), f"gemm_tcgen05(m={m}, n={n}, k={k}, {epi})")
 

@@ -256,10 +256,15 @@ def test_norm_handed_over_between_streaming_products(M, hidden, inter):
     assert kernels.stream_error() == 0
 
 
+@pytest.mark.parametrize("pair", [False, True])
 @pytest.mark.parametrize("M,N,K,bn", [(128, 256, 64, 256), (100, 200, 128, 128), (333, 1000, 512, 128),
-                                      (700, 1306, 192, 256), (2048, 3072, 2048, 256)])
-def test_gemm_tcgen05_against_float32(M, N, K, bn):
-    """TMA operands, tcgen05.mma with the accumulator in tensor memory, persistent over tiles, edge tiles included."""
+                                      (700, 1306, 192, 256), (2048, 3072, 2048, 256), (520, 1024, 320, 256)])
+def test_gemm_tcgen05_against_float32(M, N, K, bn, pair):
+    """TMA operands, tcgen05.mma with the accumulator in tensor memory, persistent over tiles, edge tiles included;
+    one SM a tile, and a pair of SMs on a tile of 256 x 256 (cta_group::2).  Full tiles leave through shared
+    memory, edge tiles straight from registers: the sizes have both."""
+    if pair and bn != 256:
+        pytest.skip("a pair's tile is 256 wide")
     torch.manual_seed(M + N)
     bf = torch.bfloat16
     a = torch.randn(M, K, device=DEV).to(bf)
@@ -267,14 +272,14 @@ def test_gemm_tcgen05_against_float32(M, N, K, bn):
     ref = a.float().cpu() @ w.float().cpu().T
     scale = float(ref.abs().max())
     out = torch.full((M, N), float("nan"), device=DEV, dtype=bf)
-    k().gemm_tcgen05(a, w, out, "bf16", bn)
+    k().gemm_tcgen05(a, w, out, "bf16", bn, pair)
     assert float((out.float().cpu() - ref).abs().max()) <= 1e-2 * scale
     res = torch.randn(M, N, device=DEV)
     want = res.cpu() + ref
-    k().gemm_tcgen05(a, w, res, "residual", bn)
+    k().gemm_tcgen05(a, w, res, "residual", bn, pair)
     assert float((res.cpu() - want).abs().max()) <= 2e-4 * scale + 1e-5
     h = torch.full((M, N // 2), float("nan"), device=DEV, dtype=bf)
-    k().gemm_tcgen05(a, w, h, "silu_mul", bn)
+    k().gemm_tcgen05(a, w, h, "silu_mul", bn, pair)
     want = plain_llama.silu(ref[:, 0::2]) * ref[:, 1::2]
     assert float((h.float().cpu() - want).abs().max()) <= 1e-2 * max(1.0, float(want.abs().max()))
     torch.cuda.synchronize()
