@@ -564,6 +564,16 @@ DECODE_CASES = [
     # long contexts: more blocks per stream than one round of the last block's merge takes
     (8, 2, 64, 16, [1, 1], [9000, 5], None, 64),
     (4, 1, 128, 16, [1, 2], [7, 6100], None, 64),
+    # every size of the cluster that adds the blocks of a (request, kv head) up: 4 to 8 blocks of six warps
+    # (head size 64) or three (128) for the long request, while the short one's other blocks have no keys
+    (8, 2, 64, 16, [1, 1], [1394, 5], None, 64),
+    (8, 2, 64, 16, [1, 1], [1778, 900], None, 64),
+    (8, 2, 64, 16, [1, 2], [2162, 5], None, 64),
+    (8, 2, 64, 16, [1, 1], [2546, 5], None, 64),
+    (8, 2, 64, 16, [1, 1], [2930, 2000], None, 64),
+    (4, 1, 128, 16, [1, 1], [818, 3], None, 64),
+    (4, 1, 128, 16, [1, 1], [1202, 3], None, 64),
+    (4, 1, 128, 16, [2, 1], [1394, 700], None, 64),
 ]
 
 
