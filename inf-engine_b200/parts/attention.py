@@ -107,7 +107,8 @@ class PagedAttention:
                 and s.n_heads // s.n_kv_heads <= 16):
             # a decode step: rotation and cache write ride in the attention kernel
             n_splits, split_keys = decode_splits(ctx.keys_cap, ctx.n_requests * s.n_kv_heads,
-                                                 *kernels.attention_decode_geometry(s.head_dim))
+                                                 *kernels.attention_decode_geometry(s.head_dim),
+                                                 block_slots=2 * kernels.sm_count())
             scratch = self._decode_scratch(ctx, n_splits)
             kernels.attention_decode_fused(q, k, v, out, cache.k, cache.v, kvctx.block_table, ctx.q_start,
                                            ctx.ctx_before, scratch, tables[0], tables[1], ctx.positions,
@@ -154,7 +155,8 @@ class PagedAttention:
                 # requests with at most 16 rows (decode tokens, as a rule): the split-key kernel; in a mixed step
                 # it leaves the others alone, and the prefill kernel below is given those only
                 n_splits, split_keys = decode_splits(small_keys, n_small * s.n_kv_heads,
-                                                      *kernels.attention_decode_geometry(s.head_dim))
+                                                      *kernels.attention_decode_geometry(s.head_dim),
+                                                      block_slots=2 * kernels.sm_count())
                 scratch = self._decode_scratch(ctx, n_splits)
                 kernels.attention_decode_mma(q, out, cache.k, cache.v, kvctx.block_table, ctx.q_start,
                                              ctx.ctx_before, scratch, ctx.n_requests, ctx.n_tokens, s.n_heads,
@@ -188,20 +190,22 @@ TCGEN05_MIN_ROWS = 128
 
 
 def decode_splits(keys: int, n_streams: int, warps_per_block: int = 6, max_blocks: int = 64,
-                  target_warps: int = 1200) -> tuple[int, int]:
+                  block_slots: int = 296) -> tuple[int, int]:
     """How the decode kernel cuts the keys: (number of splits, keys per split).
 
     One warp works on one split of one (request, kv head); a block's ``warps_per_block`` warps take
-    consecutive splits and add up in shared memory, and only blocks add up through memory.  Measured on
-    B200: a step is fastest when its warps about fill the GPU once (``target_warps``) and every warp of
-    every block has keys: the blocks per stream follow from the number of streams, the split is the
+    consecutive splits and add up in shared memory, the blocks of a stream add up as a cluster (up to 8) or
+    through memory.  Measured on B200: a step is fastest when its blocks fill the places the SMs have for
+    them (``block_slots``: two a SM) once and no more (batch 8 at 2,048 keys: 3, 4, 5, 6 blocks a stream
+    take 0.970, 0.946, 0.946, 1.043 ms a step; batch 64: 1, 2, 3 blocks 1.90, 2.16, 2.35 ms), and every warp
+    of every block has keys: the blocks per stream follow from the number of streams, the split is the
     stream's keys over that many warps, in steps of 32 keys between 64 and 512.  Few streams get short
-    splits and several blocks each (latency), many streams one block each (nothing goes through memory).
+    splits and several blocks each (latency), many streams one block each (nothing leaves the block).
     ``keys`` is an upper bound of the keys any request of the step holds, the tighter the better.
     """
     keys = max(int(keys), 1)
     w = max(int(warps_per_block), 1)
-    blocks = max(1, round(target_warps / (max(n_streams, 1) * w)))
+    blocks = max(1, int(block_slots) // max(n_streams, 1))
     blocks = min(blocks, max(1, keys // (64 * w)), max_blocks)           # no split shorter than 64 keys
     blocks = max(blocks, -(-keys // (512 * w)))                           # nor longer than 512, if the launch allows
     blocks = min(blocks, max_blocks)

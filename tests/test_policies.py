@@ -25,8 +25,12 @@ def test_decode_splits_fill_the_warps_of_a_block():
     # many streams: one block a stream, every warp with keys
     n, sk = decode_splits(2304, 512, 6)
     assert n == 6 and sk == 384
-    # the measured best at batch 8: three blocks of six warps, 128 keys a warp
-    assert decode_splits(2304, 64, 6) == (18, 128)
+    # the measured best at batch 8: four blocks of six warps (256 of the 296 places for a block), 96 keys a warp
+    assert decode_splits(2304, 64, 6) == (24, 96)
+    # never more blocks than places: a second round of blocks costs more than longer splits
+    for n_streams in (1, 8, 24, 64, 100, 512):
+        n, sk = decode_splits(2304, n_streams, 6)
+        assert -(-n // 6) * n_streams <= 296 or -(-n // 6) == 1
 
 
 def test_checking_device_errors_needs_no_device_when_nothing_was_loaded():
