@@ -494,8 +494,8 @@ __device__ __forceinline__ unsigned long long trace_now() {
 // A warp keeps up to DC_STAGES key tiles in flight (a decode step is a matter of latency: few bytes per
 // warp, all of them wanted as early as possible).  The warps of a block add their partial results up
 // through shared memory, in ascending order of the splits.  A (request, kv head) that one block covers
-// is finished there.  Otherwise, with up to 8 blocks per (request, kv head), these blocks are launched as one
-// thread-block cluster: each leaves its result in its own shared memory, and after a cluster barrier the first
+// is finished there.  Otherwise, with up to 8 blocks per (request, kv head) in a launch that the SMs hold at once,
+// these blocks are launched as one thread-block cluster: each leaves its result in its own shared memory, and after a cluster barrier the first
 // of them adds the blocks up in ascending order, reading the others' shared memory.  With more blocks each
 // writes one partial result to global memory and takes a ticket, and the block that takes the last ticket adds
 // the blocks up, again in ascending order: the result does not depend on which block that is, nor on the path.
@@ -922,13 +922,23 @@ static int decode_launch(MmaAttnParams& p, float* scratch, int n_requests, int n
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
-  // 2 to 8 blocks per (request, kv head): one cluster along x (IE_DECODE_NO_CLUSTER=1: the ticket path, to compare)
-  static int no_cluster = -1;
+  // 2 to 8 blocks per (request, kv head): one cluster along x (IE_DECODE_NO_CLUSTER=1: the ticket path, to compare),
+  // but only while the whole launch has a place on the SMs at once.  A cluster starts when all its blocks find room
+  // in one processing cluster at the same moment, and its blocks without keys stay until the others are done; in a
+  // launch of several rounds both keep places empty that single blocks would take one by one (32 requests of 128 to
+  // 4,096 keys at head size 128, three blocks each: a run of 162 steps took 1.34 s with clusters, 1.21 s without).
+  static int no_cluster = -1, block_places = 0;
   if (no_cluster < 0) {
     const char* e = getenv("IE_DECODE_NO_CLUSTER");
     no_cluster = (e && e[0] == '1') ? 1 : 0;
+    int dev = 0, sms = 0, per_sm = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess &&
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess &&
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_decode_kernel, DC_THREADS, smem) == cudaSuccess)
+      block_places = sms * per_sm;
   }
-  p.cluster_merge = (!no_cluster && p.n_blocks >= 2 && p.n_blocks <= 8) ? 1 : 0;
+  const long long launch_blocks = (long long)p.n_blocks * n_kv_heads * n_requests;
+  p.cluster_merge = (!no_cluster && p.n_blocks >= 2 && p.n_blocks <= 8 && launch_blocks <= block_places) ? 1 : 0;
   dim3 grid(p.n_blocks, n_kv_heads, n_requests);
   return launch_k_cluster(attention_decode_kernel, p.cluster_merge ? p.n_blocks : 1, grid, DC_THREADS, smem, stream, p);
 }
