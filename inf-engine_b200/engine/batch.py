@@ -80,6 +80,9 @@ class StepContext:
     def keys_of_small_requests(self, group: int, at_most: int) -> tuple[int, int]:
         """(how many requests bring at most ``at_most`` (token, head-in-group) pairs, the most keys one of them
         holds after this step); needs the host's copy of the step."""
+        key = ("small", group, at_most)          # every layer asks; the answer is the step's
+        if key in self._work:
+            return self._work[key]
         n, keys = 0, 0
         q_lens, before = self.host["q_lens"], self.host.get("ctx_before")
         if before is None:
@@ -88,6 +91,7 @@ class StepContext:
             if q_len * group <= at_most:
                 n += 1
                 keys = max(keys, b + q_len)
+        self._work[key] = (n, keys)
         return n, keys
 
 

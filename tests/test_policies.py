@@ -37,3 +37,16 @@ def test_checking_device_errors_needs_no_device_when_nothing_was_loaded():
     import inf_engine_b200.kernels as kernels
     if kernels._stream_lib is None and kernels._tc_lib is None and kernels._fa5_lib is None:
         kernels.check_device_errors()          # nothing loaded: nothing to read, no CUDA call
+
+
+def test_small_requests_of_a_step_are_counted_once():
+    from inf_engine_b200.engine.batch import StepContext
+    ctx = StepContext(None, 16)
+    ctx.host = {"q_lens": [1, 40, 2, 1], "ctx_before": [100, 0, 7, 3000]}
+    assert ctx.keys_of_small_requests(4, 16) == (3, 3001)      # 1, 2 and 1 tokens of four heads each: at most 16 rows
+    assert ctx.keys_of_small_requests(16, 16) == (2, 3001)
+    ctx.host["ctx_before"][0] = 9999                            # the step's answer is kept: every layer asks again
+    assert ctx.keys_of_small_requests(4, 16) == (3, 3001)
+    graph_ctx = StepContext(None, 16)
+    graph_ctx.host = {"q_lens": [1, 1]}                         # a captured step has no host copy of the lengths
+    assert graph_ctx.keys_of_small_requests(4, 16) == (0, 0)
