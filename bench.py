@@ -275,6 +275,63 @@ def run_ours(args):
     return 0
 
 
+def run_workload(args):
+    """Continuous batching through ``Engine.run_offline``: N requests with seeded uniform-random prompts of
+    MIN..MAX tokens, NEW generated tokens each (no end-of-sequence id, so every request runs its full length),
+    wall clock around the whole run; the run is made twice and the second one counts (the first one also captures
+    the decode graphs).  ``--workload N:MIN:MAX:NEW[:TEMPERATURE]``; BASELINE.json's other two workloads are
+    ``--model smollm2-1.7b --workload 64:64:2048:256`` and ``--model llama-3.2-3b --workload 32:128:4096:128``."""
+    import dataclasses
+
+    import numpy as np
+    import torch
+
+    from inf_engine_b200 import Engine, Request, SamplingConfig
+    from inf_engine_b200.config import get_preset
+
+    parts = args.workload.split(":")
+    if len(parts) not in (4, 5):
+        print("--workload wants N:MIN:MAX:NEW or N:MIN:MAX:NEW:TEMPERATURE")
+        return 2
+    n_req, lo, hi, new = (int(x) for x in parts[:4])
+    temperature = float(parts[4]) if len(parts) == 5 else 0.0
+    cfg = get_preset(args.model)
+    n_layers_full = cfg.num_hidden_layers
+    if args.layers:
+        cfg = dataclasses.replace(cfg, num_hidden_layers=args.layers)
+    rng = np.random.default_rng(args.seed)
+    lens = rng.integers(lo, hi + 1, n_req)
+    n_blocks = int(sum(int(n) + new for n in lens)) // PAGE + 4 * n_req + 64
+    sampling = SamplingConfig(mode="temperature", temperature=temperature, seed=1) if temperature > 0 else SamplingConfig()
+    torch.cuda.set_device(0)
+    engine = Engine.from_random(cfg, seed=args.seed, dtype="bfloat16", n_total_blocks=n_blocks, block_size=PAGE,
+                                max_requests=max(64, n_req), max_tokens_per_step=2048, eos_token=-1, sampling=sampling)
+
+    def once():
+        requests = [Request(i, rng.integers(0, cfg.vocab_size, int(n)).tolist(), new) for i, n in enumerate(lens)]
+        engine.stats = {"steps": 0, "prefill_tokens": 0, "decode_tokens": 0, "preemptions": 0}
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        out = engine.run_offline(requests)
+        torch.cuda.synchronize()
+        seconds = time.perf_counter() - t0
+        engine.completed.clear()
+        return seconds, sum(len(v) for v in out.values())
+
+    once()
+    seconds, generated = once()
+    prompt_tokens = int(lens.sum())
+    print(json.dumps({"impl": "ours", "workload": args.workload, "seconds": seconds, "generated": generated,
+                      "generated_tok_s": generated / seconds, "total_tok_s": (generated + prompt_tokens) / seconds,
+                      "prompt_tokens": prompt_tokens, "steps": engine.stats["steps"],
+                      "preemptions": engine.stats["preemptions"], "dtype": "bf16",
+                      "data": "synthetic: seeded random weights, uniform random prompt ids",
+                      "config": {"model": args.model, "layers": cfg.num_hidden_layers, "layers_of_model": n_layers_full,
+                                 "requests": n_req, "prompt_min": lo, "prompt_max": hi, "new_tokens": new,
+                                 "temperature": temperature, "page_size": PAGE, "max_tokens_per_step": 2048}}))
+    return 0
+
+
 def run_reference(args):
     print(json.dumps({"impl": "reference", "unavailable":
                       "the reference has no setup.py or pyproject.toml: pip install --no-index of it fails "
@@ -296,12 +353,16 @@ def main():
     ap.add_argument("--only", choices=["all", "decode", "prefill"], default="all",
                     help="measure one part only (short runs for profiling); the JSON line then lacks the rest")
     ap.add_argument("--pool-requests", type=int, default=64, help="requests of 4,096 tokens the cache pool is made for")
+    ap.add_argument("--workload", default=None, metavar="N:MIN:MAX:NEW[:TEMP]",
+                    help="instead of the step measurements: N requests through Engine.run_offline (continuous batching)")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py measures a single-GPU engine; --gpus {args.gpus} is not supported (use --gpus 1)")
         return 2
     if args.impl == "reference":
         return run_reference(args)
+    if args.workload:
+        return run_workload(args)
     args.warmup = max(args.warmup, 3)
     return run_ours(args)
 
