@@ -40,9 +40,11 @@ _REQUIRED = (
 class LlamaConfig:
     """Every size and constant of a ``LlamaForCausalLM`` checkpoint.
 
-    Defaults of the optional keys follow the reference's dataclass defaults
-    (engine/config.py:42-44): ``rope_theta`` 500000, ``rms_norm_eps`` 1e-5,
-    untied head.  ``head_dim`` defaults to ``hidden_size // num_attention_heads``
+    Defaults of the optional keys: ``rms_norm_eps`` 1e-5 and an untied head as in
+    the reference's dataclass (engine/config.py:42-44).  A ``config.json`` without
+    ``rope_theta`` means 10000, the value that checkpoints of this architecture had
+    before the key existed (the reference's 500000 is the default of its presets,
+    which name it).  ``head_dim`` defaults to ``hidden_size // num_attention_heads``
     (engine/config.py:60-66).
     """
 
@@ -55,7 +57,7 @@ class LlamaConfig:
     head_dim: int
     intermediate_size: int
     max_position_embeddings: int
-    rope_theta: float = 500000.0
+    rope_theta: float = 10000.0
     rope_scaling: RopeScaling | None = None
     rms_norm_eps: float = 1e-5
     tie_word_embeddings: bool = False
@@ -139,7 +141,7 @@ class LlamaConfig:
             head_dim=int(head_dim),
             intermediate_size=int(d["intermediate_size"]),
             max_position_embeddings=int(d["max_position_embeddings"]),
-            rope_theta=float(d.get("rope_theta", 500000.0)),
+            rope_theta=float(d.get("rope_theta", 10000.0)),
             rope_scaling=rope_scaling,
             rms_norm_eps=float(d.get("rms_norm_eps", 1e-5)),
             tie_word_embeddings=bool(d.get("tie_word_embeddings", False)),

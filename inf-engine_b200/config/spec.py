@@ -125,3 +125,4 @@ class ModelSpec:
     final_norm: NormSpec
     head: str | None                         # tensor name, or None: tied to the embedding
     optional_tensors: tuple[str, ...] = field(default_factory=tuple)  # present-but-unused names tolerated
+    kind: str = "decoder"                    # which registered top level puts the parts together

@@ -10,6 +10,9 @@
 // (and j > p - window when a window is set).  Keys and values are read from the
 // request's pages through its block table; the step's own tokens were written
 // there before this kernel runs, so every cut of the work sees the same keys.
+// An optional additive term enters the score before the softmax: a float32 table
+// bias[head][distance], distance = p - j clamped to the table's last column
+// (position encodings that bias scores by how far back a key lies).
 //
 // Work split: a block takes one (request, kv head) and a tile of 32
 // (token, head-in-group) pairs, so the `group` query heads that share a kv head
@@ -37,6 +40,8 @@ struct AttnGeneralParams {
   int q_stride, out_stride, table_stride;
   int n_work, n_heads, n_kv_heads, hd, page_size, window;
   float scale;
+  const float* score_bias;  // [n_heads][bias_dists] or null
+  int bias_dists;
 };
 
 template <typename T>
@@ -86,6 +91,9 @@ __global__ void __launch_bounds__(AG_THREADS) attention_general_kernel(AttnGener
   const int my_t = row_valid ? my_pair / group : 0;
   const int my_limit = ctx + my_t;                                    // last visible key
   const int my_first = p.window > 0 ? max(0, my_limit - p.window + 1) : 0;
+  const float* my_bias = (p.score_bias != nullptr && row_valid)
+                             ? p.score_bias + (size_t)(c * group + (my_pair - my_t * group)) * p.bias_dists
+                             : nullptr;
 
   const int last_pair = min(pair0 + AG_ROWS, n_pairs) - 1;
   const int key_end = ctx + last_pair / group + 1;                     // keys [.., key_end) matter to the tile
@@ -133,7 +141,9 @@ __global__ void __launch_bounds__(AG_THREADS) attention_general_kernel(AttnGener
       const float* kr = Ks + kk * ldq;
       for (int d = 0; d < hd; ++d) dot += qr[d] * kr[d];
       const bool visible = row_valid && kp <= my_limit && kp >= my_first;
-      s[jj] = visible ? dot * p.scale : -INFINITY;
+      float sc = dot * p.scale;
+      if (visible && my_bias != nullptr) sc += my_bias[min(my_limit - kp, p.bias_dists - 1)];
+      s[jj] = visible ? sc : -INFINITY;
       tile_max = fmaxf(tile_max, s[jj]);
     }
 #pragma unroll
@@ -186,16 +196,18 @@ extern "C" int ie_attention_general(const void* q, void* out, const void* kpool,
                                     const int* block_table, const int* q_start, const int* ctx_before,
                                     const int* work_req, const int* work_pair0, int q_stride, int out_stride,
                                     int table_stride, int n_work, int n_heads, int n_kv_heads, int hd,
-                                    int page_size, int window, float scale, int act_dtype, cudaStream_t stream) {
+                                    int page_size, int window, float scale, int act_dtype, const float* score_bias,
+                                    int bias_dists, cudaStream_t stream) {
   if (n_work <= 0) return IE_OK;
   if (hd % 16 || hd > 8 * AG_MAX_ACC || hd <= 0) return IE_BAD_SIZE;
   if (n_kv_heads <= 0 || n_heads % n_kv_heads) return IE_BAD_SIZE;
+  if (score_bias != nullptr && bias_dists <= 0) return IE_BAD_SIZE;
   AttnGeneralParams p;
   p.q = q; p.out = out; p.kpool = kpool; p.vpool = vpool; p.block_table = block_table;
   p.q_start = q_start; p.ctx_before = ctx_before; p.work_req = work_req; p.work_pair0 = work_pair0;
   p.q_stride = q_stride; p.out_stride = out_stride; p.table_stride = table_stride;
   p.n_work = n_work; p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.hd = hd; p.page_size = page_size;
-  p.window = window; p.scale = scale;
+  p.window = window; p.scale = scale; p.score_bias = score_bias; p.bias_dists = bias_dists;
   const size_t smem = sizeof(float) * ((size_t)AG_ROWS * (hd + 1) + (size_t)AG_KEYS * (hd + 1) +
                                        (size_t)AG_KEYS * hd + (size_t)AG_ROWS * (AG_KEYS + 1));
   dim3 grid(n_work, n_kv_heads);

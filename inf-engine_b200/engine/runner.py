@@ -15,8 +15,7 @@ import torch
 
 from ..cache.manager import CacheManager
 from ..config.registry import detect_config
-from ..parts.model import DecoderModel
-from ..parts.registry import expected_tensors
+from ..parts.registry import build_model, expected_tensors
 from ..parts.runtime import Runtime
 from ..weights.loader import load_weights
 from .batch import StepEntry, build_context
@@ -47,7 +46,7 @@ class ModelRunner:
         self.device = torch.device(device)
         torch.cuda.set_device(self.device)
         self.rt = Runtime(self.device, self.dtype)
-        self.model = DecoderModel(self.spec, tensors, self.rt)
+        self.model = build_model(self.spec, tensors, self.rt)     # the top level that spec.kind names
         max_pages_per_request = -(-self.spec.max_positions // page_size)
         self.cache = CacheManager(self.model.cache_requirements(), page_size, n_pages, max_requests,
                                   min(n_pages, max_pages_per_request))

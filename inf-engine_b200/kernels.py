@@ -76,7 +76,7 @@ def core():
         lib.ie_residual_add.argtypes = [P, P, I, I, I, P]
         lib.ie_rope_kv_write.argtypes = [P, P, P, I, I, P, P, P, P, P, P, I, I, I, I, I, I, I, P]
         lib.ie_silu_mul.argtypes = [P, P, I, I, I, I, I, P]
-        lib.ie_attention_general.argtypes = [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P]
+        lib.ie_attention_general.argtypes = [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P, I, P]
         lib.ie_gemm_simt.argtypes = [P, I, P, I, P, I, I, I, I, I, I, I, P]
         lib.ie_argmax.argtypes = [P, P, I, I, L, P]
         lib.ie_repetition_penalty.argtypes = [P, P, P, I, I, L, I, P]
@@ -161,14 +161,20 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, interleaved: bool = False
 def attention_general(q: torch.Tensor, out: torch.Tensor, kpool: torch.Tensor, vpool: torch.Tensor,
                       block_table: torch.Tensor, q_start: torch.Tensor, ctx_before: torch.Tensor,
                       work_req: torch.Tensor, work_pair0: torch.Tensor, n_work: int, n_heads: int,
-                      n_kv_heads: int, head_dim: int, page_size: int, window: int | None, scale: float) -> None:
+                      n_kv_heads: int, head_dim: int, page_size: int, window: int | None, scale: float,
+                      score_bias: torch.Tensor | None = None) -> None:
+    """Paged causal attention in float32 arithmetic.  ``score_bias`` (float32 [n_heads, D], contiguous) is added to
+    the scaled score of a query at position p and a key at position j as ``score_bias[head, min(p - j, D - 1)]``."""
     assert q.stride(1) == 1 and out.stride(1) == 1 and kpool.dtype == q.dtype == out.dtype
     assert block_table.dtype == torch.int32 and block_table.stride(1) == 1
+    if score_bias is not None:
+        assert score_bias.dtype is torch.float32 and score_bias.is_contiguous() and score_bias.shape[0] == n_heads
     _check(core().ie_attention_general(_ptr(q), _ptr(out), _ptr(kpool), _ptr(vpool), _ptr(block_table),
                                        _ptr(q_start), _ptr(ctx_before), _ptr(work_req), _ptr(work_pair0),
                                        q.stride(0), out.stride(0), block_table.stride(0), n_work, n_heads,
                                        n_kv_heads, head_dim, page_size, int(window or 0), float(scale),
-                                       dtype_code(q.dtype), _stream()),
+                                       dtype_code(q.dtype), _ptr(score_bias),
+                                       score_bias.shape[1] if score_bias is not None else 0, _stream()),
            f"attention_general(head_dim={head_dim}, heads={n_heads}/{n_kv_heads})")
 
 

@@ -1,4 +1,4 @@
-from . import attention, block, feedforward, norms, positions  # noqa: F401  (register the built-in parts)
+from . import attention, block, feedforward, model, norms, positions  # noqa: F401  (register the built-in parts)
 from .attention import CacheView, PagedAttention
 from .block import PreNormBlock
 from .feedforward import GatedMLP
@@ -10,12 +10,14 @@ from .registry import (
     BLOCKS,
     FEEDFORWARDS,
     MIXERS,
+    MODELS,
     NORMS,
     POSITIONS,
     expected_tensors,
     register_block,
     register_feedforward,
     register_mixer,
+    register_model,
     register_norm,
     register_position,
 )

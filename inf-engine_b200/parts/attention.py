@@ -101,8 +101,11 @@ class PagedAttention:
         v = qkv[:, self.q_width + self.kv_width:]
         kvctx = ctx.kv[cache.group]
         tables = self.position.rotary_tables()
+        # a position encoding may bias the scores by distance (float32 [n_heads, D]); only the general kernel takes it
+        bias_of = getattr(self.position, "score_bias", None)
+        bias = bias_of() if bias_of is not None else None
         out = rt.ws.take("attn_out", (n, self.q_width), rt.act_dtype)
-        if (tables is not None and ctx.max_q_len == 1 and ctx.n_tokens == ctx.n_requests
+        if (tables is not None and bias is None and ctx.max_q_len == 1 and ctx.n_tokens == ctx.n_requests
                 and rt.act_dtype is torch.bfloat16 and s.head_dim in kernels.MMA_HEAD_DIMS
                 and s.n_heads // s.n_kv_heads <= 16):
             # a decode step: rotation and cache write ride in the attention kernel
@@ -119,11 +122,11 @@ class PagedAttention:
             self.position.rotate(q, k, ctx)
         cos, sin = tables if tables is not None else (None, None)
         # a step of prompt portions only, on the tcgen05 kernel: q is rotated where that kernel reads it
-        q_in_kernel = tables is not None and self._portions_only_on_tcgen05(ctx)
+        q_in_kernel = tables is not None and bias is None and self._portions_only_on_tcgen05(ctx)
         kernels.rope_kv_write(q, k, v, cos, sin, ctx.positions, kvctx.slot_mapping,
                               cache.k if cache.write else None, cache.v if cache.write else None,
                               s.n_heads, s.n_kv_heads, s.head_dim, ctx.page_size, rotate_q=not q_in_kernel)
-        self._attend(q, out, cache, ctx, kvctx, (cos, sin, ctx.positions) if q_in_kernel else (None, None, None))
+        self._attend(q, out, cache, ctx, kvctx, (cos, sin, ctx.positions) if q_in_kernel else (None, None, None), bias)
         return out
 
     def _portions_only_on_tcgen05(self, ctx) -> bool:
@@ -142,10 +145,10 @@ class PagedAttention:
         n = kernels.attention_decode_scratch_floats(ctx.n_tokens, s.n_heads, n_splits, s.head_dim)
         return self.rt.ws.take("attn_scratch", (n,), torch.float32)   # zero when made; tickets stay zero
 
-    def _attend(self, q, out, cache, ctx, kvctx, rotate=(None, None, None)) -> None:
+    def _attend(self, q, out, cache, ctx, kvctx, rotate=(None, None, None), bias=None) -> None:
         s = self.spec
         group = s.n_heads // s.n_kv_heads
-        if self.rt.act_dtype is torch.bfloat16 and s.head_dim in kernels.MMA_HEAD_DIMS:
+        if bias is None and self.rt.act_dtype is torch.bfloat16 and s.head_dim in kernels.MMA_HEAD_DIMS:
             # tensor-core kernels, built for this head size when first used
             n_small, small_keys = (ctx.n_requests, ctx.keys_cap) if ctx.max_q_len * group <= 16 \
                 else ctx.keys_of_small_requests(group, 16)
@@ -182,7 +185,7 @@ class PagedAttention:
         work_req, work_pair0, n_work = ctx.attention_work(group, 32)
         kernels.attention_general(q, out, cache.k, cache.v, kvctx.block_table, ctx.q_start, ctx.ctx_before,
                                   work_req, work_pair0, n_work, s.n_heads, s.n_kv_heads, s.head_dim,
-                                  ctx.page_size, s.window, self.scale)
+                                  ctx.page_size, s.window, self.scale, bias)
 
 
 # fewer (token, head-in-group) rows than this in every request: the 64-row mma.sync tiles waste less

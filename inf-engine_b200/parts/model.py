@@ -12,10 +12,23 @@ from .. import kernels
 from ..cache.manager import CacheManager, CacheRequirement
 from .attention import CacheView
 from .linear import Linear, stream_normed
-from .registry import build_block, build_norm
+from ..weights.loader import ExpectedTensor
+from .registry import block_class, build_block, build_norm, norm_class, register_model
 
 
+@register_model("decoder")
 class DecoderModel:
+    @staticmethod
+    def expected_tensors(spec) -> dict:
+        """The token table, the layers in order, the final norm, the head."""
+        out = {spec.embedding: ExpectedTensor((spec.vocab_size, spec.hidden))}
+        for blk in spec.layers:
+            out.update(block_class(blk).expected_tensors(blk))
+        out.update(norm_class(spec.final_norm).expected_tensors(spec.final_norm))
+        if spec.head is not None:
+            out[spec.head] = ExpectedTensor((spec.vocab_size, spec.hidden))
+        return out
+
     def __init__(self, spec, tensors: dict, rt):
         self.spec = spec
         self.rt = rt
@@ -60,14 +73,23 @@ class DecoderModel:
         self._views = views
 
     # ---------------------------------------------------------------- forward
+    def embed(self, ctx) -> torch.Tensor:
+        """The float32 residual stream [n_tokens, hidden] that the first block meets."""
+        residual = self.rt.ws.take("residual", (ctx.n_tokens, self.spec.hidden), torch.float32)
+        kernels.embed_gather(ctx.token_ids, self.embedding, residual)
+        return residual
+
+    def finish_logits(self, logits: torch.Tensor, ctx) -> torch.Tensor:
+        """What a derived top level does to the head's float32 logits (in place) before they leave; nothing here."""
+        return logits
+
     def forward(self, ctx) -> torch.Tensor | None:
         """Run the step's tokens through every scheduled layer; float32 logits
         [n_wanted, vocab] at ``ctx.logit_rows`` (None when nothing is wanted)."""
         assert self._views is not None, "bind_cache() first"
         rt, spec = self.rt, self.spec
         n = ctx.n_tokens
-        residual = rt.ws.take("residual", (n, spec.hidden), torch.float32)
-        kernels.embed_gather(ctx.token_ids, self.embedding, residual)
+        residual = self.embed(ctx)
         pending = None
         ctx.handover = None
         last = len(spec.schedule) - 1
@@ -80,6 +102,10 @@ class DecoderModel:
         m = ctx.n_logits
         if m == 0:
             return None
+        return self.finish_logits(self._head_logits(residual, pending, ctx, n, m), ctx)
+
+    def _head_logits(self, residual, pending, ctx, n: int, m: int) -> torch.Tensor:
+        rt, spec = self.rt, self.spec
         logits = rt.ws.take("logits", (m, spec.vocab_size), torch.float32)
         if self.head.streams(m) and hasattr(self.final_norm, "fusable_rms"):
             # final norm on the gathered rows inside the head product

@@ -15,7 +15,7 @@ from .registry import register_norm
 class RMSNorm:
     @staticmethod
     def expected_tensors(spec):
-        return {spec.weight: ExpectedTensor((spec.size,))}
+        return {spec.weight: ExpectedTensor((spec.size,), init="gain")}
 
     def __init__(self, spec, tensors, rt):
         self.spec = spec

@@ -26,7 +26,12 @@ from .safetensors_io import StoredTensor, open_checkpoint
 
 @dataclass(frozen=True)
 class ExpectedTensor:
+    """What a part says about a tensor it reads: its shape, and how the random-weights mode should draw it
+    (``"normal"``: N(0, std), matrices, biases, learned vectors; ``"gain"``: 1 + U(-spread, spread), a norm's
+    multiplier)."""
+
     shape: tuple[int, ...]
+    init: str = "normal"
 
 
 class WeightsError(ValueError):
@@ -58,10 +63,19 @@ def kept_dtype(stored: torch.dtype, run_dtype: torch.dtype) -> torch.dtype:
     return torch.bfloat16
 
 
+# Buffers that older checkpoints of this family store beside their weights and that no model reads (the rotary
+# frequencies are computed from the configuration).  They are passed over; every other unknown name is an error.
+IGNORED_SUFFIXES = (".rotary_emb.inv_freq",)
+
+
+def ignored_buffers(found) -> list[str]:
+    return sorted(n for n in found if n.endswith(IGNORED_SUFFIXES))
+
+
 def check_names_and_shapes(found: dict[str, tuple[int, ...]], expected: dict[str, ExpectedTensor],
                            optional: tuple[str, ...] = (), where: str = "") -> None:
     missing = [n for n in expected if n not in found]
-    unexpected = [n for n in found if n not in expected and n not in optional]
+    unexpected = [n for n in found if n not in expected and n not in optional and not n.endswith(IGNORED_SUFFIXES)]
     wrong = [(n, expected[n].shape, found[n]) for n in expected if n in found and tuple(found[n]) != tuple(expected[n].shape)]
     if missing or unexpected or wrong:
         raise WeightsError(missing, unexpected, wrong, where)
@@ -72,6 +86,11 @@ def load_weights(model_dir: str | Path, expected: dict[str, ExpectedTensor], run
     """Tensors of ``model_dir`` on ``device``, validated against ``expected``."""
     stored: dict[str, StoredTensor] = open_checkpoint(model_dir)
     check_names_and_shapes({n: s.shape for n, s in stored.items()}, expected, optional, where=str(model_dir))
+    passed_over = ignored_buffers(stored)
+    if passed_over:
+        import warnings
+        warnings.warn(f"checkpoint {model_dir}: {len(passed_over)} stored buffers are not weights and were passed over "
+                      f"({passed_over[0]}, ...)", stacklevel=2)
     out: dict[str, torch.Tensor] = {}
     for name in expected:
         t = stored[name].read()

@@ -23,17 +23,20 @@ def random_tensors(expected: dict, seed: int, std: float = 0.02, gain_spread: fl
                    store_dtype: str = "bfloat16") -> dict[str, torch.Tensor]:
     """One tensor per entry of ``expected`` (name -> ExpectedTensor), in that order.
 
-    One-dimensional tensors are gains; everything else is a matrix.  Large
-    matrices are drawn in slabs so that a 128k-row table needs no second copy.
+    A tensor that its part declares as a gain (``ExpectedTensor.init == "gain"``) is 1 + U(-spread, spread);
+    everything else, one-dimensional or not, is N(0, std).  Large matrices are drawn in slabs so that a
+    128k-row table needs no second copy.
     """
     dtype = _STORE[store_dtype]
     g = torch.Generator().manual_seed(int(seed))
     out = {}
     for name, exp in expected.items():
         shape = tuple(exp.shape)
-        if len(shape) == 1:
+        if getattr(exp, "init", "normal") == "gain":
             t = 1.0 + (torch.rand(shape, generator=g) * (2 * gain_spread) - gain_spread)
             out[name] = t.to(dtype)
+        elif getattr(exp, "init", "normal") != "normal":
+            raise ValueError(f"tensor {name!r}: unknown random initialisation {exp.init!r}")
         else:
             t = torch.empty(shape, dtype=dtype)
             rows = shape[0]

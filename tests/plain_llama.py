@@ -63,7 +63,7 @@ def llama3_scale_inv_freq(inv_freq: torch.Tensor, scaling: dict) -> torch.Tensor
 def rope_tables(config: dict, n_positions: int) -> tuple[torch.Tensor, torch.Tensor]:
     """cos/sin tables of shape (n_positions, head_dim) — engine/layers.py:57-79."""
     hd = head_dim_of(config)
-    inv_freq = rope_inv_freq(hd, float(config.get("rope_theta", 500000.0)))
+    inv_freq = rope_inv_freq(hd, float(config.get("rope_theta", 10000.0)))
     scaling = config.get("rope_scaling")
     if scaling:
         kind = scaling.get("rope_type", scaling.get("type"))

@@ -41,10 +41,10 @@ def test_head_dim_defaults_to_hidden_over_heads():
         parse_config_dict(d)
 
 
-def test_optional_keys_take_reference_defaults():
+def test_optional_keys_take_their_defaults():
     d = {k: v for k, v in TINY_A.items() if k not in ("rope_theta", "rms_norm_eps", "tie_word_embeddings", "rope_scaling")}
     cfg = parse_config_dict(d)
-    assert cfg.rope_theta == 500000.0 and cfg.rms_norm_eps == 1e-5 and cfg.tie_word_embeddings is False
+    assert cfg.rope_theta == 10000.0 and cfg.rms_norm_eps == 1e-5 and cfg.tie_word_embeddings is False
     assert cfg.rope_scaling is None
 
 
@@ -129,3 +129,20 @@ def test_model_spec_is_per_layer_data():
         assert blk.mixer.head_dim == 32 and blk.mixer.n_kv_heads == 2 and blk.mixer.window is None
         assert blk.mixer_norm.eps == 1e-6 and blk.feedforward.intermediate == 328
         assert blk.mixer.position.theta == 500000.0 and blk.mixer.position.scaling.factor == 8.0
+
+
+def test_a_config_without_rope_theta_means_ten_thousand():
+    # checkpoints of this architecture written before the key existed rotate with theta = 10000; the 500000 of the
+    # reference's presets (engine/config.py:42) is named by every preset file and is no default of the reader
+    d = {k: v for k, v in TINY_B.items() if k != "rope_theta"}
+    assert parse_config_dict(d).rope_theta == 10000.0
+    assert parse_config_dict(d).model_spec().layers[0].mixer.position.theta == 10000.0
+    for name in preset_names():
+        assert get_preset(name).rope_theta in (10000.0, 130000.0, 500000.0)
+
+
+def test_model_spec_names_its_top_level():
+    from inf_engine_b200.parts import MODELS, DecoderModel
+
+    spec = parse_config_dict(TINY_A).model_spec()
+    assert spec.kind == "decoder" and MODELS["decoder"] is DecoderModel

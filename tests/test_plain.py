@@ -40,6 +40,56 @@ def test_llama3_scaling_properties():
     assert (g[:-1] >= g[1:]).all()                                       # still monotone
 
 
+# llama3 frequency scaling at the parameters of the tiny-B, Llama-3.2-1B and Llama-3.2-3B configurations: which
+# frequencies are kept, which divided by the factor, and the blended ones to twelve digits.  The figures were worked
+# out once at 50 decimal digits from the published rule, stated in periods per original context (c = orig * f / 2 pi:
+# c > high keeps f, c < low gives f / factor, else t = (c - low) / (high - low) and (1 - t) f / factor + t f), which is
+# a third way of writing it beside the product's and the plain implementation's.  The reference has no such scaling
+# (engine/layers.py:57-79 builds unscaled tables), and installed packages' model code is no source for this repository.
+LLAMA3_PINS = {
+    "tiny-b": (dict(theta=500000.0, head_dim=32, factor=8.0, low=1.0, high=4.0, orig=64), 2, 13,
+               {2: 7.940300917921e-2, 15: 5.677088100760e-7}),
+    "llama-3.2-1b": (dict(theta=500000.0, head_dim=64, factor=32.0, low=1.0, high=4.0, orig=8192), 15, 14,
+                     {15: 1.290547928209e-3, 16: 4.295567965594e-4, 17: 9.708287802628e-5, 31: 9.418306725435e-8}),
+    "llama-3.2-3b": (dict(theta=500000.0, head_dim=128, factor=32.0, low=1.0, high=4.0, orig=8192), 29, 29,
+                     {29: 2.118406996780e-3, 30: 1.290547928209e-3, 31: 7.625412033564e-4, 32: 4.295567965594e-4,
+                      33: 2.227635014685e-4, 34: 9.708287802628e-5, 63: 7.672314972286e-8}),
+}
+
+
+@pytest.mark.parametrize("name", sorted(LLAMA3_PINS))
+def test_llama3_scaling_is_pinned_to_worked_out_figures(name):
+    from inf_engine_b200.config import get_preset
+    from inf_engine_b200.parts import rotary_inv_freq
+
+    a, n_kept, n_divided, pins = LLAMA3_PINS[name]
+    cfg = get_preset(name)
+    s = cfg.rope_scaling
+    assert (cfg.rope_theta, cfg.head_dim, s.factor, s.low_freq_factor, s.high_freq_factor,
+            s.original_max_position_embeddings) == (a["theta"], a["head_dim"], a["factor"], a["low"], a["high"], a["orig"])
+    product = rotary_inv_freq(cfg.model_spec().layers[0].mixer.position).double()
+    base = plain_llama.rope_inv_freq(a["head_dim"], a["theta"])
+    plain = plain_llama.llama3_scale_inv_freq(base, dict(factor=a["factor"], low_freq_factor=a["low"],
+                                                         high_freq_factor=a["high"],
+                                                         original_max_position_embeddings=a["orig"])).double()
+    # the third formulation, in float64
+    third = []
+    for i in range(a["head_dim"] // 2):
+        f = a["theta"] ** (-2.0 * i / a["head_dim"])
+        c = a["orig"] * f / (2.0 * math.pi)
+        t = (c - a["low"]) / (a["high"] - a["low"])
+        third.append(f if c > a["high"] else f / a["factor"] if c < a["low"] else (1.0 - t) * f / a["factor"] + t * f)
+    third = torch.tensor(third, dtype=torch.float64)
+    for got in (product, plain):
+        assert float(((got - third).abs() / third).max()) < 3e-7          # float32 tables against float64
+        assert int((got == base.double()).sum()) == n_kept
+        assert int(((got * a["factor"] - base.double()).abs() / base.double() < 1e-6).sum()) == n_divided
+        for i, want in pins.items():
+            assert abs(float(got[i]) - want) / want < 3e-7, (name, i, float(got[i]), want)
+    for i, want in pins.items():
+        assert abs(float(third[i]) - want) / want < 1e-11
+
+
 def test_product_rope_tables_equal_the_plain_ones():
     from helpers import TINY_A, TINY_B
     from inf_engine_b200.config import parse_config_dict

@@ -145,3 +145,34 @@ def test_random_weights_depend_on_the_seed_only(tmp_path):
     assert (a / "model.safetensors").read_bytes() != (c / "model.safetensors").read_bytes()
     _, f32 = _folder(tmp_path / "w", TINY_A, seed=7, store="float32")
     assert open_checkpoint(f32)["model.norm.weight"].dtype_tag == "F32"
+
+
+def test_stored_rotary_frequencies_are_passed_over_and_reported(tmp_path):
+    cfg, folder = _folder(tmp_path, TINY_A)
+    stored = {k: v.read().clone() for k, v in open_checkpoint(folder).items()}
+    stored["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.ones(8)
+    stored["model.layers.1.self_attn.rotary_emb.inv_freq"] = torch.ones(8)
+    d = tmp_path / "old_style"
+    d.mkdir()
+    write_safetensors(d / "model.safetensors", stored)
+    spec = cfg.model_spec()
+    with pytest.warns(UserWarning, match="2 stored buffers are not weights"):
+        out = load_weights(d, expected_tensors(spec), torch.float32, "cpu", spec.optional_tensors)
+    assert set(out) == set(expected_tensors(spec))
+    # anything else that the model does not read is still an error
+    stored["model.layers.0.self_attn.rotary_emb.other"] = torch.ones(8)
+    write_safetensors(d / "model.safetensors", stored)
+    with pytest.raises(WeightsError, match="rotary_emb.other"):
+        load_weights(d, expected_tensors(spec), torch.float32, "cpu", spec.optional_tensors)
+
+
+def test_only_declared_gains_are_drawn_as_gains():
+    from inf_engine_b200.weights.loader import ExpectedTensor
+    from inf_engine_b200.weights.random_init import random_tensors
+
+    t = random_tensors({"gain": ExpectedTensor((4096,), init="gain"), "bias": ExpectedTensor((4096,)),
+                        "matrix": ExpectedTensor((64, 64))}, seed=3, std=0.02, store_dtype="float32")
+    assert abs(float(t["gain"].mean()) - 1.0) < 0.01 and float(t["gain"].min()) >= 0.9
+    assert abs(float(t["bias"].mean())) < 0.005 and 0.015 < float(t["bias"].std()) < 0.025
+    with pytest.raises(ValueError, match="unknown random initialisation"):
+        random_tensors({"x": ExpectedTensor((4,), init="ones")}, seed=0)
