@@ -332,10 +332,169 @@ def run_workload(args):
     return 0
 
 
+REF_DIR = os.path.join(ROOT, "baseline", "_ref")
+
+
+def _reference_package():
+    """The reference's ``engine`` package, unmodified, under ``baseline/_ref`` (git-ignored).  It has no setup.py or
+    pyproject.toml, so ``pip install --target baseline/_ref`` refuses it; it is pure Python over torch and runs from a
+    plain copy of its folder, which is made here when a checkout of the reference lies beside this repository."""
+    if not os.path.isfile(os.path.join(REF_DIR, "engine", "llama_paged_engine.py")):
+        src = os.environ.get("INF_ENGINE_REFERENCE", os.path.join(os.path.dirname(ROOT), "reference"))
+        if not os.path.isfile(os.path.join(src, "engine", "llama_paged_engine.py")):
+            return f"no copy of the reference's engine package under baseline/_ref and no checkout at {src}"
+        import shutil
+        os.makedirs(REF_DIR, exist_ok=True)
+        shutil.copytree(os.path.join(src, "engine"), os.path.join(REF_DIR, "engine"))
+    return None
+
+
 def run_reference(args):
-    print(json.dumps({"impl": "reference", "unavailable":
-                      "the reference has no setup.py or pyproject.toml: pip install --no-index of it fails "
-                      "('not installable'), so no unmodified install exists under baseline/_ref"}))
+    """The reference arm: the UNMODIFIED reference (``baseline/_ref/engine``) through its own public API and stock
+    path: ``LlamaModel`` over a ``LlamaWeights`` dictionary of seeded random bfloat16 tensors (built as its own
+    tests build one, tests/test_paged_cache.py:42-72) at its ``LLAMA_3_2_1B`` preset (engine/config.py:77-89),
+    ``LlamaPagedEngine(model, n_total_blocks, block_size)`` with its defaults (engine/llama_paged_engine.py:129-166),
+    prompts through ``submit`` and ``step`` (:169-174, :418-442).  Nothing of this repository's package is imported in
+    this process.  Same metric, batch, prompt length, pool and page size as the other arm."""
+    why = _reference_package()
+    if why:
+        print(json.dumps({"impl": "reference", "unavailable": why}))
+        return 0
+    sys.path.insert(0, REF_DIR)
+    try:
+        import numpy as np
+        import torch
+        from engine.config import LLAMA_3_2_1B, LLAMA_3_2_3B, SMOLLM2_1_7B
+        from engine.llama_model import LlamaModel
+        from engine.llama_paged_engine import LlamaPagedEngine, LlamaRequest
+        from engine.llama_weights import LlamaWeights
+    except Exception as e:                                   # noqa: BLE001 - whatever keeps it from importing
+        print(json.dumps({"impl": "reference", "unavailable": f"the reference does not import here: {e!r}"[:300]}))
+        return 0
+    presets = {"llama-3.2-1b": LLAMA_3_2_1B, "llama-3.2-3b": LLAMA_3_2_3B, "smollm2-1.7b": SMOLLM2_1_7B}
+    if args.model not in presets:
+        print(json.dumps({"impl": "reference", "unavailable": f"the reference has no preset for {args.model}"}))
+        return 0
+    if not torch.cuda.is_available():
+        print(json.dumps({"impl": "reference", "unavailable": "no CUDA device"}))
+        return 0
+    cfg = presets[args.model]
+    n_layers_full = cfg.n_layer
+    if args.layers:
+        import dataclasses
+        cfg = dataclasses.replace(cfg, n_layer=args.layers)
+    pk = peaks()
+    dev = "cuda:0"
+    torch.cuda.set_device(0)
+    g = torch.Generator(device=dev).manual_seed(args.seed)
+    d, hq, hk, f, V = cfg.d_model, cfg.n_head * cfg.head_dim, cfg.n_kv_heads * cfg.head_dim, cfg.intermediate_size, cfg.vocab_size
+
+    def mat(*shape):
+        return (torch.randn(*shape, generator=g, device=dev, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+
+    def gain():
+        return (1.0 + (torch.rand(d, generator=g, device=dev) * 0.2 - 0.1)).to(torch.bfloat16)
+
+    tensors = {"model.embed_tokens.weight": mat(V, d), "model.norm.weight": gain()}
+    for i in range(cfg.n_layer):
+        p = f"model.layers.{i}."
+        tensors.update({p + "input_layernorm.weight": gain(), p + "post_attention_layernorm.weight": gain(),
+                        p + "self_attn.q_proj.weight": mat(hq, d), p + "self_attn.k_proj.weight": mat(hk, d),
+                        p + "self_attn.v_proj.weight": mat(hk, d), p + "self_attn.o_proj.weight": mat(d, hq),
+                        p + "mlp.gate_proj.weight": mat(f, d), p + "mlp.up_proj.weight": mat(f, d),
+                        p + "mlp.down_proj.weight": mat(d, f)})
+    if not cfg.tie_word_embeddings:
+        tensors["lm_head.weight"] = mat(V, d)
+    model = LlamaModel(LlamaWeights(tensors, cfg), cfg)
+    engine = LlamaPagedEngine(model, n_total_blocks=args.pool_requests * POOL_CONTEXT // PAGE, block_size=PAGE)
+    rng = np.random.default_rng(args.seed)
+    clocks = ClockSampler()
+    clocks.start()
+
+    def prompt():
+        return rng.integers(0, V, PROMPT_LEN).tolist()
+
+    # prefill: one 2,048-token request that is done after its first token, so step() is its prefill and nothing else
+    def prefill_once():
+        engine.submit(LlamaRequest(req_id=-1, prompt_ids=prompt(), max_new_tokens=1))
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        engine.step()
+        e1.record()
+        torch.cuda.synchronize()
+        engine.completed.clear()
+        return e0.elapsed_time(e1)
+
+    for _ in range(3):
+        prefill_once()
+    pre_ms = sorted(prefill_once() for _ in range(args.prefill_reps))
+    pre = pre_ms[len(pre_ms) // 2]
+    L, H, hd = cfg.n_layer, cfg.n_head, cfg.head_dim
+    linear_params = L * ((hq + 2 * hk) * d + d * hq + 3 * f * d)
+    flops = 2 * PROMPT_LEN * linear_params + L * 4 * H * hd * (PROMPT_LEN * (PROMPT_LEN + 1) // 2) + 2 * V * d
+    prefill = {"value": PROMPT_LEN / pre * 1e3, "unit": "tok/s", "tokens": PROMPT_LEN, "ms": pre,
+               "frac": flops / (pre * 1e-3) / (pk["bf16_tflops"] * 1e12), "peak_tflops": pk["bf16_tflops"],
+               "peak_source": pk["source"], "note": "flops of the wanted logit row only; the reference computes every row's"}
+
+    def decode(batch, steps, warmup):
+        reqs = [LlamaRequest(req_id=i, prompt_ids=prompt(), max_new_tokens=warmup + steps + 8) for i in range(batch)]
+        for r in reqs:
+            assert engine.submit(r)
+        engine.step()                                         # admits and prefills all of them, one decode step
+        assert len(engine._active) == batch, "the reference did not admit the whole batch"
+        for _ in range(warmup):
+            engine.step()
+        torch.cuda.synchronize()
+        ctx0 = len(reqs[0].prompt_ids) + len(reqs[0].generated)
+        n_before = sum(len(r.generated) for r in reqs)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        e0.record()
+        for _ in range(steps):
+            engine.step()                                     # reads the sampled ids on the host every step
+        e1.record()
+        torch.cuda.synchronize()
+        t1 = time.perf_counter()
+        n_tok = sum(len(r.generated) for r in reqs) - n_before
+        ms = e0.elapsed_time(e1)
+        while engine.has_work:
+            engine.step()
+        engine.completed.clear()
+        return dict(tok_s=n_tok / ms * 1e3, e2e=n_tok / (t1 - t0), ms_per_step=ms / steps, t0=t0, t1=t1,
+                    ctx=(ctx0, ctx0 + steps))
+
+    args.warmup = max(args.warmup, 3)
+    main = decode(args.batch, args.steps, args.warmup)
+    points = {}
+    for b in (1, 64):
+        if b <= args.pool_requests and not args.no_points:
+            # fewer steps: the reference's cache gathers block by block in Python, a second a step at batch 64
+            points[f"decode_b{b}"] = decode(b, max(4, args.steps // 16), 3)["tok_s"]
+    clocks.stop()
+    weight_bytes = 2 * (linear_params + V * d)
+    bytes_step = weight_bytes + args.batch * (main["ctx"][0] + args.steps / 2) * (2 * L * hk * 2)
+    achieved = bytes_step / (main["ms_per_step"] * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": "decode tok/s at batch 8 (Llama-3.2-1B size, random weights)", "impl": "reference",
+        "value": main["tok_s"], "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": main["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: seeded random weights, uniform random prompt ids",
+        "config": {"model": args.model, "layers": cfg.n_layer, "layers_of_model": n_layers_full, "hidden": d,
+                   "heads": cfg.n_head, "kv_heads": cfg.n_kv_heads, "head_dim": hd, "intermediate": f, "vocab": V,
+                   "global_batch": args.batch, "seq_len": PROMPT_LEN, "context_start": main["ctx"][0],
+                   "context_end": main["ctx"][1], "pool_context": POOL_CONTEXT, "page_size": PAGE,
+                   "parallelism": "single-gpu", "l2": "inputs larger than L2 (weights 2.5 GB per step)",
+                   "decode": "the reference's defaults: eager steps, enable_cuda_graphs=False"},
+        "e2e": {"value": main["e2e"], "unit": "tok/s", "h2d_bytes_per_step": 8 * args.batch,
+                "d2h_bytes_per_step": 8 * args.batch,
+                "note": "the reference builds its step tensors from Python lists and reads int64 ids back (.tolist())"},
+        "gpu_launches": 0, "launch_note": "library kernels only (torch); none of this repository's",
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": achieved / pk["hbm_gbs"], "peak_source": pk["source"]},
+        "points": points, "clocks": clocks.summary(main["t0"], main["t1"]),
+    }))
     return 0
 
 
@@ -353,6 +512,7 @@ def main():
     ap.add_argument("--only", choices=["all", "decode", "prefill"], default="all",
                     help="measure one part only (short runs for profiling); the JSON line then lacks the rest")
     ap.add_argument("--pool-requests", type=int, default=64, help="requests of 4,096 tokens the cache pool is made for")
+    ap.add_argument("--no-points", action="store_true", help="leave out the batch-1 and batch-64 points")
     ap.add_argument("--workload", default=None, metavar="N:MIN:MAX:NEW[:TEMP]",
                     help="instead of the step measurements: N requests through Engine.run_offline (continuous batching)")
     args = ap.parse_args()

@@ -127,14 +127,18 @@ class CacheManager:
         self.lengths: dict = {}      # request id -> tokens held
         self.reserved: dict = {}     # request id -> tokens that pages are reserved for
         self.device = None
+        # A debugging aid: pages that nobody holds are filled with NaN (all of them at the start, each one again when
+        # it is given back), so that a kernel that reads a key or value it has no right to shows at once.
+        self.poison_free_pages = False
 
     # ------------------------------------------------------------------ storage
     def allocate_storage(self, device) -> None:
         self.device = torch.device(device)
         for g in self.kv_groups:
             shape = (len(g.entries), self.n_pages, g.n_kv_heads, self.page_size, g.head_dim)
-            g.k = torch.zeros(shape, dtype=g.dtype, device=self.device)
-            g.v = torch.zeros(shape, dtype=g.dtype, device=self.device)
+            fill = float("nan") if self.poison_free_pages else 0.0
+            g.k = torch.full(shape, fill, dtype=g.dtype, device=self.device)
+            g.v = torch.full(shape, fill, dtype=g.dtype, device=self.device)
         for g in self.state_groups:
             g.data = torch.zeros((len(g.entries), self.max_requests) + g.shape, dtype=g.dtype, device=self.device)
 
@@ -214,10 +218,17 @@ class CacheManager:
             table = g.tables[rid]
             lo = g.first_live[rid]
             if first > lo:
-                g.pool.free([p for p in table[lo:first] if p >= 0])
+                self._give_back(g, [p for p in table[lo:first] if p >= 0])
                 for i in range(lo, min(first, len(table))):
                     table[i] = -1
                 g.first_live[rid] = first
+
+    def _give_back(self, g: KVGroup, pages: list[int]) -> None:
+        g.pool.free(pages)
+        if self.poison_free_pages and pages and g.k is not None:
+            idx = torch.tensor(pages, dtype=torch.long, device=g.k.device)
+            g.k.index_fill_(1, idx, float("nan"))
+            g.v.index_fill_(1, idx, float("nan"))
 
     def _any_table(self, rid):
         return self.kv_groups[0].tables[rid] if self.kv_groups else []
@@ -227,7 +238,7 @@ class CacheManager:
         if rid not in self.slots:
             raise PageAccountingError(f"request {rid!r} closed twice or never opened")
         for g in self.kv_groups:
-            g.pool.free([p for p in g.tables.pop(rid) if p >= 0])
+            self._give_back(g, [p for p in g.tables.pop(rid) if p >= 0])
             g.first_live.pop(rid)
         self._free_slots.append(self.slots.pop(rid))
         self.lengths.pop(rid)

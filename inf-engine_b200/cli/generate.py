@@ -120,7 +120,7 @@ def main(argv=None) -> int:
     print(f"[{n_new} tokens in {t_gen:.3f} s = {n_new / max(t_gen, 1e-9):.1f} tok/s; load {t_load:.2f} s]", file=sys.stderr)
     if args.stats_json:
         Path(args.stats_json).write_text(json.dumps({"load_s": t_load, "generate_s": t_gen, "new_tokens": n_new,
-                                                     **engine.stats}, indent=1))
+                                                     **engine.stats, **engine.latency_stats(requests)}, indent=1))
     return 0
 
 

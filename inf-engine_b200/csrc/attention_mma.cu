@@ -922,15 +922,19 @@ static int decode_launch(MmaAttnParams& p, float* scratch, int n_requests, int n
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
-  // 2 to 8 blocks per (request, kv head): one cluster along x (IE_DECODE_NO_CLUSTER=1: the ticket path, to compare),
+  // 2 to 8 blocks per (request, kv head): one cluster along x (-DIE_DC_NO_CLUSTER=1 builds the ticket path only),
   // but only while the whole launch has a place on the SMs at once.  A cluster starts when all its blocks find room
   // in one processing cluster at the same moment, and its blocks without keys stay until the others are done; in a
   // launch of several rounds both keep places empty that single blocks would take one by one (32 requests of 128 to
   // 4,096 keys at head size 128, three blocks each: a run of 162 steps took 1.34 s with clusters, 1.21 s without).
-  static int no_cluster = -1, block_places = 0;
-  if (no_cluster < 0) {
-    const char* e = getenv("IE_DECODE_NO_CLUSTER");
-    no_cluster = (e && e[0] == '1') ? 1 : 0;
+#if defined(IE_DC_NO_CLUSTER) && IE_DC_NO_CLUSTER
+  constexpr bool no_cluster = true;
+#else
+  constexpr bool no_cluster = false;
+#endif
+  static int block_places = -1;
+  if (block_places < 0) {
+    block_places = 0;
     int dev = 0, sms = 0, per_sm = 0;
     if (cudaGetDevice(&dev) == cudaSuccess &&
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess &&
@@ -951,6 +955,9 @@ extern "C" int ie_attention_decode(const void* q, void* out, const void* kpool, 
   if (n_requests <= 0) return IE_OK;
   int rc = check_common(q, out, kpool, vpool, q_stride, out_stride, n_heads, n_kv_heads, hd, page_size);
   if (rc) return rc;
+  // a request takes part with at most 16 (token, head-in-group) rows; larger ones are left to the prefill kernel,
+  // and with more than 16 query heads a kv head no request could take part at all
+  if ((n_heads / n_kv_heads) > 16) return IE_BAD_SIZE;
   MmaAttnParams p;
   fill(p, q, out, kpool, vpool, block_table, q_start, ctx_before, q_stride, out_stride, table_stride, n_heads,
        n_kv_heads, page_size, window, scale);

@@ -26,6 +26,10 @@
  *   GPU (different streams) race on the array; keep calls on one device in one
  *   stream or order them yourself.
  * - No cudaMalloc, cudaFree or allocating library routine is called.
+ * - As with ie_attention_decode, a request takes part only if it brings at most 16
+ *   rows (its tokens times the query heads per kv head): the rows of `out` that belong
+ *   to a larger request are left untouched, and a model with more than 16 query heads
+ *   per kv head is refused (-2).
  *
  * Arguments are those of ie_attention_decode without its scratch pointer; the
  * head size is the one the library was built for (ie_attention_mma_head_dim()).

@@ -9,7 +9,9 @@
 //
 //   warp 0      TMA producer: for each key tile looks the pages up in the block table and issues one tensor
 //               copy per page for K and for V into a two-stage ring (a page that is not held or lies past the
-//               end is replaced by page 0: its keys are masked and its values get weight zero)
+//               end is replaced by page 0: its keys are masked, and the value rows from the block's last key on
+//               are cleared in shared memory before the MMA reads them, so that nothing stored there, not
+//               even a NaN, reaches the output)
 //   warp 1      allocates tensor memory, issues  S = Q K^T  and  O += P V  (V is the MN-major operand: its rows
 //               are keys, as the cache stores them).  S has two buffers in tensor memory: the scores of tile j+1
 //               are issued before the thread waits for the softmax of tile j, so a softmax thread finds its next
@@ -481,6 +483,22 @@ __global__ void __launch_bounds__(FA_THREADS, Geo<HD, KT, STAGES>::BLOCKS_PER_SM
         }
       }
       l = l * corr + sum;
+      if (j == n_tiles - 1 && k_end < (j + 1) * KT) {
+        // The last tile came in as whole pages: its rows from key k_end on are the unused tail of the request's last
+        // page or a stand-in page, and hold whatever was stored there before (another request's values, NaN).
+        // Their P is zero, but 0 x NaN is NaN: the value rows are cleared before the MMA reads them.  The copies
+        // have landed (the scores of this tile, which this thread has read, were issued after them).
+        const int first_dead = k_end - j * KT;
+        unsigned char* vst = gen_base + G::V_OFF + (uint32_t)(j % STAGES) * G::KV_STAGE;
+        for (int idx = part * ROWS + r; idx < KT * G::HALVES; idx += ROWS * SPLIT) {
+          const int row = idx % KT, half = idx / KT;
+          if (row >= first_dead) {
+            uint4* dst = reinterpret_cast<uint4*>(vst + half * G::KV_HALF + row * 128);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) dst[i] = make_uint4(0u, 0u, 0u, 0u);
+          }
+        }
+      }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();

@@ -89,13 +89,13 @@ static inline int launch_status() { return (int)cudaGetLastError(); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// -DIE_NO_PDL=1 builds a library whose launches do not carry the attribute (for comparisons; the package never sets it)
 static inline bool pdl_enabled() {
-  static int on = -1;
-  if (on < 0) {
-    const char* e = getenv("IE_NO_PDL");
-    on = (e && e[0] == '1') ? 0 : 1;
-  }
-  return on == 1;
+#if defined(IE_NO_PDL) && IE_NO_PDL
+  return false;
+#else
+  return true;
+#endif
 }
 
 // cluster_x > 1: consecutive blocks along x form thread-block clusters of that size (grid.x a multiple of it)

@@ -41,7 +41,16 @@ constexpr int CONSUMER_THREADS = CONSUMER_WARPS * 32;
 constexpr int THREADS = CONSUMER_THREADS + 32;
 constexpr int ROW_PAD = 64;          // bytes added to a row's pitch: keeps 16-byte fragment loads off shared banks
 constexpr int MAX_STAGES = 12;
-constexpr unsigned SPIN_LIMIT = 1u << 20;   // polls of a wait that normally lasts microseconds
+// polls of a wait that normally lasts microseconds.  Two switches exist for the test of the give-up path alone:
+// -DIE_STREAM_SPIN_LIMIT=n shortens the waits, -DIE_STREAM_ARM_EXTRA=b arms every stage's barrier for b bytes more
+// than are copied, so that no stage ever completes and every role runs into its limit.
+#ifndef IE_STREAM_SPIN_LIMIT
+#define IE_STREAM_SPIN_LIMIT (1u << 20)
+#endif
+#ifndef IE_STREAM_ARM_EXTRA
+#define IE_STREAM_ARM_EXTRA 0
+#endif
+constexpr unsigned SPIN_LIMIT = IE_STREAM_SPIN_LIMIT;
 
 __device__ int g_stream_error = 0;
 
@@ -173,7 +182,7 @@ __device__ __forceinline__ bool produce(const TmaParams& p, int nt, const BlockC
       const uint32_t bar = b.full0 + 8 * pos.s;
       if (lane == 0) {
         ok = mbar_wait(b.empty0 + 8 * pos.s, pos.phase ^ 1);
-        if (ok) mbar_expect_tx(bar, row_bytes * rows);
+        if (ok) mbar_expect_tx(bar, row_bytes * rows + IE_STREAM_ARM_EXTRA);
       }
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       if (!ok) break;
@@ -606,14 +615,9 @@ extern "C" int ie_gemm_stream_tma(const void* A, const void* W, void* C, const v
   // it in the chain, which then prefetches its weights early: that needs dynamic + static shared memory
   // of each to stay under 113 KB.
   bool deep = (size_t)N * K * 2 / (size_t)n_sms > 192 * 1024;
-  {
-    static int force = -2;   // IE_STREAM_RING=shallow|deep overrides the choice (for measurements)
-    if (force == -2) {
-      const char* e = getenv("IE_STREAM_RING");
-      force = !e ? -1 : (e[0] == 's' ? 0 : 1);
-    }
-    if (force >= 0) deep = force == 1;
-  }
+#if defined(IE_STREAM_RING_DEEP)      // -DIE_STREAM_RING_DEEP=0|1 fixes the choice (for measurements)
+  deep = IE_STREAM_RING_DEEP != 0;
+#endif
   size_t budget = (size_t)((deep ? 212 : 113) - (nt == 2 ? 17 : 9)) * 1024;
   int n_stages = 0;
   size_t stage_bytes = 0;

@@ -29,13 +29,6 @@ constexpr unsigned TC_SPIN_LIMIT = 1u << 20;
 
 __device__ int g_tc_error = 0;
 
-// Compile-time switches for measurements (results are then wrong or slower; the package never sets them):
-// 1 the epilogue stores nothing, 2 nor does it read tensor memory, 4 MMAs without waiting for operands (no copies),
-// 8 copies without MMAs, 16 no tile leaves through shared memory.
-#ifndef IE_TC_DIAG
-#define IE_TC_DIAG 0
-#endif
-
 // silu(g) = g / (1 + e^-g) in float32 with ex2.approx and the approximate division: a relative error near 1e-6,
 // where the bfloat16 result keeps 4e-3; the precise forms cost the gate/up product 6 % of its time
 __device__ __forceinline__ float tc_silu(float g) { return __fdividef(g, 1.f + __expf(-g)); }
@@ -280,7 +273,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tcgen05_kernel(const __gri
   pdl_wait();   // the activations come from the kernel ahead
 
   if (warp == 0) {
-    if (lane == 0 && !(IE_TC_DIAG & 4)) {
+    if (lane == 0) {
       int s = 0;
       uint32_t phase = 0;
       for (int t = blockIdx.x; t < total_tiles && !failed; t += gridDim.x) {
@@ -311,13 +304,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tcgen05_kernel(const __gri
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
         for (int kb = 0; kb < k_blocks; ++kb) {
-          if (!(IE_TC_DIAG & 4) && (failed || !tc_mbar_wait(full0 + 8 * s, phase))) { atomicExch(&g_tc_error, 2); failed = 1; break; }
+          if (failed || !tc_mbar_wait(full0 + 8 * s, phase)) { atomicExch(&g_tc_error, 2); failed = 1; break; }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t a_src = ring + s * STAGE_BYTES, w_src = a_src + A_BYTES;
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
             const uint64_t ad = umma_desc(a_src + k * UMMA_K * 2), wd = umma_desc(w_src + k * UMMA_K * 2);
-            if (!(IE_TC_DIAG & 8)) umma_f16(d_tmem, ad, wd, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            umma_f16(d_tmem, ad, wd, idesc, (kb > 0 || k > 0) ? 1u : 0u);
           }
           umma_commit(empty0 + 8 * s);          // arrives when these MMAs have read the stage
           if (++s == p.n_stages) { s = 0; phase ^= 1; }
@@ -347,29 +340,25 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tcgen05_kernel(const __gri
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
         uint32_t r[32];
-        if (!(IE_TC_DIAG & 2)) {
-          tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c0), r);
-          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        }
+        tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c0), r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         if (c0 + 32 >= BN) {
           // everything of this accumulator is in registers: the MMA thread may reuse it
           asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
           __syncwarp();
           if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty0 + 8 * buf) : "memory");
         }
-        if (!(IE_TC_DIAG & 3)) {
-          if (staged) {
-            tc_stage_row(stage, lane, off, p.epi, r);
-            off += out32;
-            if (off == 128) {
-              __syncwarp();
-              tc_flush(p, stage, lane, m - lane, (size_t)(n0 + c0 + 32) * (out32 >> 5) - 128);
-              __syncwarp();
-              off = 0;
-            }
-          } else {
-            tc_epilogue_store(p, m, n0 + c0, r);
+        if (staged) {
+          tc_stage_row(stage, lane, off, p.epi, r);
+          off += out32;
+          if (off == 128) {
+            __syncwarp();
+            tc_flush(p, stage, lane, m - lane, (size_t)(n0 + c0 + 32) * (out32 >> 5) - 128);
+            __syncwarp();
+            off = 0;
           }
+        } else {
+          tc_epilogue_store(p, m, n0 + c0, r);
         }
       }
     }
@@ -380,210 +369,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tcgen05_kernel(const __gri
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "n"(2 * BN) : "memory");
-  }
-}
-
-// ------------------------------------------------------------------ two SMs on one tile (cta_group::2)
-// The same product with a pair of blocks (a cluster of two, on the two SMs of a pair) on one tile of 256 rows by
-// BN columns.  Block r of the pair owns rows 128 r .. 128 r + 127: it loads those rows of A and HALF of the weight
-// tile (weight rows BN/2 r .. + BN/2 - 1), so a k block costs an SM 16 KB + BN/2 * 128 bytes of shared-memory
-// traffic instead of 16 KB + BN * 128.  One thread of the first block issues tcgen05.mma.cta_group::2 (M = 256):
-// the tensor cores of both SMs read both blocks' shared memory and each fills its own tensor memory (128 lanes x
-// BN columns).  Hand-overs:
-//   full[s]       in the first block only: its producer arms it with the bytes of BOTH blocks' copies; the second
-//                 block's copies complete on it too (.cta_group::2 form of the tensor copy, barrier address mapped
-//                 into the first block)
-//   empty[s]      in each block, one arrival: tcgen05.commit.cta_group::2 arrives on both at once
-//   acc_full[b]   in each block, one arrival: the same commit form
-//   acc_empty[b]  in the first block, eight arrivals: the four epilogue warps of each block
-// Every wait is bounded; both blocks always reach the cluster barrier at the end, after which tensor memory is freed.
-__device__ __forceinline__ uint32_t tc_cluster_rank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-__device__ __forceinline__ uint32_t tc_map_to_rank(uint32_t local_addr, uint32_t rank) {
-  uint32_t remote;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
-  return remote;
-}
-__device__ __forceinline__ void tc_cluster_sync() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-// tensor copy of a block of a pair: completes on a barrier that may lie in the other block of the pair
-__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t cluster_bar) {
-  asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-               ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(cluster_bar) : "memory");
-}
-__device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}"
-               ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-// arrives on the barrier at this offset in both blocks of the pair when the MMAs issued so far are done
-__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
-  const uint16_t both = 3;
-  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
-               ::"r"(bar), "h"(both) : "memory");
-}
-__device__ __forceinline__ void tc_mbar_arrive_cluster(uint32_t cluster_bar) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
-}
-
-template <int BN>
-__global__ void __launch_bounds__(TC_THREADS, 1) gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a,
-                                                                          const __grid_constant__ CUtensorMap map_w,
-                                                                          TcParams p) {
-  extern __shared__ __align__(1024) unsigned char smem_raw[];
-  __shared__ __align__(8) unsigned long long bars[2 * 8 + 4];
-  __shared__ uint32_t tmem_base_slot;
-  __shared__ volatile int failed;
-  constexpr int PM = 2 * BM;                    // rows of a pair's tile
-  constexpr int HALF_N = BN / 2;                // weight rows a block loads
-  constexpr uint32_t A_BYTES = BM * BK * 2, W_BYTES = HALF_N * BK * 2, STAGE_BYTES = A_BYTES + W_BYTES;
-
-  pdl_trigger();
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const uint32_t rank = tc_cluster_rank();      // 0: issues the MMAs and owns full[] and acc_empty[]
-  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
-  const uint32_t ring = (saddr(smem_raw) + 1023u) & ~1023u;
-  const uint32_t full0 = saddr(&bars[0]), empty0 = saddr(&bars[8]);
-  const uint32_t acc_full0 = saddr(&bars[16]), acc_empty0 = saddr(&bars[18]);
-  const int k_blocks = p.K / BK;
-  const int m_tiles = (p.M + PM - 1) / PM, n_tiles = (p.N + BN - 1) / BN;
-  const int total_tiles = m_tiles * n_tiles;
-
-  if (tid == 0) {
-    failed = 0;
-    for (int s = 0; s < p.n_stages; ++s) {
-      tc_mbar_init(full0 + 8 * s, 1);
-      tc_mbar_init(empty0 + 8 * s, 1);
-    }
-    for (int b = 0; b < 2; ++b) {
-      tc_mbar_init(acc_full0 + 8 * b, 1);
-      tc_mbar_init(acc_empty0 + 8 * b, 8);     // one arrival per epilogue warp of either block
-    }
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  if (warp == 1) {
-    // the same warp of both blocks: one allocation of 2 BN columns in each block's tensor memory
-    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(saddr(&tmem_base_slot)), "n"(2 * BN) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
-  }
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-  __syncthreads();
-  tc_cluster_sync();                            // the other block's barriers exist before anything arrives on them
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  const uint32_t tmem_base = tmem_base_slot;
-
-  pdl_wait();   // the activations come from the kernel ahead
-
-  if (warp == 0) {
-    if (lane == 0 && !(IE_TC_DIAG & 4)) {
-      const uint32_t full_first = tc_map_to_rank(full0, 0);     // full[] of the first block, as this block addresses it
-      int s = 0;
-      uint32_t phase = 0;
-      for (int t = pair; t < total_tiles && !failed; t += n_pairs) {
-        const int m0 = (t % m_tiles) * PM + (int)rank * BM, n0 = (t / m_tiles) * BN + (int)rank * HALF_N;
-        for (int kb = 0; kb < k_blocks; ++kb) {
-          if (failed || !tc_mbar_wait(empty0 + 8 * s, phase ^ 1)) { atomicExch(&g_tc_error, 11); failed = 1; break; }
-          if (rank == 0) tc_mbar_expect_tx(full0 + 8 * s, 2 * STAGE_BYTES);   // both blocks' copies
-          const uint32_t a_dst = ring + s * STAGE_BYTES, w_dst = a_dst + A_BYTES;
-          tma_load_2d_pair(a_dst, &map_a, kb * BK, m0, full_first + 8 * s);
-          tma_load_2d_pair(w_dst, &map_w, kb * BK, n0, full_first + 8 * s);
-          if (++s == p.n_stages) { s = 0; phase ^= 1; }
-        }
-      }
-      // the commits that free the last stages arrive in this block's shared memory: they have to land before it leaves
-      for (int i = 0; i < p.n_stages && !failed; ++i) {
-        if (!tc_mbar_wait(empty0 + 8 * s, phase ^ 1)) { atomicExch(&g_tc_error, 15); failed = 1; break; }
-        if (++s == p.n_stages) { s = 0; phase ^= 1; }
-      }
-      if (failed) for (int i = 0; i < 2048; ++i) __nanosleep(64);   // copies already issued still land in the pair's memory
-    }
-  } else if (warp == 1) {
-    if (lane == 0 && rank == 0) {
-      const uint32_t idesc = umma_idesc(PM, BN);
-      int s = 0;
-      uint32_t phase = 0;
-      int it = 0;
-      for (int t = pair; t < total_tiles && !failed; t += n_pairs, ++it) {
-        const int buf = it & 1;
-        const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
-        // both blocks' epilogues have drained this accumulator (immediately true the first time round)
-        if (!tc_mbar_wait(acc_empty0 + 8 * buf, acc_phase ^ 1)) { atomicExch(&g_tc_error, 14); failed = 1; break; }
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
-        for (int kb = 0; kb < k_blocks; ++kb) {
-          if (!(IE_TC_DIAG & 4) && (failed || !tc_mbar_wait(full0 + 8 * s, phase))) { atomicExch(&g_tc_error, 12); failed = 1; break; }
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint32_t a_src = ring + s * STAGE_BYTES, w_src = a_src + A_BYTES;   // the same offsets in both blocks
-#pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
-            const uint64_t ad = umma_desc(a_src + k * UMMA_K * 2), wd = umma_desc(w_src + k * UMMA_K * 2);
-            if (!(IE_TC_DIAG & 8)) umma_f16_pair(d_tmem, ad, wd, idesc, (kb > 0 || k > 0) ? 1u : 0u);
-          }
-          umma_commit_pair(empty0 + 8 * s);
-          if (++s == p.n_stages) { s = 0; phase ^= 1; }
-        }
-        if (failed) break;
-        umma_commit_pair(acc_full0 + 8 * buf);
-      }
-    }
-  } else {
-    // ----------------------------------------------------------- epilogue: this block's 128 rows of the tile
-    const int quarter = warp & 3;
-    unsigned char* stage = smem_raw + (ring - saddr(smem_raw)) + (size_t)p.n_stages * STAGE_BYTES + (warp - 2) * TC_STAGE_BYTES;
-    const int out32 = tc_out_bytes32(p.epi);
-    const uint32_t acc_empty_first = tc_map_to_rank(acc_empty0, 0);
-    int it = 0;
-    for (int t = pair; t < total_tiles; t += n_pairs, ++it) {
-      const int buf = it & 1;
-      const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
-      const int m0 = (t % m_tiles) * PM + (int)rank * BM, n0 = (t / m_tiles) * BN;
-      const int m = m0 + quarter * 32 + lane;
-      bool ok = !failed && tc_mbar_wait(acc_full0 + 8 * buf, acc_phase);
-      if (!ok && lane == 0) { atomicExch(&g_tc_error, 13); failed = 1; }
-      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0 && !failed;
-      if (!ok) break;
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const bool staged = p.staged && n0 + BN <= p.N;     // full width: whole lines through shared memory
-      int off = 0;
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        uint32_t r[32];
-        if (!(IE_TC_DIAG & 2)) {
-          tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c0), r);
-          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        }
-        if (c0 + 32 >= BN) {
-          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-          __syncwarp();
-          if (lane == 0) tc_mbar_arrive_cluster(acc_empty_first + 8 * buf);
-        }
-        if (!(IE_TC_DIAG & 3)) {
-          if (staged) {
-            tc_stage_row(stage, lane, off, p.epi, r);
-            off += out32;
-            if (off == 128) {
-              __syncwarp();
-              tc_flush(p, stage, lane, m - lane, (size_t)(n0 + c0 + 32) * (out32 >> 5) - 128);
-              __syncwarp();
-              off = 0;
-            }
-          } else {
-            tc_epilogue_store(p, m, n0 + c0, r);
-          }
-        }
-      }
-    }
-  }
-
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-  __syncthreads();
-  tc_cluster_sync();      // neither block frees tensor memory, or leaves, while the other still works
-  if (warp == 1) {
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "n"(2 * BN) : "memory");
   }
 }
 
@@ -635,42 +420,6 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mw, TcParams p, i
   return launch_k(gemm_tcgen05_kernel<BN>, grid, TC_THREADS, smem, stream, ma, mw, p);
 }
 
-
-// pairs of blocks on tiles of 256 rows: as many pairs as the device runs at once (a pair needs two SMs of one
-// processing cluster, so that may be fewer than half the SMs)
-template <int BN>
-static int launch_tc_pair(const CUtensorMap& ma, const CUtensorMap& mw, TcParams p, int n_sms, cudaStream_t stream) {
-  const uint32_t stage = (BM + BN / 2) * BK * 2;
-  int n_stages = (200 * 1024 - 1024) / stage;
-  if (n_stages > 8) n_stages = 8;
-  p.n_stages = n_stages;
-  const size_t smem = (size_t)n_stages * stage + 1024 + 4 * TC_STAGE_BYTES;
-  static int max_pairs = 0;
-  if (max_pairs == 0) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(2 * (n_sms / 2));
-    cfg.blockDim = dim3(TC_THREADS);
-    cfg.dynamicSmemBytes = smem;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    int n = 0;
-    e = cudaOccupancyMaxActiveClusters(&n, gemm_tcgen05_pair_kernel<BN>, &cfg);
-    if (e != cudaSuccess) return (int)e;
-    if (n <= 0) return IE_BAD_SIZE;
-    max_pairs = n < n_sms / 2 ? n : n_sms / 2;
-  }
-  const int tiles = ((p.M + 2 * BM - 1) / (2 * BM)) * ((p.N + BN - 1) / BN);
-  const int pairs = tiles < max_pairs ? tiles : max_pairs;
-  return launch_k_cluster(gemm_tcgen05_pair_kernel<BN>, 2, dim3(2 * pairs), dim3(TC_THREADS), smem, stream, ma, mw, p);
-}
-
 }  // namespace
 
 extern "C" int ie_gemm_tcgen05_error() {
@@ -703,26 +452,6 @@ extern "C" int ie_gemm_tcgen05(const void* A, const void* W, void* C, int M, int
   if (rc) return rc;
   TcParams p;
   p.C = C; p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.epi = epi; p.n_stages = 0;
-  p.staged = (((uintptr_t)C & 15) == 0 && ((size_t)ldc * (epi == TC_EPI_RESIDUAL ? 4 : 2)) % 16 == 0 && !(IE_TC_DIAG & 16)) ? 1 : 0;
+  p.staged = (((uintptr_t)C & 15) == 0 && ((size_t)ldc * (epi == TC_EPI_RESIDUAL ? 4 : 2)) % 16 == 0) ? 1 : 0;
   return bn == 256 ? launch_tc<256>(ma, mw, p, n_sms, stream) : launch_tc<128>(ma, mw, p, n_sms, stream);
-}
-
-// The same product by pairs of blocks on tiles of 256 x 256 (cta_group::2): for many rows (M of 256 and more pays).
-extern "C" int ie_gemm_tcgen05_pair(const void* A, const void* W, void* C, int M, int N, int K, int lda, int ldw,
-                                    int ldc, int epi, int n_sms, cudaStream_t stream) {
-  if (n_sms < 2) return IE_BAD_SIZE;
-  if (M <= 0 || N <= 0) return IE_OK;
-  if (!ie_gemm_tcgen05_supports(M, N, K, lda, ldw)) return IE_BAD_SIZE;
-  if (((uintptr_t)A | (uintptr_t)W) & 15) return IE_BAD_ALIGN;
-  if (epi != TC_EPI_BF16 && epi != TC_EPI_SILU_MUL && epi != TC_EPI_RESIDUAL) return IE_BAD_DTYPE;
-  if (epi == TC_EPI_SILU_MUL && (N & 1)) return IE_BAD_SIZE;
-  CUtensorMap ma, mw;
-  int rc = make_map(&ma, A, M, K, lda, BM);
-  if (rc) return rc;
-  rc = make_map(&mw, W, N, K, ldw, 128);     // each block of a pair loads half of the 256 weight rows
-  if (rc) return rc;
-  TcParams p;
-  p.C = C; p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.epi = epi; p.n_stages = 0;
-  p.staged = (((uintptr_t)C & 15) == 0 && ((size_t)ldc * (epi == TC_EPI_RESIDUAL ? 4 : 2)) % 16 == 0 && !(IE_TC_DIAG & 16)) ? 1 : 0;
-  return launch_tc_pair<256>(ma, mw, p, n_sms, stream);
 }

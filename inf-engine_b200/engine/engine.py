@@ -68,7 +68,22 @@ class Engine:
 
     # ------------------------------------------------------------------ queue
     def submit(self, req: Request) -> bool:
+        if not req.arrival_time:
+            req.arrival_time = time.perf_counter()      # the clock that run_offline and generate step with
         return self.scheduler.submit(req)
+
+    @staticmethod
+    def latency_stats(requests: list[Request]) -> dict:
+        """Time to the first token and time per later token over finished requests: mean, median and worst, in
+        seconds, and the per-request figures."""
+        def summary(values):
+            v = sorted(x for x in values if x is not None)
+            if not v:
+                return None
+            return {"mean": sum(v) / len(v), "p50": v[len(v) // 2], "max": v[-1]}
+        per = [{"req_id": r.req_id, "prompt_tokens": len(r.prompt_ids), "new_tokens": len(r.generated),
+                "ttft_s": r.ttft, "tpot_s": r.tpot, "preemptions": r.preemptions} for r in requests if r.finish_time]
+        return {"ttft_s": summary(p["ttft_s"] for p in per), "tpot_s": summary(p["tpot_s"] for p in per), "requests": per}
 
     @property
     def has_work(self) -> bool:

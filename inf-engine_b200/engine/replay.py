@@ -24,7 +24,7 @@ import json
 import sys
 from pathlib import Path
 
-MAX_LIVE_REQUESTS = 16
+MAX_LIVE_REQUESTS = 64
 
 
 def main(argv=None) -> int:
@@ -35,6 +35,8 @@ def main(argv=None) -> int:
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens that live requests hold at any time (rounded up per request to 64)")
     ap.add_argument("--page-size", type=int, default=16, help="tokens per cache page (a divisor of 64)")
+    ap.add_argument("--poison-free-pages", action="store_true",
+                    help="fill every cache page that no request holds with NaN (at the start and when it is given back)")
     ap.add_argument("--device", default="cuda:0")
     args = ap.parse_args(argv)
     if args.page_size <= 0 or 64 % args.page_size:
@@ -53,7 +55,8 @@ def main(argv=None) -> int:
     out_dir.mkdir(parents=True, exist_ok=True)
     n_pages = max(1, -(-args.max_tokens // args.page_size))
     runner = ModelRunner.from_dir(args.model, dtype=args.dtype, device=args.device, page_size=args.page_size,
-                                  n_pages=n_pages, max_requests=MAX_LIVE_REQUESTS)
+                                  n_pages=n_pages, max_requests=MAX_LIVE_REQUESTS,
+                                  poison_free_pages=args.poison_free_pages)
     for line in sys.stdin:
         line = line.strip()
         if not line:

@@ -39,7 +39,7 @@ def parse_dtype(dtype) -> torch.dtype:
 
 class ModelRunner:
     def __init__(self, config, tensors: dict, dtype, device="cuda:0", page_size: int = 16, n_pages: int = 256,
-                 max_requests: int = 64, spec=None, use_graphs: bool = True):
+                 max_requests: int = 64, spec=None, use_graphs: bool = True, poison_free_pages: bool = False):
         self.config = config
         self.spec = spec if spec is not None else config.model_spec()
         self.dtype = parse_dtype(dtype)
@@ -50,6 +50,7 @@ class ModelRunner:
         max_pages_per_request = -(-self.spec.max_positions // page_size)
         self.cache = CacheManager(self.model.cache_requirements(), page_size, n_pages, max_requests,
                                   min(n_pages, max_pages_per_request))
+        self.cache.poison_free_pages = poison_free_pages      # a debugging aid: NaN in every page that nobody holds
         self.cache.allocate_storage(self.device)
         self.model.bind_cache(self.cache)
         self.page_size = page_size

@@ -58,6 +58,19 @@ class Request:
     def tokens(self) -> list[int]:
         return self.prompt_ids + self.generated
 
+    # the reference keeps the three time stamps (engine/llama_paged_engine.py:92-95) and leaves the figures to its caller
+    @property
+    def ttft(self) -> float | None:
+        """Seconds from arrival to the first generated token (None until there is one)."""
+        return self.start_time - self.arrival_time if self.start_time else None
+
+    @property
+    def tpot(self) -> float | None:
+        """Seconds per generated token after the first (None unless finished with at least two)."""
+        if not self.finish_time or len(self.generated) < 2:
+            return None
+        return (self.finish_time - self.start_time) / (len(self.generated) - 1)
+
 
 PLACEHOLDER = -1    # stands in ``generated`` for a token that was sampled on the device and not read yet
 

@@ -8,7 +8,6 @@ missing library is an error.
 from __future__ import annotations
 
 import ctypes
-import os
 from ctypes import c_float, c_int, c_longlong, c_void_p
 
 import torch
@@ -33,6 +32,11 @@ def dtype_code(dtype: torch.dtype) -> int:
 
 
 LAUNCHES = 0     # launchers called so far (graph replays add what their capture counted)
+
+# Extra -D flags per library ("core", "stream", "tcgen05", "attn_tcgen05", "attn_mma"), read when a library is first
+# loaded.  Empty in the product; a measurement or a test that wants a variant (clock notes, no programmatic
+# dependent launch, a short spin limit) fills it before the first call or passes ``defines`` to the loader itself.
+BUILD_DEFINES: dict[str, dict] = {}
 
 
 def _check(status: int, what: str) -> None:
@@ -65,7 +69,7 @@ _core = None
 def core():
     global _core
     if _core is None:
-        lib = load_library("core")
+        lib = load_library("core", defines=dict(BUILD_DEFINES.get("core", {})))
         P, I, F, L = c_void_p, c_int, c_float, c_longlong
         lib.ie_embed_gather.argtypes = [P, P, I, P, I, I, I, P]
         lib.ie_patch_tokens.argtypes = [P, P, P, I, P]
@@ -224,11 +228,7 @@ def attention_mma_library(head_dim: int):
         raise KernelError(f"tensor-core attention is built for head sizes {MMA_HEAD_DIMS}, not {head_dim}")
     lib = _mma.get(head_dim)
     if lib is None:
-        defines = {"IE_HD": head_dim}
-        # for measurements: IE_ATTN_DEFINES="IE_DC_WARPS=4,IE_DC_STAGES=4" builds a variant of its own
-        for item in filter(None, os.environ.get("IE_ATTN_DEFINES", "").split(",")):
-            name, _, value = item.partition("=")
-            defines[name.strip()] = int(value)
+        defines = {"IE_HD": head_dim, **BUILD_DEFINES.get("attn_mma", {})}
         lib = load_library(f"attn_mma_hd{head_dim}", ["attention_mma.cu"], defines, ["attention_noalloc.h"])
         P, I, F = c_void_p, c_int, c_float
         lib.ie_attention_prefill.argtypes = [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P]
@@ -317,26 +317,33 @@ STREAM_BEST_ROWS = 16       # beyond this the library product is faster (activat
 _EPI = {"bf16": 0, "f32": 1, "residual": 2, "silu_mul": 3, "residual_normout": 4}
 SSQ_SLOT = 16               # floats per block in a sums-of-squares array
 _stream_lib = None
+_stream_variants: dict = {}
 
 
-def stream_library():
+def _bind_stream(lib):
+    P, I, F = c_void_p, c_int, c_float
+    lib.ie_gemm_stream.argtypes = [P, P, P, P, I, P, I, I, I, I, I, I, F, I, I, I, P]
+    lib.ie_gemm_stream.restype = c_int
+    lib.ie_gemm_stream_tma.argtypes = [P, P, P, P, I, P, I, I, I, I, I, I, F, I, I, I, P, I, P, I, P, I, P]
+    lib.ie_gemm_stream_tma.restype = c_int
+    lib.ie_gemm_stream_tma_supports.argtypes = [I, I, I, I]
+    lib.ie_gemm_stream_tma_supports.restype = c_int
+    lib.ie_gemm_stream_tma_error.restype = c_int
+    return lib
+
+
+def stream_library(defines: dict | None = None):
+    """The streaming products' library.  With ``defines`` a variant compiled with those -D flags (kept apart from the
+    product's own; ``gemm_stream(..., lib=...)`` runs it)."""
     global _stream_lib
+    if defines:
+        key = repr(sorted(defines.items()))
+        if key not in _stream_variants:
+            _stream_variants[key] = _bind_stream(load_library("stream", ["gemm_stream.cu", "gemm_stream_tma.cu"], dict(defines)))
+        return _stream_variants[key]
     if _stream_lib is None:
-        # for measurements: IE_STREAM_DEFINES="IE_STREAM_TRACE=1" builds a variant that notes clock values
-        defines = {}
-        for item in filter(None, os.environ.get("IE_STREAM_DEFINES", "").split(",")):
-            name, _, value = item.partition("=")
-            defines[name.strip()] = int(value)
-        lib = load_library("stream", ["gemm_stream.cu", "gemm_stream_tma.cu"], defines)
-        P, I, F = c_void_p, c_int, c_float
-        lib.ie_gemm_stream.argtypes = [P, P, P, P, I, P, I, I, I, I, I, I, F, I, I, I, P]
-        lib.ie_gemm_stream.restype = c_int
-        lib.ie_gemm_stream_tma.argtypes = [P, P, P, P, I, P, I, I, I, I, I, I, F, I, I, I, P, I, P, I, P, I, P]
-        lib.ie_gemm_stream_tma.restype = c_int
-        lib.ie_gemm_stream_tma_supports.argtypes = [I, I, I, I]
-        lib.ie_gemm_stream_tma_supports.restype = c_int
-        lib.ie_gemm_stream_tma_error.restype = c_int
-        _stream_lib = lib
+        _stream_lib = _bind_stream(load_library("stream", ["gemm_stream.cu", "gemm_stream_tma.cu"],
+                                                dict(BUILD_DEFINES.get("stream", {}))))
     return _stream_lib
 
 
@@ -350,14 +357,14 @@ def sm_count() -> int:
     return _n_sms[dev]
 
 
-def stream_error() -> int:
+def stream_error(lib=None) -> int:
     """Reads and clears the error word of the bulk-copy streaming kernel (0: no wait ever timed out)."""
-    return int(stream_library().ie_gemm_stream_tma_error())
+    return int((lib or stream_library()).ie_gemm_stream_tma_error())
 
 
 def gemm_stream(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, m: int, epi: str = "bf16",
                 gain: torch.Tensor | None = None, eps: float = 0.0, row_index: torch.Tensor | None = None,
-                nt: int | None = None, prenormed=None, normout=None) -> None:
+                nt: int | None = None, prenormed=None, normout=None, lib=None) -> None:
     """c = a @ w^T for m <= 64 rows, bfloat16 weights, reading w once at HBM speed.
 
     With ``gain`` the input ``a`` is the float32 residual stream (rows gathered by ``row_index`` if given)
@@ -371,7 +378,7 @@ def gemm_stream(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, m: int, epi: 
     ignored, the input is ``xg`` and the 1/rms comes from ``ssq``: RMSNorm without reading the residual again."""
     n, k = w.shape
     assert w.dtype is torch.bfloat16 and w.stride(1) == 1 and a.stride(-1) == 1 and c.stride(-1) == 1
-    lib = stream_library()
+    lib = lib or stream_library()
     if prenormed is not None or normout is not None:
         pro = 2 if prenormed is not None else 0
         xg, ssq = (prenormed if prenormed is not None else (normout[0], normout[2]))
@@ -417,12 +424,10 @@ _tc_lib = None
 def tcgen05_library():
     global _tc_lib
     if _tc_lib is None:
-        lib = load_library("tcgen05", ["gemm_tcgen05.cu"])
+        lib = load_library("tcgen05", ["gemm_tcgen05.cu"], dict(BUILD_DEFINES.get("tcgen05", {})))
         P, I = c_void_p, c_int
         lib.ie_gemm_tcgen05.argtypes = [P, P, P, I, I, I, I, I, I, I, I, I, P]
         lib.ie_gemm_tcgen05.restype = c_int
-        lib.ie_gemm_tcgen05_pair.argtypes = [P, P, P, I, I, I, I, I, I, I, I, P]
-        lib.ie_gemm_tcgen05_pair.restype = c_int
         lib.ie_gemm_tcgen05_supports.argtypes = [I, I, I, I, I]
         lib.ie_gemm_tcgen05_supports.restype = c_int
         lib.ie_gemm_tcgen05_error.restype = c_int
@@ -439,21 +444,14 @@ def gemm_tcgen05_error() -> int:
     return int(tcgen05_library().ie_gemm_tcgen05_error())
 
 
-def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epi: str = "bf16", bn: int = 256,
-                 pair: bool = False) -> None:
+def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epi: str = "bf16", bn: int = 256) -> None:
     """c = a @ w^T on the fifth-generation tensor cores (TMA operands, accumulator in tensor memory).
 
     ``epi``: "bf16" store, "residual" adds into the float32 ``c``, "silu_mul" takes w's rows as alternating
-    gate/up and writes silu(gate)*up, half as wide.  ``pair``: two SMs share a tile of 256 x 256
-    (``tcgen05.mma.cta_group::2``), each loading half of the weight tile."""
+    gate/up and writes silu(gate)*up, half as wide.  ``bn``: tile width, 128 or 256."""
     m, k = a.shape
     n = w.shape[0]
     assert a.dtype is torch.bfloat16 and w.dtype is torch.bfloat16 and a.stride(1) == 1 and w.stride(1) == 1
-    if pair:
-        _check(tcgen05_library().ie_gemm_tcgen05_pair(_ptr(a), _ptr(w), _ptr(c), m, n, k, a.stride(0), w.stride(0),
-                                                      c.stride(0), _EPI[epi], sm_count(), _stream()),
-               f"gemm_tcgen05_pair(m={m}, n={n}, k={k}, {epi})")
-        return
     _check(tcgen05_library().ie_gemm_tcgen05(_ptr(a), _ptr(w), _ptr(c), m, n, k, a.stride(0), w.stride(0), c.stride(0),
                                              _EPI[epi], bn, sm_count(), _stream()), f"gemm_tcgen05(m={m}, n={n}, k={k}, {epi})")
 
@@ -465,11 +463,7 @@ _fa5_lib = None
 def attention_tcgen05_library():
     global _fa5_lib
     if _fa5_lib is None:
-        defines = {}
-        for item in filter(None, os.environ.get("IE_FA_DEFINES", "").split(",")):
-            name, _, value = item.partition("=")
-            defines[name.strip()] = int(value)
-        lib = load_library("attn_tcgen05", ["attention_tcgen05.cu"], defines)
+        lib = load_library("attn_tcgen05", ["attention_tcgen05.cu"], dict(BUILD_DEFINES.get("attn_tcgen05", {})))
         P, I = c_void_p, c_int
         lib.ie_attention_tcgen05.argtypes = [P] * 9 + [I] * 9 + [c_float, P, P, P, P]
         lib.ie_attention_tcgen05.restype = c_int

@@ -25,3 +25,15 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+def pytest_sessionfinish(session, exitstatus):
+    """With IE_TEST_STATS=<file> set, what every comparison with the plain implementation measured is written there."""
+    path = os.environ.get("IE_TEST_STATS")
+    if not path:
+        return
+    import json
+
+    import helpers
+    with open(path, "w") as f:
+        json.dump(helpers.STATS, f, indent=0)

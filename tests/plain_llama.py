@@ -180,8 +180,9 @@ def block(x: torch.Tensor, w: dict, prefix: str, config: dict, cos, sin) -> torc
 
 
 # ----------------------------------------------------------------------------- model
-def forward_logits(weights: dict, config: dict, token_ids: list[int]) -> torch.Tensor:
-    """Logits (T, vocab) of one whole sequence — engine/llama_model.py:128-149.
+def forward_logits(weights: dict, config: dict, token_ids: list[int], rows: list[int] | None = None) -> torch.Tensor:
+    """Logits (T, vocab) of one whole sequence — engine/llama_model.py:128-149; with ``rows`` only
+    those positions go through the final norm and the head (a large vocabulary is slow on the CPU).
 
     Embedding row gather without scaling (:128), the blocks in order (:139-144),
     final norm (:147) and the head, which is the embedding table when
@@ -194,6 +195,8 @@ def forward_logits(weights: dict, config: dict, token_ids: list[int]) -> torch.T
     cos, sin = rope_tables(config, len(token_ids))
     for i in range(int(config["num_hidden_layers"])):
         x = block(x, w, f"model.layers.{i}.", config, cos, sin)
+    if rows is not None:
+        x = x[torch.tensor(rows, dtype=torch.long)]
     x = rms_norm(x, w["model.norm.weight"], float(config.get("rms_norm_eps", 1e-5)))
     if config.get("tie_word_embeddings", False) or "lm_head.weight" not in w:
         head = w["model.embed_tokens.weight"]

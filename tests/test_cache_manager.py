@@ -130,3 +130,32 @@ def test_random_orders_never_lose_or_share_a_page(seed):
         m.close(rid)
     m.check()
     assert all(g.pool.n_free == 24 for g in m.kv_groups) and m.n_free_slots == 5
+
+
+def test_pages_nobody_holds_can_be_filled_with_nan():
+    """The debugging aid behind ``trace_run --poison-free-pages``: every page starts as NaN and is NaN again once it is
+    given back, at the end of a request or when a window has passed it."""
+    reqs = [CacheRequirement(kind="kv", n_kv_heads=1, head_dim=4, window=None, dtype=torch.float32),
+            CacheRequirement(kind="kv", n_kv_heads=1, head_dim=4, window=8, dtype=torch.float32)]
+    m = CacheManager(reqs, page_size=4, n_pages=6, max_requests=2)
+    m.poison_free_pages = True
+    m.allocate_storage("cpu")
+    full, win = m.kv_groups
+    assert torch.isnan(full.k).all() and torch.isnan(win.v).all()
+    m.open("a")
+    assert m.reserve("a", 10)
+    for g in (full, win):
+        for p in g.tables["a"]:
+            g.k[:, p] = 1.0
+            g.v[:, p] = 1.0
+    m.advance("a", 10)                                   # a query at position 10 sees keys 3..10: nothing passed yet
+    assert not torch.isnan(win.k[:, win.tables["a"][0]]).any()
+    assert m.reserve("a", 16)
+    m.advance("a", 16)                                   # keys 9..16: the first two pages of the window group go back
+    gone = [p for p in range(6) if not win.pool.is_held(p)]
+    assert len(gone) == 6 - 2 and all(torch.isnan(win.k[:, p]).all() and torch.isnan(win.v[:, p]).all() for p in gone)
+    held = [p for p in full.tables["a"]]
+    assert not torch.isnan(full.k[:, held[:3]]).any()    # the full group still holds every page it wrote
+    m.close("a")
+    assert torch.isnan(full.k).all() and torch.isnan(win.k).all()
+    m.check()

@@ -13,7 +13,7 @@ import pytest
 import torch
 
 import plain_llama
-from helpers import TINY, assert_close, make_model_dir, plain_inputs, random_tokens
+from helpers import BF16_NEAR_TIE, TINY, assert_close, make_model_dir, plain_inputs, random_tokens
 
 pytestmark = pytest.mark.gpu
 DTYPES = ["float32", "bfloat16"]
@@ -239,7 +239,7 @@ def test_greedy_generation_through_the_entry_point(tmp_path, name, dtype):
             if dtype == "float32":
                 assert tok == int(row.argmax()), f"{name} request {i} token {j}"
             else:
-                assert float(row.max() - row[tok]) <= 4e-2 * max(1.0, float(row.abs().max()))
+                assert float(row.max() - row[tok]) <= BF16_NEAR_TIE * max(1.0, float(row.abs().max()))
     assert engine.runner.cache.n_free_pages() == 24 and engine.stats["prefill_tokens"] >= 56
     if dtype == "float32":
         assert out[0] == plain_llama.greedy_generate(weights, config, prompts[0], 8)
@@ -267,7 +267,7 @@ def test_graphs_follow_the_growing_context_and_old_ones_are_dropped(tmp_path, mo
             if dtype == "float32":
                 assert tok == int(row.argmax())
             else:
-                assert float(row.max() - row[tok]) <= 4e-2 * max(1.0, float(row.abs().max()))
+                assert float(row.max() - row[tok]) <= BF16_NEAR_TIE * max(1.0, float(row.abs().max()))
 
 
 def test_generation_survives_a_pool_that_runs_out(tmp_path):
@@ -351,25 +351,45 @@ def test_command_line(tmp_path):
     got = {int(l.split(":")[0]): [int(t) for t in l.split(":")[1].split(",")] for l in lines}
     assert got[0] == plain_llama.greedy_generate(weights, config, [5, 17, 3], 6)
     assert got[1] == plain_llama.greedy_generate(weights, config, [9, 9, 9, 9], 6)
-    assert json.loads(stats.read_text())["new_tokens"] == 12
+    st = json.loads(stats.read_text())
+    assert st["new_tokens"] == 12
+    # time to the first token and time per later token, per request and summed up
+    assert len(st["requests"]) == 2 and all(r["ttft_s"] > 0 and r["tpot_s"] > 0 for r in st["requests"])
+    assert 0 < st["ttft_s"]["p50"] <= st["ttft_s"]["max"] and st["tpot_s"]["mean"] > 0
 
 
-@pytest.mark.parametrize("preset,layers", [("llama-3.2-1b", 2), ("llama-3.2-3b", 1)])
-def test_full_width_layers_in_bfloat16_against_the_32bit_path(tmp_path, preset, layers):
-    """The real widths (hidden 2,048 / 3,072, heads of 64 / 128, vocabulary 128,256) take the kernels' large-size
-    paths, which the tiny models never reach: the tensor-core products and attention of a long prompt, the streaming
-    products and the split-key attention of decode steps inside captured graphs, and a mixed step.  The plain
-    implementation is too slow at this size; the 32-bit path of the engine, which the tiny models tie to it, stands
-    in as the reference."""
+@pytest.mark.parametrize("preset,layers", [("llama-3.2-1b", 2), ("llama-3.2-3b", 1), ("smollm2-1.7b", 2)])
+def test_full_width_layers_against_the_plain_implementation(tmp_path, preset, layers):
+    """The real widths (hidden 2,048 / 3,072, heads of 64 / 128, grouped and not, vocabularies of 128,256 and 49,152)
+    take the kernels' large-size paths, which most tiny models never reach: the tensor-core products and attention of
+    a long prompt, the streaming products with the norm handed over and the split-key attention of decode steps
+    inside captured graphs, and a mixed step.  Both precisions against the plain implementation, whose head runs on
+    the wanted rows only (engine/llama_model.py:147-148 computes every row's)."""
     from inf_engine_b200.config import get_preset
     from inf_engine_b200.weights import write_random_model
 
     cfg = dataclasses.replace(get_preset(preset), num_hidden_layers=layers)
     d = tmp_path / "wide"
     write_random_model(cfg, 11, d)
+    config, weights = plain_inputs(d)
     V = cfg.vocab_size
     a, b = random_tokens(V, 300, 1), random_tokens(V, 150, 2)
     tail = random_tokens(V, 4, 3)
+    a_all, b_all = a + tail + [7, 8], b + [8, 9]
+    # (request, position) of every row the steps below ask for, in order
+    asked = [("a", 298), ("a", 299), ("a", 300), ("a", 301), ("a", 302), ("b", 99), ("a", 303), ("b", 149),
+             ("a", 304), ("b", 150), ("a", 305), ("b", 151)]
+    ref_a = plain_llama.forward_logits(weights, config, a_all, rows=[p for r, p in asked if r == "a"])
+    ref_b = plain_llama.forward_logits(weights, config, b_all, rows=[p for r, p in asked if r == "b"])
+    ia = ib = 0
+    ref = []
+    for r, _ in asked:
+        if r == "a":
+            ref.append(ref_a[ia]); ia += 1
+        else:
+            ref.append(ref_b[ib]); ib += 1
+    ref = torch.stack(ref)
+    del weights
 
     def run(dtype):
         r = runner_for(d, dtype, page_size=16, n_pages=64, max_requests=4)
@@ -385,7 +405,47 @@ def test_full_width_layers_in_bfloat16_against_the_32bit_path(tmp_path, preset, 
             out.append(r.step([entry("a", [t]), entry("b", [t + 1])]).cpu().clone())
         return torch.cat(out)
 
-    ref = run("float32")
-    got = run("bfloat16")
-    assert_close(got, ref, "bfloat16", f"{preset} widths, {layers} layers")
-    assert (got.argmax(-1) == ref.argmax(-1)).float().mean() >= 0.75      # mostly the same next token
+    assert_close(run("float32"), ref, "float32", f"{preset} widths, {layers} layers, float32")
+    assert_close(run("bfloat16"), ref, "bfloat16", f"{preset} widths, {layers} layers, bfloat16")
+
+
+def test_preset_tiny_b_sampled_workload_follows_the_plain_distribution(tmp_path):
+    """The tiny-b preset exactly as stated (3 layers, one kv head for four query heads, llama3 scaling, pages of 8):
+    prompts of 1, 9, 40 and 70 tokens as a mixed batch in portions of 16, then 12 tokens each at temperature 0.7,
+    seed 1.  Every token the engine draws must be the one the plain implementation's distribution gives at the
+    number hashed from (seed, request, how many it had generated): plain logits, temperature, softmax, inverse CDF."""
+    from inf_engine_b200 import Engine, Request, SamplingConfig
+    from inf_engine_b200.sampling import request_key, uniform_of
+
+    d = make_model_dir(tmp_path, "tiny-b")
+    config, weights = plain_inputs(d)
+    assert (config["num_hidden_layers"], config["num_key_value_heads"], config["head_dim"], config["vocab_size"]) == (3, 1, 32, 384)
+    prompts = [random_tokens(config["vocab_size"], n, 90 + n) for n in (1, 9, 40, 70)]
+    s = SamplingConfig(mode="temperature", temperature=0.7, seed=1)
+    for pipeline in (False, True):
+        engine = Engine.from_dir(d, dtype="float32", n_total_blocks=64, block_size=8, max_tokens_per_step=64, chunk=16,
+                                 pipeline=pipeline)
+        out = engine.run_offline([Request(i, p, 12, sampling=s) for i, p in enumerate(prompts)])
+        for i, p in enumerate(prompts):
+            assert len(out[i]) == 12
+            logits = plain_llama.forward_logits(weights, config, p + out[i])
+            for j, tok in enumerate(out[i]):
+                probs = plain_llama.filtered_distribution(logits[len(p) + j - 1], "temperature", temperature=0.7).double()
+                cdf = probs.cumsum(0)
+                u = uniform_of(1, request_key(i, j))
+                lo = float(cdf[tok - 1]) if tok > 0 else 0.0
+                assert lo - 2e-5 <= u <= float(cdf[tok]) + 2e-5, \
+                    f"request {i} token {j}: u={u} is outside [{lo}, {float(cdf[tok])}] of token {tok}"
+
+
+def test_preset_tiny_a_workload_is_the_plain_greedy_continuation(tmp_path):
+    """The tiny-a preset exactly as stated: prompts of 5, 17 and 33 tokens, 8 greedy tokens each, pages of 16."""
+    from inf_engine_b200 import Engine, Request
+
+    d = make_model_dir(tmp_path, "tiny-a")
+    config, weights = plain_inputs(d)
+    prompts = [random_tokens(config["vocab_size"], n, 50 + n) for n in (5, 17, 33)]
+    engine = Engine.from_dir(d, dtype="float32", n_total_blocks=16, block_size=16)
+    out = engine.run_offline([Request(i, p, 8) for i, p in enumerate(prompts)])
+    for i, p in enumerate(prompts):
+        assert out[i] == plain_llama.greedy_generate(weights, config, p, 8)

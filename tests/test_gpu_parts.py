@@ -9,7 +9,7 @@ import pytest
 import torch
 
 import plain_llama
-from helpers import random_tokens
+from helpers import assert_close, random_tokens
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
@@ -248,13 +248,14 @@ def test_a_toy_mixer_with_its_own_state_is_registered_built_and_stepped(dtype):
             lg = r.step(es).cpu()
             got_a.append(lg[:na].clone()); got_b.append(lg[na:].clone())
             pa += na; pb += nb
-        t = dict(atol=2e-5, rtol=1e-5) if dtype is torch.float32 else dict(atol=4e-2, rtol=4e-2)
-        assert torch.allclose(torch.cat(got_a), ref_a, **t) and torch.allclose(torch.cat(got_b), ref_b, **t)
+        name = "float32" if dtype is torch.float32 else "bfloat16"
+        assert_close(torch.cat(got_a), ref_a, name, "toy mixer, request a")
+        assert_close(torch.cat(got_b), ref_b, name, "toy mixer, request b")
         # the slot of a finished request is zeroed for the next one
         r.close("a")
         r.open("c")
         lg = r.step([StepEntry("c", a, list(range(len(a))))]).cpu()
-        assert torch.allclose(lg, ref_a, **t)
+        assert_close(lg, ref_a, name, "toy mixer, a slot used again")
     finally:
         MIXERS.pop("toy_decay")
 
@@ -297,8 +298,8 @@ def _stepped_in_cuts(r, a, b):
     return torch.cat(got_a), torch.cat(got_b)
 
 
-def _logit_tol(dtype):
-    return dict(atol=2e-5, rtol=1e-5) if dtype is torch.float32 else dict(atol=4e-2, rtol=4e-2)
+def _check(got, ref, dtype, what):
+    assert_close(got, ref, "float32" if dtype is torch.float32 else "bfloat16", what)
 
 
 @dataclass(frozen=True)
@@ -382,7 +383,8 @@ def test_a_toy_feedforward_with_routing_beside_the_dense_one(dtype):
         ref_a, ref_b = plain(a), plain(b)
         assert min(margins) > 0.25, "the test's tokens must not sit on the edge between two experts"
         got_a, got_b = _stepped_in_cuts(r, a, b)
-        assert torch.allclose(got_a, ref_a, **_logit_tol(dtype)) and torch.allclose(got_b, ref_b, **_logit_tol(dtype))
+        _check(got_a, ref_a, dtype, "toy routed feed-forward, a")
+        _check(got_b, ref_b, dtype, "toy routed feed-forward, b")
     finally:
         FEEDFORWARDS.pop("toy_routed")
 
@@ -465,6 +467,141 @@ def test_a_toy_position_encoding_with_a_learned_tensor(dtype):
         a, b = random_tokens(256, 40, 3), random_tokens(256, 23, 4)
         ref_a, ref_b = plain(a), plain(b)
         got_a, got_b = _stepped_in_cuts(r, a, b)
-        assert torch.allclose(got_a, ref_a, **_logit_tol(dtype)) and torch.allclose(got_b, ref_b, **_logit_tol(dtype))
+        _check(got_a, ref_a, dtype, "toy position encoding, a")
+        _check(got_b, ref_b, dtype, "toy position encoding, b")
     finally:
         POSITIONS.pop("toy_decay_position")
+
+
+@dataclass(frozen=True)
+class ToySlopePositionSpec:
+    """No rotation at all: a key that lies d positions back loses slope[head] * d from its score (a linear bias by
+    distance, one slope per query head, stated in the spec)."""
+
+    kind: str
+    slopes: tuple
+    max_positions: int
+
+
+class ToySlopePosition:
+    @staticmethod
+    def expected_tensors(spec):
+        return {}
+
+    def __init__(self, spec, tensors, rt):
+        d = torch.arange(spec.max_positions, dtype=torch.float32)
+        self.table = (-torch.tensor(spec.slopes, dtype=torch.float32)[:, None] * d[None, :]).contiguous().to(rt.device)
+
+    def rotary_tables(self):
+        return None
+
+    def rotate(self, q, k, ctx):
+        return None
+
+    def score_bias(self):
+        return self.table
+
+
+def _plain_slope_attention(h, w, prefix, config, slopes):
+    T = h.shape[0]
+    H, C, hd = config["num_attention_heads"], config["num_key_value_heads"], config["head_dim"]
+    q = (h @ w[prefix + "q_proj.weight"].T).view(T, H, hd).transpose(0, 1)
+    k = (h @ w[prefix + "k_proj.weight"].T).view(T, C, hd).transpose(0, 1).repeat_interleave(H // C, dim=0)
+    v = (h @ w[prefix + "v_proj.weight"].T).view(T, C, hd).transpose(0, 1).repeat_interleave(H // C, dim=0)
+    i, j = torch.arange(T)[:, None], torch.arange(T)[None, :]
+    scores = (q @ k.transpose(1, 2)) * hd ** -0.5 - torch.tensor(slopes)[:, None, None] * (i - j)[None].float()
+    scores = scores.masked_fill(~(j <= i)[None], float("-inf"))
+    out = (torch.softmax(scores, dim=-1) @ v).transpose(0, 1).reshape(T, H * hd)
+    return out @ w[prefix + "o_proj.weight"].T
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_toy_position_encoding_that_biases_scores_by_distance(dtype):
+    """Layer 0 rotates by tables, layer 1 has no rotation and biases every score by how far back its key lies:
+    the attention part hands the bias table to its general kernel (the tensor-core kernels step aside)."""
+    from inf_engine_b200.parts import POSITIONS, register_position
+    from helpers import TINY_A
+
+    register_position("toy_slope_position", ToySlopePosition)
+    try:
+        slopes = (0.5, 0.125, 0.03125, 0.0)                     # the last head sees no bias at all
+        pos = ToySlopePositionSpec("toy_slope_position", slopes, 512)
+        r, w = _two_layer_model(
+            dtype, lambda blk: dataclasses.replace(blk, mixer=dataclasses.replace(blk.mixer, position=pos)), seed=12)
+        assert r.model.graph_safe
+
+        def plain(toks, slopes=slopes):
+            x = w["model.embed_tokens.weight"][torch.tensor(toks)]
+            x = plain_llama.block(x, w, "model.layers.0.", TINY_A, *plain_llama.rope_tables(TINY_A, len(toks)))
+            h = plain_llama.rms_norm(x, w["model.layers.1.input_layernorm.weight"], 1e-5)
+            x = x + _plain_slope_attention(h, w, "model.layers.1.self_attn.", TINY_A, slopes)
+            h = plain_llama.rms_norm(x, w["model.layers.1.post_attention_layernorm.weight"], 1e-5)
+            x = x + plain_llama.swiglu(h, *(w[f"model.layers.1.mlp.{p}_proj.weight"] for p in ("gate", "up", "down")))
+            return plain_llama.rms_norm(x, w["model.norm.weight"], 1e-5) @ w["model.embed_tokens.weight"].T
+
+        a, b = random_tokens(256, 70, 5), random_tokens(256, 23, 6)
+        ref_a, ref_b = plain(a), plain(b)
+        # the bias matters: without it the logits differ by far more than any tolerance
+        assert float((plain(a, (0.0, 0.0, 0.0, 0.0)) - ref_a).abs().max()) > 1e-2
+        got_a, got_b = _stepped_in_cuts(r, a, b)
+        _check(got_a, ref_a, dtype, "toy score bias, a")
+        _check(got_b, ref_b, dtype, "toy score bias, b")
+    finally:
+        POSITIONS.pop("toy_slope_position")
+
+
+def _toy_top_level():
+    """Another top level, put together from the same blocks: the embedding is scaled by sqrt(hidden) and the logits
+    are capped smoothly, cap * tanh(logits / cap).  Registered under a ``kind`` of its own; the runner builds it
+    because the spec names it."""
+    from inf_engine_b200.parts import DecoderModel
+
+    class ToyTopLevel(DecoderModel):
+        CAP = 0.8
+
+        def embed(self, ctx):
+            residual = super().embed(ctx)
+            residual.mul_(float(self.spec.hidden) ** 0.5)
+            return residual
+
+        def finish_logits(self, logits, ctx):
+            return logits.div_(self.CAP).tanh_().mul_(self.CAP)
+
+    return ToyTopLevel
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_toy_top_level_with_a_scaled_embedding_and_capped_logits(dtype):
+    from inf_engine_b200 import ModelRunner, StepEntry
+    from inf_engine_b200.config import parse_config_dict
+    from inf_engine_b200.parts import MODELS, expected_tensors, register_model
+    from inf_engine_b200.weights import kept_dtype, random_tensors
+    from helpers import TINY_A
+
+    ToyTopLevel = _toy_top_level()
+    register_model("toy_scaled_capped", ToyTopLevel)
+    try:
+        cfg = parse_config_dict(TINY_A)
+        spec = dataclasses.replace(cfg.model_spec(), kind="toy_scaled_capped")
+        cpu = random_tensors(expected_tensors(spec), seed=13, std=0.05)
+        tensors = {n: t.to(DEV, kept_dtype(t.dtype, dtype)) for n, t in cpu.items()}
+        r = ModelRunner(cfg, tensors, dtype, page_size=16, n_pages=16, max_requests=3, spec=spec)
+        assert type(r.model) is ToyTopLevel and r.model.graph_safe
+        w = {n: t.float() for n, t in cpu.items()}
+
+        def plain(toks):
+            x = w["model.embed_tokens.weight"][torch.tensor(toks)] * 64 ** 0.5
+            cos, sin = plain_llama.rope_tables(TINY_A, len(toks))
+            for i in range(2):
+                x = plain_llama.block(x, w, f"model.layers.{i}.", TINY_A, cos, sin)
+            logits = plain_llama.rms_norm(x, w["model.norm.weight"], 1e-5) @ w["model.embed_tokens.weight"].T
+            return ToyTopLevel.CAP * torch.tanh(logits / ToyTopLevel.CAP)
+
+        a, b = random_tokens(256, 40, 7), random_tokens(256, 23, 8)
+        ref_a, ref_b = plain(a), plain(b)
+        assert float(ref_a.abs().max()) > 0.8 * ToyTopLevel.CAP       # the cap bites
+        got_a, got_b = _stepped_in_cuts(r, a, b)
+        _check(got_a, ref_a, dtype, "toy top level, a")
+        _check(got_b, ref_b, dtype, "toy top level, b")
+    finally:
+        MODELS.pop("toy_scaled_capped")
