@@ -30,7 +30,7 @@ def entry(rid, toks, want="all"):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_d", "tiny_e"])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_d", "tiny_e", "tiny_f", "tiny_g"])
 def test_long_decoding(tmp_path, name, dtype):
     d = make_model_dir(tmp_path, name)
     config, weights = plain_inputs(d)
@@ -45,7 +45,7 @@ def test_long_decoding(tmp_path, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c", "tiny_d", "tiny_e"])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c", "tiny_d", "tiny_e", "tiny_f", "tiny_g"])
 def test_first_tokens_of_a_sequence(tmp_path, name, dtype):
     d = make_model_dir(tmp_path, name)
     config, weights = plain_inputs(d)
@@ -110,8 +110,10 @@ def test_peaked_attention_over_reused_pages(tmp_path, name, dtype):
     while pc < len(c):
         n = min(2 + pc % 23, len(c) - pc)
         got["c"].append(r.step([entry("c", c[pc:pc + n])]).cpu().clone()); pc += n
+    # the scores of the bfloat16 run are 2.5 x 2.5 times larger, and their rounding error with them: a key from a
+    # wrong page or offset moves the logits by their own size, a hundred times this bound
     for k in got:
-        assert_close(torch.cat(got[k]), ref[k], dtype, f"{name} {dtype} peaked request {k}")
+        assert_close(torch.cat(got[k]), ref[k], dtype, f"{name} {dtype} peaked request {k}", noise=2.5)
     r.cache.check()
 
 
