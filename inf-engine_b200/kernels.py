@@ -456,65 +456,6 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epi: str = "
                                              _EPI[epi], bn, sm_count(), _stream()), f"gemm_tcgen05(m={m}, n={n}, k={k}, {epi})")
 
 
-# ------------------------------------- tcgen05 product for 17 to 128 rows over weights stored tile by tile
-WTILE_MIN_ROWS, WTILE_MAX_ROWS = 17, 128
-_wt_lib = None
-
-
-def wtile_library():
-    global _wt_lib
-    if _wt_lib is None:
-        lib = load_library("wtile", ["gemm_wtile_tcgen05.cu"], dict(BUILD_DEFINES.get("wtile", {})))
-        P, I = c_void_p, c_int
-        lib.ie_gemm_wtile.argtypes = [P, P, P, I, I, I, I, I, I, I, I, P]
-        lib.ie_gemm_wtile.restype = c_int
-        lib.ie_wtile_pack.argtypes = [P, P, I, I, I, P]
-        lib.ie_wtile_pack.restype = c_int
-        lib.ie_wtile_bytes.argtypes = [I, I]
-        lib.ie_wtile_bytes.restype = c_longlong
-        lib.ie_gemm_wtile_supports.argtypes = [I, I, I, I]
-        lib.ie_gemm_wtile_supports.restype = c_int
-        lib.ie_gemm_wtile_splits.argtypes = [I, I, I, I]
-        lib.ie_gemm_wtile_splits.restype = c_int
-        lib.ie_gemm_wtile_error.restype = c_int
-        _wt_lib = lib
-    return _wt_lib
-
-
-def gemm_wtile_supports(m: int, n: int, k: int, lda: int) -> bool:
-    return bool(wtile_library().ie_gemm_wtile_supports(m, n, k, lda))
-
-
-def gemm_wtile_error() -> int:
-    """Reads and clears the error word that a timed-out wait of the tiled-weight product leaves (0: none)."""
-    return int(wtile_library().ie_gemm_wtile_error())
-
-
-def wtile_pack(w: torch.Tensor) -> torch.Tensor:
-    """The copy of a bfloat16 weight [N, K] (K a multiple of 64) stored tile by tile, as ``gemm_wtile`` streams it:
-    tiles of 128 rows x 64 columns, each the 16 KB image that the tensor cores read from shared memory."""
-    n, k = w.shape
-    assert w.dtype is torch.bfloat16 and w.stride(1) == 1
-    nbytes = int(wtile_library().ie_wtile_bytes(n, k))
-    if nbytes < 0:
-        raise KernelError(f"wtile_pack: K = {k} is no multiple of 64")
-    out = torch.empty(nbytes // 2, dtype=torch.bfloat16, device=w.device)
-    _check(wtile_library().ie_wtile_pack(_ptr(w), _ptr(out), n, k, w.stride(0), _stream()), "wtile_pack")
-    return out
-
-
-def gemm_wtile(x: torch.Tensor, tiles: torch.Tensor, c: torch.Tensor, n: int, epi: str = "bf16", splits: int = 0) -> None:
-    """c = x @ w^T for 1 to 128 rows of bfloat16 ``x`` [M, K] with ``tiles = wtile_pack(w)``, w [n, K]: every weight
-    tile is read once, by one bulk copy.  ``epi``: "bf16" or "f32" store, "silu_mul" takes w's rows as alternating
-    gate/up and writes silu(gate)*up, half as wide.  ``splits``: blocks that share a tile's K (0: chosen)."""
-    m, k = x.shape
-    assert x.dtype is torch.bfloat16 and tiles.dtype is torch.bfloat16 and x.stride(1) == 1 and c.stride(1) == 1
-    assert c.dtype is (torch.float32 if epi == "f32" else torch.bfloat16)
-    assert c.shape == (m, n // 2 if epi == "silu_mul" else n)
-    _check(wtile_library().ie_gemm_wtile(_ptr(x), _ptr(tiles), _ptr(c), m, n, k, x.stride(0), c.stride(0), _EPI[epi],
-                                         splits, sm_count(), _stream()), f"gemm_wtile(m={m}, n={n}, k={k}, {epi})")
-
-
 # ------------------------------------------- prompt-portion attention on tcgen05 (head sizes 64 and 128)
 _fa5_lib = None
 
@@ -568,7 +509,5 @@ def check_device_errors() -> None:
         found.append(f"tcgen05 product: code {e}")
     if _fa5_lib is not None and (e := attention_tcgen05_error()):
         found.append(f"tcgen05 attention: code {e}")
-    if _wt_lib is not None and (e := gemm_wtile_error()):
-        found.append(f"tiled-weight product: code {e}")
     if found:
         raise KernelError("a kernel gave up a bounded wait; its results are not valid (" + "; ".join(found) + ")")

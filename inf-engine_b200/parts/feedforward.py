@@ -63,9 +63,6 @@ class GatedMLP:
             # gate/up on the tcgen05 tensor cores with silu(gate)*up in the epilogue: the [n, 2*intermediate]
             # matrix never goes to memory
             kernels.gemm_tcgen05(x, w, h, "silu_mul")
-        elif self.gate_up.takes_tiles(x) and dt is torch.bfloat16:
-            # a decode step of 17 to 128 requests: the weights stream once, tile by tile, silu(gate)*up in the epilogue
-            kernels.gemm_wtile(x, self.gate_up.tiles(), h, 2 * s.intermediate, "silu_mul")
         else:
             gu = self.gate_up(x, ws.take("ff_gate_up", (n, 2 * s.intermediate), dt))
             kernels.silu_mul(gu, h, interleaved=True)

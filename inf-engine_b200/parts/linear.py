@@ -4,11 +4,10 @@
 Which kernel runs is decided by the dtypes:
   * float32 activations, or a weight kept in float32: the CUDA-core kernel of
     this package (float32 products and sums, no tensor cores);
-  * bfloat16 activations and weight: this package's own kernels where they take
-    the shape (1 to 16 rows: the weight-streaming kernel; 17 to 128 rows: the
-    tcgen05 kernel over a copy of the weight stored tile by tile, made when such
-    a step first comes), else the library matrix product (cuBLAS through
-    ``torch.mm``), which is what the reference's engine uses for every projection.
+  * bfloat16 activations and weight: the library matrix product (cuBLAS through
+    ``torch.mm``), which is what the reference's engine uses for every
+    projection, or this package's own kernels where they are registered for the
+    shape.
 """
 
 from __future__ import annotations
@@ -25,19 +24,6 @@ class Linear:
         self.rt = rt
         self.name = name
         self.out_features, self.in_features = weight.shape
-        self._tiles = None
-
-    def takes_tiles(self, x: torch.Tensor) -> bool:
-        """True when the tiled-weight tcgen05 kernel takes this product: a decode step of 17 to 128 requests."""
-        return (self.weight.dtype is torch.bfloat16 and x.dtype is torch.bfloat16
-                and kernels.WTILE_MIN_ROWS <= x.shape[0] <= kernels.WTILE_MAX_ROWS and x.stride(1) == 1
-                and kernels.gemm_wtile_supports(x.shape[0], self.out_features, self.in_features, x.stride(0)))
-
-    def tiles(self) -> torch.Tensor:
-        """The weight stored tile by tile (a second copy, made once when a step of 17 to 128 rows first comes)."""
-        if self._tiles is None:
-            self._tiles = kernels.wtile_pack(self.weight)
-        return self._tiles
 
     def streams(self, n_rows: int) -> bool:
         """True when the weight-streaming kernel of this package takes this product:
@@ -63,9 +49,6 @@ class Linear:
         # bfloat16 x bfloat16
         if self.streams(x.shape[0]) and out.dtype in (torch.bfloat16, torch.float32):
             return self.stream(x, out, x.shape[0], "bf16" if out.dtype is torch.bfloat16 else "f32")
-        if self.takes_tiles(x) and out.dtype in (torch.bfloat16, torch.float32):
-            kernels.gemm_wtile(x, self.tiles(), out, self.out_features, "bf16" if out.dtype is torch.bfloat16 else "f32")
-            return out
         if out.dtype is torch.bfloat16 and out.is_contiguous():
             torch.mm(x, w.t(), out=out)
         elif out.dtype is torch.float32 and out.is_contiguous():

@@ -316,58 +316,6 @@ def test_gemm_tcgen05_against_float32(M, N, K, bn):
     assert k().gemm_tcgen05_error() == 0
 
 
-@pytest.mark.parametrize("M,N,K,splits", [(17, 256, 64, 0), (33, 200, 128, 0), (64, 3072, 2048, 0), (64, 2048, 8192, 0),
-                                          (128, 1000, 512, 0), (100, 2048, 2048, 0), (20, 2048, 2048, 1),
-                                          (20, 2048, 2048, 2), (31, 2048, 2048, 4), (32, 2048, 2048, 8),
-                                          (64, 384, 1024, 8), (128, 640, 1024, 8), (48, 16384, 2048, 0),
-                                          (1, 128, 64, 0), (64, 128256, 256, 0)])
-def test_gemm_wtile_against_float32(M, N, K, splits):
-    """The product for decode steps of 17 to 128 requests: weights stored tile by tile and streamed by bulk copies,
-    128 weight rows as the rows of a tcgen05.mma and the tokens as its columns (32, 64 or 128), K split over the
-    blocks of a cluster that add up through each other's shared memory.  Edge tiles in N, rows past M, every split."""
-    from inf_engine_b200 import kernels
-    torch.manual_seed(M + N + K)
-    bf = torch.bfloat16
-    xs = torch.randn(M, K + 8, device=DEV).to(bf)
-    x = xs[:, :K]                                              # rows K + 8 elements apart
-    w = (torch.randn(N, K, device=DEV) * 0.05).to(bf)
-    tiles = kernels.wtile_pack(w)
-    assert tiles.numel() == -(-N // 128) * 128 * K
-    ref = x.float().cpu() @ w.float().cpu().T
-    scale = max(float(ref.abs().max()), 1e-3)
-    if splits == 0:
-        splits_used = kernels.wtile_library().ie_gemm_wtile_splits(M, N, K, kernels.sm_count())
-        assert splits_used in (1, 2, 4, 8)
-    for _ in range(2):                                         # twice: the barriers and tensor memory start afresh
-        out = torch.full((M, N + 3), float("nan"), device=DEV, dtype=bf)[:, :N]
-        kernels.gemm_wtile(x, tiles, out, N, "bf16", splits)
-        assert float((out.float().cpu() - ref).abs().max()) <= 1e-2 * scale
-    out32 = torch.full((M, N), float("nan"), device=DEV)
-    kernels.gemm_wtile(x, tiles, out32, N, "f32", splits)
-    assert float((out32.cpu() - ref).abs().max()) <= 2e-4 * scale + 1e-5
-    if N % 2 == 0:
-        h = torch.full((M, N // 2), float("nan"), device=DEV, dtype=bf)
-        kernels.gemm_wtile(x, tiles, h, N, "silu_mul", splits)
-        want = plain_llama.silu(ref[:, 0::2]) * ref[:, 1::2]
-        assert float((h.float().cpu() - want).abs().max()) <= 1e-2 * max(1.0, float(want.abs().max()))
-    torch.cuda.synchronize()
-    assert kernels.gemm_wtile_error() == 0
-
-
-def test_gemm_wtile_refuses_what_it_cannot_take():
-    from inf_engine_b200 import kernels
-    from inf_engine_b200.kernels import KernelError
-    bf = torch.bfloat16
-    assert not kernels.gemm_wtile_supports(129, 256, 64, 64) and not kernels.gemm_wtile_supports(32, 256, 96, 96)
-    w = torch.zeros(256, 128, device=DEV, dtype=bf)
-    tiles = kernels.wtile_pack(w)
-    x, out = torch.zeros(20, 128, device=DEV, dtype=bf), torch.zeros(20, 256, device=DEV, dtype=bf)
-    with pytest.raises(KernelError, match="unsupported size"):
-        kernels.gemm_wtile(x, tiles, out, 256, "bf16", splits=4)        # two k blocks cannot be split four ways
-    with pytest.raises(KernelError, match="no multiple of 64"):
-        kernels.wtile_pack(torch.zeros(128, 96, device=DEV, dtype=bf))
-
-
 def test_gemm_tcgen05_refuses_what_it_cannot_take():
     from inf_engine_b200.kernels import KernelError
     bf = torch.bfloat16
