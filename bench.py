@@ -245,6 +245,18 @@ def run_ours(args):
             points[f"decode_b{b}"] = decode_device(b, args.steps, args.warmup)["tok_s"]
     clocks.stop()
     clk = clocks.summary(main["t0"], main["t1"])
+    # the other two configurations of the baseline: continuous batching at their sizes, wall clock
+    workloads = {}
+    if not args.no_workloads:
+        import gc
+        del engine, runner
+        gc.collect()
+        torch.cuda.empty_cache()
+        for key, model, n_req, lo, hi, new, temps in WORKLOADS:
+            for rec in measure_workload(model, n_req, lo, hi, new, temps, args.seed):
+                workloads[key + ("" if rec["temperature"] == 0 else f"_t{rec['temperature']}")] = {
+                    k: rec[k] for k in ("seconds", "generated_tok_s", "total_tok_s", "steps", "preemptions",
+                                        "ttft_s_p50", "tpot_s_mean")}
 
     achieved = main["bytes_step"] / (main["ms_per_step"] * 1e-3) / 1e9
     out = {
@@ -268,6 +280,7 @@ def run_ours(args):
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": achieved / pk["hbm_gbs"], "peak_source": pk["source"]},
         "points": points,
+        "workloads": workloads,
         "clocks": clk,
         "build_s": t_build,
     }
@@ -275,13 +288,18 @@ def run_ours(args):
     return 0
 
 
-def run_workload(args):
+# BASELINE.json's other two configurations: (key, preset, requests, shortest and longest prompt, new tokens, temperatures)
+WORKLOADS = [("llama-3.2-3b_32req_128-4096_128new", "llama-3.2-3b", 32, 128, 4096, 128, (0.0,)),
+             ("smollm2-1.7b_64req_64-2048_256new", "smollm2-1.7b", 64, 64, 2048, 256, (0.0, 0.8))]
+
+
+def measure_workload(model, n_req, lo, hi, new, temperatures, seed=0, layers=0):
     """Continuous batching through ``Engine.run_offline``: N requests with seeded uniform-random prompts of
     MIN..MAX tokens, NEW generated tokens each (no end-of-sequence id, so every request runs its full length),
-    wall clock around the whole run; the run is made twice and the second one counts (the first one also captures
-    the decode graphs).  ``--workload N:MIN:MAX:NEW[:TEMPERATURE]``; BASELINE.json's other two workloads are
-    ``--model smollm2-1.7b --workload 64:64:2048:256`` and ``--model llama-3.2-3b --workload 32:128:4096:128``."""
+    wall clock around the whole run; every run is made twice and the second one counts (the first one also captures
+    the decode graphs).  One engine serves every temperature; returns one record per temperature."""
     import dataclasses
+    import gc
 
     import numpy as np
     import torch
@@ -289,44 +307,60 @@ def run_workload(args):
     from inf_engine_b200 import Engine, Request, SamplingConfig
     from inf_engine_b200.config import get_preset
 
+    cfg = get_preset(model)
+    n_layers_full = cfg.num_hidden_layers
+    if layers:
+        cfg = dataclasses.replace(cfg, num_hidden_layers=layers)
+    rng = np.random.default_rng(seed)
+    lens = rng.integers(lo, hi + 1, n_req)
+    n_blocks = int(sum(int(n) + new for n in lens)) // PAGE + 4 * n_req + 64
+    torch.cuda.set_device(0)
+    engine = Engine.from_random(cfg, seed=seed, dtype="bfloat16", n_total_blocks=n_blocks, block_size=PAGE,
+                                max_requests=max(64, n_req), max_tokens_per_step=2048, eos_token=-1)
+    out = []
+    for temperature in temperatures:
+        sampling = SamplingConfig(mode="temperature", temperature=temperature, seed=1) if temperature > 0 else SamplingConfig()
+
+        def once():
+            requests = [Request(i, rng.integers(0, cfg.vocab_size, int(n)).tolist(), new, sampling=sampling)
+                        for i, n in enumerate(lens)]
+            engine.stats = {"steps": 0, "prefill_tokens": 0, "decode_tokens": 0, "preemptions": 0}
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            res = engine.run_offline(requests)
+            torch.cuda.synchronize()
+            seconds = time.perf_counter() - t0
+            engine.completed.clear()
+            return seconds, sum(len(v) for v in res.values()), Engine.latency_stats(requests)
+
+        once()
+        seconds, generated, lat = once()
+        prompt_tokens = int(lens.sum())
+        out.append({"seconds": seconds, "generated": generated, "generated_tok_s": generated / seconds,
+                    "total_tok_s": (generated + prompt_tokens) / seconds, "prompt_tokens": prompt_tokens,
+                    "steps": engine.stats["steps"], "preemptions": engine.stats["preemptions"],
+                    "temperature": temperature, "ttft_s_p50": lat["ttft_s"]["p50"], "tpot_s_mean": lat["tpot_s"]["mean"],
+                    "layers": cfg.num_hidden_layers, "layers_of_model": n_layers_full})
+    del engine
+    gc.collect()
+    torch.cuda.empty_cache()
+    return out
+
+
+def run_workload(args):
+    """``--workload N:MIN:MAX:NEW[:TEMPERATURE]`` with ``--model``: one continuous-batching run (see measure_workload);
+    BASELINE.json's other two workloads are ``--model smollm2-1.7b --workload 64:64:2048:256`` and
+    ``--model llama-3.2-3b --workload 32:128:4096:128``; the default run prints both under ``workloads``."""
     parts = args.workload.split(":")
     if len(parts) not in (4, 5):
         print("--workload wants N:MIN:MAX:NEW or N:MIN:MAX:NEW:TEMPERATURE")
         return 2
     n_req, lo, hi, new = (int(x) for x in parts[:4])
     temperature = float(parts[4]) if len(parts) == 5 else 0.0
-    cfg = get_preset(args.model)
-    n_layers_full = cfg.num_hidden_layers
-    if args.layers:
-        cfg = dataclasses.replace(cfg, num_hidden_layers=args.layers)
-    rng = np.random.default_rng(args.seed)
-    lens = rng.integers(lo, hi + 1, n_req)
-    n_blocks = int(sum(int(n) + new for n in lens)) // PAGE + 4 * n_req + 64
-    sampling = SamplingConfig(mode="temperature", temperature=temperature, seed=1) if temperature > 0 else SamplingConfig()
-    torch.cuda.set_device(0)
-    engine = Engine.from_random(cfg, seed=args.seed, dtype="bfloat16", n_total_blocks=n_blocks, block_size=PAGE,
-                                max_requests=max(64, n_req), max_tokens_per_step=2048, eos_token=-1, sampling=sampling)
-
-    def once():
-        requests = [Request(i, rng.integers(0, cfg.vocab_size, int(n)).tolist(), new) for i, n in enumerate(lens)]
-        engine.stats = {"steps": 0, "prefill_tokens": 0, "decode_tokens": 0, "preemptions": 0}
-        torch.cuda.synchronize()
-        t0 = time.perf_counter()
-        out = engine.run_offline(requests)
-        torch.cuda.synchronize()
-        seconds = time.perf_counter() - t0
-        engine.completed.clear()
-        return seconds, sum(len(v) for v in out.values())
-
-    once()
-    seconds, generated = once()
-    prompt_tokens = int(lens.sum())
-    print(json.dumps({"impl": "ours", "workload": args.workload, "seconds": seconds, "generated": generated,
-                      "generated_tok_s": generated / seconds, "total_tok_s": (generated + prompt_tokens) / seconds,
-                      "prompt_tokens": prompt_tokens, "steps": engine.stats["steps"],
-                      "preemptions": engine.stats["preemptions"], "dtype": "bf16",
+    rec = measure_workload(args.model, n_req, lo, hi, new, (temperature,), args.seed, args.layers)[0]
+    print(json.dumps({"impl": "ours", "workload": args.workload, **rec, "dtype": "bf16",
                       "data": "synthetic: seeded random weights, uniform random prompt ids",
-                      "config": {"model": args.model, "layers": cfg.num_hidden_layers, "layers_of_model": n_layers_full,
+                      "config": {"model": args.model, "layers": rec["layers"], "layers_of_model": rec["layers_of_model"],
                                  "requests": n_req, "prompt_min": lo, "prompt_max": hi, "new_tokens": new,
                                  "temperature": temperature, "page_size": PAGE, "max_tokens_per_step": 2048}}))
     return 0
@@ -513,6 +547,8 @@ def main():
                     help="measure one part only (short runs for profiling); the JSON line then lacks the rest")
     ap.add_argument("--pool-requests", type=int, default=64, help="requests of 4,096 tokens the cache pool is made for")
     ap.add_argument("--no-points", action="store_true", help="leave out the batch-1 and batch-64 points")
+    ap.add_argument("--no-workloads", action="store_true",
+                    help="leave out the two continuous-batching workloads at the other models' sizes")
     ap.add_argument("--workload", default=None, metavar="N:MIN:MAX:NEW[:TEMP]",
                     help="instead of the step measurements: N requests through Engine.run_offline (continuous batching)")
     args = ap.parse_args()

@@ -11,15 +11,18 @@
 // the ring with this kernel's weights while the kernel ahead is still running; only
 // the consumers wait for its output.
 //
-//   producer  warp 4, one lane: for every (unit, k-stage) wait for the stage to be
+//   producer  warp 8: for every (unit, k-stage) wait for the stage to be
 //             free, arm its mbarrier with the byte count, issue one bulk copy per
 //             weight row (rows are contiguous in global memory)
 //   consumers warps 0-7: stage the activations once per block in shared memory
 //             (bfloat16; with the RMSNorm prologue x*gain and 1/rms are computed here
 //             in float32, engine/layers.py:24-25), then per stage each warp takes a
 //             eighth of k, builds MMA fragments with 16-byte shared loads and runs
-//             mma.sync m16n8k16; at the end of a unit the eight partial sums are added
-//             in warp order and the epilogue of gemm_stream.cu is applied.
+//             mma.sync m16n8k16; at the end of a unit each warp leaves its partial sums in
+//             shared memory and goes on with the next unit
+//   epilogue  warp 9: adds the eight partial sums of a unit in warp order and applies the
+//             epilogue of gemm_stream.cu, one unit behind the consumers (two buffers of sums,
+//             handed over through named barriers)
 //
 // Every wait on an mbarrier is bounded; on a timeout the block records an error
 // word that ie_gemm_stream_tma_error() reads, stops issuing copies and leaves.
@@ -38,7 +41,8 @@ constexpr int SSQ_SLOT = 16;         // floats per block in the sums-of-squares 
 
 constexpr int CONSUMER_WARPS = 8;
 constexpr int CONSUMER_THREADS = CONSUMER_WARPS * 32;
-constexpr int THREADS = CONSUMER_THREADS + 32;
+constexpr int THREADS = CONSUMER_THREADS + 64;          // + the producer warp + the epilogue warp
+constexpr int HANDOVER_THREADS = CONSUMER_THREADS + 32; // the consumers and the epilogue warp
 constexpr int ROW_PAD = 64;          // bytes added to a row's pitch: keeps 16-byte fragment loads off shared banks
 constexpr int MAX_STAGES = 12;
 // polls of a wait that normally lasts microseconds.  Two switches exist for the test of the give-up path alone:
@@ -51,6 +55,7 @@ constexpr int MAX_STAGES = 12;
 #define IE_STREAM_ARM_EXTRA 0
 #endif
 constexpr unsigned SPIN_LIMIT = IE_STREAM_SPIN_LIMIT;
+
 
 __device__ int g_stream_error = 0;
 
@@ -134,7 +139,13 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
   asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
   return v;
 }
-__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_THREADS) : "memory"); }
+// barrier 1: consumers and epilogue warp, once, when the activations are staged.  Barriers 2, 3 ("sums of unit are
+// in red[0], red[1]") and 4, 5 ("red[0], red[1] have been read"): the consumers arrive on the first pair without
+// waiting and the epilogue warp waits there; the other way round on the second pair.  So the consumers go on with the
+// next unit's MMAs while the epilogue warp adds up and stores the one before.
+__device__ __forceinline__ void handover_sync() { asm volatile("bar.sync 1, %0;" ::"n"(HANDOVER_THREADS) : "memory"); }
+__device__ __forceinline__ void named_sync(int id) { asm volatile("bar.sync %0, %1;" ::"r"(id), "n"(HANDOVER_THREADS) : "memory"); }
+__device__ __forceinline__ void named_arrive(int id) { asm volatile("bar.arrive %0, %1;" ::"r"(id), "n"(HANDOVER_THREADS) : "memory"); }
 __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                          uint32_t b0, uint32_t b1) {
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
@@ -200,6 +211,7 @@ __device__ __forceinline__ bool produce(const TmaParams& p, int nt, const BlockC
 template <int NT, int PRO, int EPI, bool XS>
 __device__ __forceinline__ void consume(const TmaParams& p, const BlockCtx& b, RingPos& pos, bool first, unsigned int trace_id) {
   constexpr int UNIT_ROWS = 8 * NT;
+  constexpr int ASETS = 2;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n_units = (p.N + UNIT_ROWS - 1) / UNIT_ROWS;
   const int k_stages = p.K / p.ks;
@@ -310,22 +322,25 @@ __device__ __forceinline__ void consume(const TmaParams& p, const BlockCtx& b, R
     }
   }
   TRACE(7);                                                  // warp 0 has staged its rows
-  consumer_sync();
+  handover_sync();
   TRACE(3);                                                  // activations staged
 
   const int kw = warp * (p.ks / CONSUMER_WARPS);        // this warp's k offset inside a stage
   const int chunks = p.ks / (CONSUMER_WARPS * 32);      // 32-wide chunks per warp per stage
   const bool two = p.x_rows > 8;
-  int parity = 0;
-  float ssq_mine = 0.f;   // RESIDUAL_NORMOUT: squares of the new residual values this thread has stored (one row m per thread)
+  int parity = 0, n_done = 0;
   bool dead = false;   // after a timed-out wait a warp stops waiting and computing but still meets every barrier
   for (int u = blockIdx.x; u < n_units; u += gridDim.x) {
     // two accumulators per n-tile: the two MMAs of a chunk do not wait for each other
-    float acc[NT][2][4];
+    // two accumulators per n-tile: the two MMAs of a chunk do not wait for each other (4 and 8 per n-tile were
+    // measured too: a step of 16 layers at batch 8 took 0.968 and 0.985 ms against 0.941, for the registers they cost)
+    float acc[NT][ASETS][4];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) acc[nt][0][e] = acc[nt][1][e] = 0.f;
+      for (int a = 0; a < ASETS; ++a)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[nt][a][e] = 0.f;
     for (int ksi = 0; ksi < k_stages; ++ksi) {
       // activations that stay in L2 (plain bfloat16, long K) are requested before the wait for the stage:
       // they do not depend on it, and their latency then hides behind it
@@ -352,16 +367,21 @@ __device__ __forceinline__ void consume(const TmaParams& p, const BlockCtx& b, R
       const uint32_t wbase = ring + s * stage_bytes + g * w_pitch + (kw + t * 8) * 2;
       if (XS) {
         const uint32_t xbase = xs + g * x_pitch + (ksi * p.ks + kw + t * 8) * 2;
-#pragma unroll 4
-        for (int c = 0; c < chunks; ++c) {
-          const uint4 x0 = lds128(xbase + c * 64);
-          uint4 x1 = make_uint4(0u, 0u, 0u, 0u);
-          if (two) x1 = lds128(xbase + 8 * x_pitch + c * 64);
+        for (int c0 = 0; c0 < chunks; c0 += ASETS / 2) {
 #pragma unroll
-          for (int nt = 0; nt < NT; ++nt) {
-            const uint4 w = lds128(wbase + nt * 8 * w_pitch + c * 64);
-            mma16816(acc[nt][0], x0.x, x1.x, x0.y, x1.y, w.x, w.y);
-            mma16816(acc[nt][1], x0.z, x1.z, x0.w, x1.w, w.z, w.w);
+          for (int cc = 0; cc < ASETS / 2; ++cc) {
+            const int c = c0 + cc;
+            if (c < chunks) {
+              const uint4 x0 = lds128(xbase + c * 64);
+              uint4 x1 = make_uint4(0u, 0u, 0u, 0u);
+              if (two) x1 = lds128(xbase + 8 * x_pitch + c * 64);
+#pragma unroll
+              for (int nt = 0; nt < NT; ++nt) {
+                const uint4 w = lds128(wbase + nt * 8 * w_pitch + c * 64);
+                mma16816(acc[nt][2 * cc], x0.x, x1.x, x0.y, x1.y, w.x, w.y);
+                mma16816(acc[nt][2 * cc + 1], x0.z, x1.z, x0.w, x1.w, w.z, w.w);
+              }
+            }
           }
         }
       } else {
@@ -371,8 +391,8 @@ __device__ __forceinline__ void consume(const TmaParams& p, const BlockCtx& b, R
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
               const uint4 w = lds128(wbase + nt * 8 * w_pitch + u * 64);
-              mma16816(acc[nt][0], xg0[u].x, xg1[u].x, xg0[u].y, xg1[u].y, w.x, w.y);
-              mma16816(acc[nt][1], xg0[u].z, xg1[u].z, xg0[u].w, xg1[u].w, w.z, w.w);
+              mma16816(acc[nt][(2 * u) % ASETS], xg0[u].x, xg1[u].x, xg0[u].y, xg1[u].y, w.x, w.y);
+              mma16816(acc[nt][(2 * u + 1) % ASETS], xg0[u].z, xg1[u].z, xg0[u].w, xg1[u].w, w.z, w.w);
             }
           }
         }
@@ -381,81 +401,117 @@ __device__ __forceinline__ void consume(const TmaParams& p, const BlockCtx& b, R
       if (lane == 0) mbar_arrive(empty0 + 8 * s);
       if (++s == b.n_stages) { s = 0; phase ^= 1; }
     }
-    // partial sums of the four warps, added in warp order
+    // this warp's partial sums -> red[parity]; the buffer was last used two units ago, and the epilogue warp has
+    // said when it had read it
+    if (n_done >= 2) named_sync(4 + parity);
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) red[parity][warp][nt * 4 + e][lane] = acc[nt][0][e] + acc[nt][1][e];
-    consumer_sync();
-    if (u == (int)blockIdx.x) TRACE(5);                      // first unit multiplied
-    if (tid < 64 * NT && !failed) {
-      const int ln = tid & 31, h = (tid >> 5) & 1, nt = tid >> 6;
-      const int gg = ln >> 2, tt = ln & 3;
-      const int m = gg + h * 8;
-      const int n = u * UNIT_ROWS + nt * 8 + tt * 2;
-      if (m < p.M && n < p.N) {
-        float v0 = 0.f, v1 = 0.f;
+      for (int e = 0; e < 4; ++e) {
+        float sum = acc[nt][0][e];
 #pragma unroll
-        for (int w4 = 0; w4 < CONSUMER_WARPS; ++w4) {
-          v0 += red[parity][w4][nt * 4 + h * 2][ln];
-          v1 += red[parity][w4][nt * 4 + h * 2 + 1][ln];
-        }
-        if (PRO != PRO_PLAIN) {
-          v0 *= inv_rms[m];
-          v1 *= inv_rms[m];
-        }
-        const bool has1 = n + 1 < p.N;
-        if (EPI == EPI_BF16) {
-          bf16* c = (bf16*)p.C + (size_t)m * p.ldc + n;
-          if (has1 && ((((uintptr_t)c) & 3) == 0)) *reinterpret_cast<uint32_t*>(c) = pack2(v0, v1);
-          else { c[0] = __float2bfloat16_rn(v0); if (has1) c[1] = __float2bfloat16_rn(v1); }
-        } else if (EPI == EPI_F32) {
-          float* c = (float*)p.C + (size_t)m * p.ldc + n;
-          c[0] = v0;
-          if (has1) c[1] = v1;
-        } else if (EPI == EPI_RESIDUAL) {
-          float* c = (float*)p.C + (size_t)m * p.ldc + n;
-          c[0] += v0;
-          if (has1) c[1] += v1;
-        } else if (EPI == EPI_RESIDUAL_NORMOUT) {
-          float* c = (float*)p.C + (size_t)m * p.ldc + n;
-          const float r0 = c[0] + v0, r1 = has1 ? c[1] + v1 : 0.f;
-          c[0] = r0;
-          if (has1) c[1] = r1;
-          ssq_mine += r0 * r0 + r1 * r1;
-          const float g0 = p.gain_next_is_f32 ? ((const float*)p.gain_next)[n] : __bfloat162float(((const bf16*)p.gain_next)[n]);
-          const float g1 = !has1 ? 0.f : (p.gain_next_is_f32 ? ((const float*)p.gain_next)[n + 1] : __bfloat162float(((const bf16*)p.gain_next)[n + 1]));
-          bf16* xg = p.xg_out + (size_t)m * p.ld_xg + n;
-          if (has1 && ((((uintptr_t)xg) & 3) == 0)) *reinterpret_cast<uint32_t*>(xg) = pack2(r0 * g0, r1 * g1);
-          else { xg[0] = __float2bfloat16_rn(r0 * g0); if (has1) xg[1] = __float2bfloat16_rn(r1 * g1); }
-        } else {
-          const float sg = 1.f / (1.f + expf(-v0));
-          ((bf16*)p.C)[(size_t)m * p.ldc + (n >> 1)] = __float2bfloat16_rn((v0 * sg) * v1);
+        for (int a = 1; a < ASETS; ++a) sum += acc[nt][a][e];
+        red[parity][warp][nt * 4 + e][lane] = sum;
+      }
+    named_arrive(2 + parity);
+    if (u == (int)blockIdx.x) TRACE(5);                      // first unit multiplied
+    parity ^= 1;
+    ++n_done;
+  }
+  TRACE(6);                                                  // last unit multiplied
+}
+
+// ------------------------------------------------------------- epilogue (one warp)
+// Lane ln holds, per n-tile nt and half h, the two neighbouring outputs (m = ln / 4 + 8 h, n = unit + 8 nt + 2 (ln % 4)):
+// the layout of the MMA's accumulator, so the sums are read from red[] as the consumers wrote them.
+template <int NT, int PRO, int EPI>
+__device__ __forceinline__ void finish_units(const TmaParams& p, const BlockCtx& b, bool first) {
+  constexpr int UNIT_ROWS = 8 * NT;
+  const int lane = threadIdx.x & 31;
+  const int n_units = (p.N + UNIT_ROWS - 1) / UNIT_ROWS;
+  volatile int& failed = *b.failed;
+  const float* const inv_rms = b.inv_rms;
+  float (*red)[CONSUMER_WARPS][4 * NT][32] = reinterpret_cast<float (*)[CONSUMER_WARPS][4 * NT][32]>(b.red);
+  if (first) pdl_wait();                                     // nothing is written before the kernel ahead has finished
+  handover_sync();                                           // inv_rms is there
+  const int gg = lane >> 2, tt = lane & 3;
+  float ssq_lo = 0.f, ssq_hi = 0.f;    // RESIDUAL_NORMOUT: squares of the new residual values of rows gg and gg + 8
+  int parity = 0;
+  for (int u = blockIdx.x; u < n_units; u += gridDim.x) {
+    named_sync(2 + parity);                                  // every consumer warp has left its sums
+    if (!failed) {
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int m = gg + h * 8;
+          const int n = u * UNIT_ROWS + nt * 8 + tt * 2;
+          float v0 = 0.f, v1 = 0.f;
+#pragma unroll
+          for (int w4 = 0; w4 < CONSUMER_WARPS; ++w4) {
+            v0 += red[parity][w4][nt * 4 + h * 2][lane];
+            v1 += red[parity][w4][nt * 4 + h * 2 + 1][lane];
+          }
+          if (m < p.M && n < p.N) {
+            if (PRO != PRO_PLAIN) {
+              v0 *= inv_rms[m];
+              v1 *= inv_rms[m];
+            }
+            const bool has1 = n + 1 < p.N;
+            if (EPI == EPI_BF16) {
+              bf16* c = (bf16*)p.C + (size_t)m * p.ldc + n;
+              if (has1 && ((((uintptr_t)c) & 3) == 0)) *reinterpret_cast<uint32_t*>(c) = pack2(v0, v1);
+              else { c[0] = __float2bfloat16_rn(v0); if (has1) c[1] = __float2bfloat16_rn(v1); }
+            } else if (EPI == EPI_F32) {
+              float* c = (float*)p.C + (size_t)m * p.ldc + n;
+              c[0] = v0;
+              if (has1) c[1] = v1;
+            } else if (EPI == EPI_RESIDUAL) {
+              float* c = (float*)p.C + (size_t)m * p.ldc + n;
+              c[0] += v0;
+              if (has1) c[1] += v1;
+            } else if (EPI == EPI_RESIDUAL_NORMOUT) {
+              float* c = (float*)p.C + (size_t)m * p.ldc + n;
+              const float r0 = c[0] + v0, r1 = has1 ? c[1] + v1 : 0.f;
+              c[0] = r0;
+              if (has1) c[1] = r1;
+              if (h == 0) ssq_lo += r0 * r0 + r1 * r1;
+              else ssq_hi += r0 * r0 + r1 * r1;
+              const float g0 = p.gain_next_is_f32 ? ((const float*)p.gain_next)[n] : __bfloat162float(((const bf16*)p.gain_next)[n]);
+              const float g1 = !has1 ? 0.f : (p.gain_next_is_f32 ? ((const float*)p.gain_next)[n + 1] : __bfloat162float(((const bf16*)p.gain_next)[n + 1]));
+              bf16* xg = p.xg_out + (size_t)m * p.ld_xg + n;
+              if (has1 && ((((uintptr_t)xg) & 3) == 0)) *reinterpret_cast<uint32_t*>(xg) = pack2(r0 * g0, r1 * g1);
+              else { xg[0] = __float2bfloat16_rn(r0 * g0); if (has1) xg[1] = __float2bfloat16_rn(r1 * g1); }
+            } else {
+              const float sg = 1.f / (1.f + expf(-v0));
+              ((bf16*)p.C)[(size_t)m * p.ldc + (n >> 1)] = __float2bfloat16_rn((v0 * sg) * v1);
+            }
+          }
         }
       }
     }
+    // the consumers write this buffer again for the unit after the next: tell them that it has been read
+    if (u + 2 * (int)gridDim.x < n_units) named_arrive(4 + parity);
     parity ^= 1;
   }
   if (EPI == EPI_RESIDUAL_NORMOUT) {
-    // the block's sums of squares, row by row, added in a fixed order: the four threads of a row's quad, then the
-    // n-tiles; red is free (the last unit's sums were read before its consumers passed the barrier below)
-    float sq = ssq_mine;
-    sq += __shfl_xor_sync(0xffffffffu, sq, 1);
-    sq += __shfl_xor_sync(0xffffffffu, sq, 2);
-    consumer_sync();
-    float* rows = &red[0][0][0][0];                          // [NT][16]
-    if (tid < 64 * NT && (lane & 3) == 0) rows[(tid >> 6) * 16 + (lane >> 2) + ((tid >> 5) & 1) * 8] = sq;
-    consumer_sync();
-    if (tid < SSQ_SLOT) {
-      float total = rows[tid];
-      if (NT == 2) total += rows[16 + tid];
-      p.ssq_out[(size_t)blockIdx.x * SSQ_SLOT + tid] = total;
+    // the block's sums of squares, row by row, in a fixed order: this lane's units and n-tiles in turn, then the four
+    // lanes of a row's quad
+    ssq_lo += __shfl_xor_sync(0xffffffffu, ssq_lo, 1);
+    ssq_lo += __shfl_xor_sync(0xffffffffu, ssq_lo, 2);
+    ssq_hi += __shfl_xor_sync(0xffffffffu, ssq_hi, 1);
+    ssq_hi += __shfl_xor_sync(0xffffffffu, ssq_hi, 2);
+    if (tt == 0) {
+      p.ssq_out[(size_t)blockIdx.x * SSQ_SLOT + gg] = ssq_lo;
+      p.ssq_out[(size_t)blockIdx.x * SSQ_SLOT + gg + 8] = ssq_hi;
       // the reader adds ssq_blocks slots up: those of blocks that this launch does not have are zero
       if (blockIdx.x == 0)
-        for (int j = gridDim.x; j < p.ssq_blocks; ++j) p.ssq_out[(size_t)j * SSQ_SLOT + tid] = 0.f;
+        for (int j = gridDim.x; j < p.ssq_blocks; ++j) {
+          p.ssq_out[(size_t)j * SSQ_SLOT + gg] = 0.f;
+          p.ssq_out[(size_t)j * SSQ_SLOT + gg + 8] = 0.f;
+        }
     }
   }
-  TRACE(6);                                                  // last unit stored
 }
 
 // One product per launch.
@@ -503,6 +559,10 @@ __global__ void __launch_bounds__(THREADS, NT == 1 ? 2 : 1) gemm_stream_tma_kern
       for (int i = 0; i < 4096; ++i) __nanosleep(64);
     }
     pdl_wait();
+    return;
+  }
+  if (warp == CONSUMER_WARPS + 1) {
+    finish_units<NT, PRO, EPI>(p, b, true);
     return;
   }
 #ifdef IE_STREAM_TRACE

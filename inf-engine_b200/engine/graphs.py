@@ -185,7 +185,7 @@ class DecodeGraphs:
         try:
             if b.graph is None or b.generation != self.generation:
                 # warm-up outside capture (sizes the buffers, builds the work lists), then capture
-                before = self.ws.reserved_bytes()
+                before = self.ws.moves
                 s = torch.cuda.Stream()
                 s.wait_stream(torch.cuda.current_stream())
                 with torch.cuda.stream(s):
@@ -193,8 +193,11 @@ class DecodeGraphs:
                         self._forward(b)
                 torch.cuda.current_stream().wait_stream(s)
                 torch.cuda.synchronize()
-                if self.ws.reserved_bytes() != before:
-                    self.generation += 1          # a buffer moved: graphs captured earlier point at freed memory
+                if self.ws.moves != before:
+                    # a buffer was replaced by a larger one: graphs captured earlier point at freed memory.  (A buffer
+                    # that is new leaves them alone: the first step of at most 16 requests brings buffers of its own,
+                    # and throwing the graphs of the larger steps away for that cost a run of 32 requests 0.1 s.)
+                    self.generation += 1
                 from .. import kernels
                 g = torch.cuda.CUDAGraph()
                 n0 = kernels.LAUNCHES

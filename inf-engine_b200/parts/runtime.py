@@ -21,6 +21,7 @@ class Workspace:
         self._buffers: dict[str, torch.Tensor] = {}
         self._views: dict[tuple, torch.Tensor] = {}     # (name, shape, dtype) -> the view handed out last time
         self.frozen = False
+        self.moves = 0      # how often a buffer was replaced by a larger one (what pointed at the old one is stale)
 
     def take(self, name: str, shape: tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
         key = (name, shape, dtype)
@@ -46,6 +47,8 @@ class Workspace:
             # round up so that slowly growing steps do not reallocate every time
             cap = max(nbytes, 256)
             cap = 1 << (cap - 1).bit_length() if cap < (1 << 20) else -(-cap // (1 << 20)) * (1 << 20)
+            if buf is not None:
+                self.moves += 1
             buf = torch.zeros(cap, dtype=torch.uint8, device=self.device)   # some kernels keep counters that start at zero
             self._buffers[name] = buf
             self._views = {k: v for k, v in self._views.items() if k[0] != name}   # views of the buffer it replaces
