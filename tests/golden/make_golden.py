@@ -1,5 +1,5 @@
 """Compare the plain implementation with the reference project's own model code
-on the CPU and write the small outputs that ``tests/test_plain_golden.py`` checks.
+on the CPU and write the small outputs that ``tests/test_plain.py`` checks.
 
 Usage:  python tests/golden/make_golden.py --reference <checkout of waleedalfar/inf-engine>
 
