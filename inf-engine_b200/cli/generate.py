@@ -47,6 +47,8 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--chunk", type=int, default=None, help="largest prompt portion of one request in a step")
     p.add_argument("--eos-id", type=int, default=None)
     p.add_argument("--stats-json", default=None, help="write timing and engine counters here")
+    p.add_argument("--trace-jsonl", default=None, help="write one JSON line per engine step here (batch make-up, pages free, host time)")
+    p.add_argument("--nvtx", action="store_true", help="an NVTX range around every engine step, for a timeline tool")
     p.add_argument("--list-presets", action="store_true")
     return p
 
@@ -92,7 +94,7 @@ def main(argv=None) -> int:
         n_blocks = -(-per // args.block_size) * min(len(prompts), args.max_batch)
     kw = dict(dtype=args.dtype, device=args.device, n_total_blocks=n_blocks, block_size=args.block_size,
               max_requests=args.max_batch, eos_token=args.eos_id, max_tokens_per_step=args.max_tokens_per_step,
-              chunk=args.chunk)
+              chunk=args.chunk, trace_path=args.trace_jsonl, nvtx=args.nvtx)
     t0 = time.perf_counter()
     if model_dir is not None:
         engine = Engine.from_dir(model_dir, **kw)

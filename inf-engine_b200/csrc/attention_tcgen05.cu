@@ -155,6 +155,29 @@ __device__ __forceinline__ float fa_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
   return y;
 }
+// Packed float32 arithmetic of sm_100 (two lanes per instruction) and the three-input maximum: the softmax threads
+// are bound by how many instructions they issue per score, not by any one pipe.
+__device__ __forceinline__ uint64_t fa_pair(float lo, float hi) {
+  uint64_t v;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "f"(lo), "f"(hi));
+  return v;
+}
+__device__ __forceinline__ void fa_unpair(uint64_t v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ uint64_t fa_fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t fa_add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ float fa_max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
 __device__ __forceinline__ uint32_t fa_pack(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
@@ -414,8 +437,13 @@ __global__ void __launch_bounds__(FA_THREADS, Geo<HD, KT, STAGES>::BLOCKS_PER_SM
         float sc[32];
         fa_tmem_ld32(tmem_s + lane_addr + (j & 1) * KT + c_base + q4 * 32, sc);
         if (interior) {
+          float mb = -INFINITY;                              // two chains of three-input maxima
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, sc[i]);
+          for (int i = 0; i < 32; i += 4) {
+            mx = fa_max3(mx, sc[i], sc[i + 1]);
+            mb = fa_max3(mb, sc[i + 2], sc[i + 3]);
+          }
+          mx = fmaxf(mx, mb);
         } else {
 #pragma unroll
           for (int i = 0; i < 32; ++i)
@@ -463,7 +491,8 @@ __global__ void __launch_bounds__(FA_THREADS, Geo<HD, KT, STAGES>::BLOCKS_PER_SM
         }
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       }
-      float sum = 0.f;
+      const uint64_t scale2 = fa_pair(p.scale_log2, p.scale_log2), neg_m2 = fa_pair(-ms, -ms);
+      uint64_t sum2a = fa_pair(0.f, 0.f), sum2b = sum2a;
 #pragma unroll
       for (int q4 = 0; q4 < SCOLS / 32; ++q4) {
         float sc[32];
@@ -472,15 +501,27 @@ __global__ void __launch_bounds__(FA_THREADS, Geo<HD, KT, STAGES>::BLOCKS_PER_SM
         for (int ch = 0; ch < 4; ++ch) {
           float e[8];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const float x = fa_exp2(fmaf(sc[ch * 8 + i], p.scale_log2, -ms));
-            e[i] = (interior || k0 + c_base + q4 * 32 + ch * 8 + i <= limit) ? x : 0.f;
-            sum += e[i];
+          for (int i = 0; i < 8; i += 2) {
+            float x0, x1;
+            fa_unpair(fa_fma2(fa_pair(sc[ch * 8 + i], sc[ch * 8 + i + 1]), scale2, neg_m2), x0, x1);
+            x0 = fa_exp2(x0);
+            x1 = fa_exp2(x1);
+            e[i] = (interior || k0 + c_base + q4 * 32 + ch * 8 + i <= limit) ? x0 : 0.f;
+            e[i + 1] = (interior || k0 + c_base + q4 * 32 + ch * 8 + i + 1 <= limit) ? x1 : 0.f;
+            if (i & 2) sum2b = fa_add2(sum2b, fa_pair(e[i], e[i + 1]));
+            else sum2a = fa_add2(sum2a, fa_pair(e[i], e[i + 1]));
           }
           const int col = c_base + q4 * 32 + ch * 8;       // key index inside the tile
           const uint4 v = make_uint4(fa_pack(e[0], e[1]), fa_pack(e[2], e[3]), fa_pack(e[4], e[5]), fa_pack(e[6], e[7]));
           *reinterpret_cast<uint4*>(gen_base + G::P_OFF + (col >> 6) * ATOM_BYTES + sw128(r, (col & 63) >> 3)) = v;
         }
+      }
+      float sum;
+      {
+        float a0, a1, b0, b1;
+        fa_unpair(sum2a, a0, a1);
+        fa_unpair(sum2b, b0, b1);
+        sum = (a0 + a1) + (b0 + b1);
       }
       l = l * corr + sum;
       if (j == n_tiles - 1 && k_end < (j + 1) * KT) {

@@ -28,7 +28,8 @@ from .scheduler import PLACEHOLDER, Request, Scheduler
 class Engine:
     def __init__(self, runner: ModelRunner, eos_token=None, sampling: SamplingConfig | None = None,
                  max_queue_depth: int = 4096, max_batch: int | None = None, max_tokens_per_step: int = 2048,
-                 chunk: int | None = None, pipeline: bool = True):
+                 chunk: int | None = None, pipeline: bool = True, trace_path: str | Path | None = None,
+                 nvtx: bool = False):
         self.runner = runner
         self.cfg = sampling or SamplingConfig()
         if eos_token is None:
@@ -47,6 +48,24 @@ class Engine:
         self._host_ids = [torch.empty(max(1, runner.cache.max_requests), dtype=torch.int32, pin_memory=True)
                           for _ in range(3)]
         self._host_next = 0
+        # Observation, both off unless asked for: one JSON line per step (what the step was made of, pages free, the
+        # host's time for it) into ``trace_path``, and an NVTX range around every step for a timeline tool.
+        self._trace = open(trace_path, "w") if trace_path else None
+        self._nvtx = bool(nvtx)
+
+    def _observe(self, plan, t_host0: float, ahead: bool) -> None:
+        if self._trace is None:
+            return
+        import json
+        prefill = [e for e in plan.entries if not (len(e.tokens) == 1 and e.request.generated)]
+        rec = {"step": self.stats["steps"], "requests": len(plan.entries), "tokens": sum(len(e.tokens) for e in plan.entries),
+               "prefill_tokens": sum(len(e.tokens) for e in prefill), "decode_tokens": len(plan.entries) - len(prefill),
+               "sampled": sum(1 for e in plan.entries if e.wants_logits), "preempted": len(plan.preempted),
+               "running": len(self.scheduler.running), "queued": len(self.scheduler.queue),
+               "pages_free": self.runner.cache.n_free_pages(), "graph_replays": self.runner.graphs.replays,
+               "enqueued_ahead": ahead, "host_us": round((time.perf_counter() - t_host0) * 1e6, 1)}
+        self._trace.write(json.dumps(rec) + "\n")
+        self._trace.flush()
 
     # ------------------------------------------------------------ construction
     @classmethod
@@ -100,10 +119,16 @@ class Engine:
 
         With ``pipeline`` the step is enqueued before the tokens of the step before are read (they are
         taken on the device), and the requests returned are those that the step BEFORE completed."""
-        if self.pipeline and self._can_pipeline():
-            return self._step_ahead(now)
-        done = self._drain(now)
-        return done + self._step_now(now)
+        if self._nvtx:
+            torch.cuda.nvtx.range_push(f"engine step {self.stats['steps']}")
+        try:
+            if self.pipeline and self._can_pipeline():
+                return self._step_ahead(now)
+            done = self._drain(now)
+            return done + self._step_now(now)
+        finally:
+            if self._nvtx:
+                torch.cuda.nvtx.range_pop()
 
     # a penalty over generated tokens needs them on the host; so does a plan that may have to preempt
     def _can_pipeline(self) -> bool:
@@ -128,6 +153,7 @@ class Engine:
         return self.scheduler.resolve(plan, {e.request.req_id: t for e, t in zip(wanted, ids)}, in_flight, now)
 
     def _step_ahead(self, now: float) -> list[Request]:
+        t_host0 = time.perf_counter()
         prev = self._pending
         plan = self.scheduler.plan()
         self.stats["preemptions"] += len(plan.preempted)
@@ -154,6 +180,7 @@ class Engine:
         for e in plan.entries:
             self.stats["decode_tokens" if len(e.tokens) == 1 and e.request.generated else "prefill_tokens"] += len(e.tokens)
         self.stats["steps"] += 1
+        self._observe(plan, t_host0, True)
         self.scheduler.book(plan)
         new = None
         if wanted:
@@ -168,6 +195,7 @@ class Engine:
         return done
 
     def _step_now(self, now: float) -> list[Request]:
+        t_host0 = time.perf_counter()
         plan = self.scheduler.plan()
         self.stats["preemptions"] += len(plan.preempted)
         if not plan.entries:
@@ -194,6 +222,7 @@ class Engine:
         for e in plan.entries:
             self.stats["decode_tokens" if len(e.tokens) == 1 and e.request.generated else "prefill_tokens"] += len(e.tokens)
         self.stats["steps"] += 1
+        self._observe(plan, t_host0, False)
         return self.scheduler.commit(plan, sampled, now)
 
     def run_offline(self, requests: list[Request]) -> dict[int, list[int]]:

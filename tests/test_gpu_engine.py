@@ -346,7 +346,8 @@ def test_command_line(tmp_path):
     root = Path(__file__).resolve().parent.parent
     stats = tmp_path / "stats.json"
     p = subprocess.run([sys.executable, str(root / "bin" / "generate_llama"), "--model-dir", str(d), "--dtype", "float32",
-                        "--prompt-ids", "5,17,3;9,9,9,9", "--n", "6", "--stats-json", str(stats)],
+                        "--prompt-ids", "5,17,3;9,9,9,9", "--n", "6", "--stats-json", str(stats),
+                        "--trace-jsonl", str(tmp_path / "steps.jsonl"), "--nvtx"],
                        capture_output=True, text=True, timeout=600)
     assert p.returncode == 0, p.stderr[-2000:]
     lines = [l for l in p.stdout.splitlines() if ":" in l]
@@ -358,6 +359,11 @@ def test_command_line(tmp_path):
     # time to the first token and time per later token, per request and summed up
     assert len(st["requests"]) == 2 and all(r["ttft_s"] > 0 and r["tpot_s"] > 0 for r in st["requests"])
     assert 0 < st["ttft_s"]["p50"] <= st["ttft_s"]["max"] and st["tpot_s"]["mean"] > 0
+    # one line per step: the first step holds both prompts, the later ones a decoded token of each
+    steps = [json.loads(l) for l in (tmp_path / "steps.jsonl").read_text().splitlines()]
+    assert len(steps) == st["steps"] and steps[0]["prefill_tokens"] == 7 and steps[0]["requests"] == 2
+    assert sum(s["prefill_tokens"] + s["decode_tokens"] for s in steps) == st["prefill_tokens"] + st["decode_tokens"]
+    assert all(s["host_us"] > 0 and s["pages_free"] >= 0 for s in steps) and steps[-1]["decode_tokens"] >= 1
 
 
 @pytest.mark.parametrize("preset,layers", [("llama-3.2-1b", 2), ("llama-3.2-3b", 1), ("smollm2-1.7b", 2)])
