@@ -97,8 +97,8 @@ struct TmaParams {
   const void* gain_next;  // gain of the norm that comes next
   int gain_next_is_f32;
   int ld_xg;
-  float* ssq_out;         // [grid, SSQ_SLOT] this block's sums of squares of the new residual rows
-  const float* ssq_in;    // [ssq_blocks, SSQ_SLOT] the sums of the product ahead (PRENORMED)
+  float* ssq_out;         // [SSQ_SLOT rows][ssq_blocks] this block's sums of squares of the new residual rows
+  const float* ssq_in;    // [SSQ_SLOT rows][ssq_blocks] the sums of the product ahead (PRENORMED)
   int ssq_blocks;
 };
 
@@ -259,7 +259,7 @@ __device__ __forceinline__ void consume(const TmaParams& p, const BlockCtx& b, R
       if (PRO == PRO_PRENORMED) {
 #pragma unroll
         for (int j = 0; j < 8; ++j)
-          part[j] = (j * 32 + lane < p.ssq_blocks) ? __ldcg(p.ssq_in + (size_t)(j * 32 + lane) * SSQ_SLOT + m) : 0.f;
+          part[j] = (j * 32 + lane < p.ssq_blocks) ? __ldcg(p.ssq_in + (size_t)m * p.ssq_blocks + (j * 32 + lane)) : 0.f;
       }
       if (PRO == PRO_PLAIN || PRO == PRO_PRENORMED) {
         const bf16* src = (const bf16*)p.A + (size_t)m * p.lda;
@@ -502,13 +502,14 @@ __device__ __forceinline__ void finish_units(const TmaParams& p, const BlockCtx&
     ssq_hi += __shfl_xor_sync(0xffffffffu, ssq_hi, 1);
     ssq_hi += __shfl_xor_sync(0xffffffffu, ssq_hi, 2);
     if (tt == 0) {
-      p.ssq_out[(size_t)blockIdx.x * SSQ_SLOT + gg] = ssq_lo;
-      p.ssq_out[(size_t)blockIdx.x * SSQ_SLOT + gg + 8] = ssq_hi;
-      // the reader adds ssq_blocks slots up: those of blocks that this launch does not have are zero
+      // laid out [16 rows][ssq_blocks]: the reader's warp takes one row of it, contiguous
+      p.ssq_out[(size_t)gg * p.ssq_blocks + blockIdx.x] = ssq_lo;
+      p.ssq_out[(size_t)(gg + 8) * p.ssq_blocks + blockIdx.x] = ssq_hi;
+      // the reader adds ssq_blocks entries up: those of blocks that this launch does not have are zero
       if (blockIdx.x == 0)
         for (int j = gridDim.x; j < p.ssq_blocks; ++j) {
-          p.ssq_out[(size_t)j * SSQ_SLOT + gg] = 0.f;
-          p.ssq_out[(size_t)j * SSQ_SLOT + gg + 8] = 0.f;
+          p.ssq_out[(size_t)gg * p.ssq_blocks + j] = 0.f;
+          p.ssq_out[(size_t)(gg + 8) * p.ssq_blocks + j] = 0.f;
         }
     }
   }

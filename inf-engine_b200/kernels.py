@@ -315,7 +315,7 @@ def attention_decode_fused(q, k_new, v_new, out, kpool, vpool, block_table, q_st
 STREAM_MAX_ROWS = 64        # what the kernel takes
 STREAM_BEST_ROWS = 16       # beyond this the library product is faster (activations are re-read per block)
 _EPI = {"bf16": 0, "f32": 1, "residual": 2, "silu_mul": 3, "residual_normout": 4}
-SSQ_SLOT = 16               # floats per block in a sums-of-squares array
+SSQ_SLOT = 16               # rows of a sums-of-squares array ([SSQ_SLOT, blocks]: a block's sum for each activation row)
 _stream_lib = None
 _stream_variants: dict = {}
 
@@ -374,7 +374,7 @@ def gemm_stream(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, m: int, epi: 
 
     Two products can hand a norm over between them.  ``normout=(xg, gain_next, ssq)`` with epi "residual":
     besides adding into ``c`` the kernel writes ``xg`` = bfloat16(new c * gain_next) and, per block, the sums of
-    squares of the new rows into ``ssq`` ([SMs, SSQ_SLOT] float32).  ``prenormed=(xg, ssq)`` with ``eps``: ``a`` is
+    squares of the new rows into ``ssq`` ([SSQ_SLOT rows, SMs] float32).  ``prenormed=(xg, ssq)`` with ``eps``: ``a`` is
     ignored, the input is ``xg`` and the 1/rms comes from ``ssq``: RMSNorm without reading the residual again."""
     n, k = w.shape
     assert w.dtype is torch.bfloat16 and w.stride(1) == 1 and a.stride(-1) == 1 and c.stride(-1) == 1
@@ -390,7 +390,7 @@ def gemm_stream(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, m: int, epi: 
         _check(lib.ie_gemm_stream_tma(_ptr(src), _ptr(w), _ptr(c), None, 0, None, m, n, k, src.stride(0), w.stride(0),
                                       c.stride(0), float(eps), pro, code, sm_count(), _ptr(xg), xg.stride(0),
                                       _ptr(gain_next), dtype_code(gain_next.dtype) if gain_next is not None else 0,
-                                      _ptr(ssq), ssq.shape[0], _stream()),
+                                      _ptr(ssq), ssq.shape[1], _stream()),
                f"gemm_stream_tma(m={m}, n={n}, k={k}, {epi}, handed-over norm)")
         return
     if gain is None:

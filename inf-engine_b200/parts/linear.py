@@ -98,7 +98,7 @@ def stream_into_residual(linear: Linear, x: torch.Tensor, residual: torch.Tensor
         gain, eps = nxt.fusable_rms()
         if gain.dtype in (torch.bfloat16, torch.float32) and linear.out_features % 256 == 0:
             xg = rt.ws.take("handover_xg", (n, residual.shape[1]), torch.bfloat16)
-            ssq = rt.ws.take("handover_ssq", (kernels.sm_count(), kernels.SSQ_SLOT), torch.float32)
+            ssq = rt.ws.take("handover_ssq", (kernels.SSQ_SLOT, kernels.sm_count()), torch.float32)
             kernels.gemm_stream(x, linear.weight, residual, n, "residual", normout=(xg, gain, ssq))
             ctx.handover = NormHandover(gain, eps, xg, ssq)
             return

@@ -234,15 +234,15 @@ def test_norm_handed_over_between_streaming_products(M, hidden, inter):
         gain = (1 + 0.1 * torch.randn(hidden, device=DEV)).to(gain_dtype)
         res = res0.clone()
         xg = torch.full((M, hidden), float("nan"), device=DEV, dtype=bf)
-        ssq = torch.full((kernels.sm_count(), kernels.SSQ_SLOT), float("nan"), device=DEV)
+        ssq = torch.full((kernels.SSQ_SLOT, kernels.sm_count()), float("nan"), device=DEV)
         kernels.gemm_stream(hmid, wd, res, M, "residual", normout=(xg, gain, ssq))
         want_res = res0.cpu() + hmid.float().cpu() @ wd.float().cpu().T
         assert float((res.cpu() - want_res).abs().max()) <= 2e-3 * max(1.0, float(want_res.abs().max()))
         # what was prepared: bfloat16(residual * gain), and sums of squares that add up to the rows' own
         assert torch.equal(xg.float().cpu(), (res.cpu() * gain.float().cpu()).to(bf).float())
-        total = ssq[:, :M].sum(dim=0).cpu()
+        total = ssq[:M].sum(dim=1).cpu()
         assert torch.allclose(total, (res.cpu() ** 2).sum(dim=1), rtol=1e-5)
-        assert torch.isfinite(ssq).all() and float(ssq[:, M:].abs().max()) == 0.0
+        assert torch.isfinite(ssq).all() and float(ssq[M:].abs().max()) == 0.0
         # the product that takes it, against the one that normalises for itself
         out_a = torch.empty(M, wq.shape[0], device=DEV, dtype=bf)
         out_b = torch.empty_like(out_a)
