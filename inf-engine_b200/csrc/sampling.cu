@@ -133,19 +133,11 @@ extern "C" int ie_repetition_penalty(float* logits, const int* context, const fl
 }
 
 // --------------------------------------------------------------------- sample
-__global__ void __launch_bounds__(SM_THREADS) sample_kernel(const float* __restrict__ logits,
-                                                            const SampleRow* __restrict__ rows,
-                                                            int* __restrict__ out, int vocab, size_t row_stride,
-                                                            int skip_greedy) {
-  __shared__ float red[33];
-  __shared__ int redi[33];
-  __shared__ float chunk_sum[SM_THREADS];
-  pdl_trigger();
-  pdl_wait();
-  const float* x = logits + (size_t)blockIdx.x * row_stride;
-  const SampleRow r = rows[blockIdx.x];
+// One row by one block of SM_THREADS threads: x its logits, r its record, *out its token.  The caller gives the
+// block's scratch (red, redi: 33 words each; chunk_sum: SM_THREADS floats).
+__device__ __forceinline__ void sample_row(const float* __restrict__ x, const SampleRow r, int* __restrict__ out, int vocab,
+                                           float* red, int* redi, float* chunk_sum) {
   const int tid = threadIdx.x;
-  if (skip_greedy && r.temperature <= 0.f) return;    // greedy_split_kernel answers this row
 
   // the maximum (and its first index, which is the greedy answer)
   float best = -INFINITY;
@@ -165,7 +157,7 @@ __global__ void __launch_bounds__(SM_THREADS) sample_kernel(const float* __restr
       int t = redi[tid];
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) t = min(t, __shfl_xor_sync(0xffffffffu, t, o));
-      if (tid == 0) out[blockIdx.x] = t == 0x7fffffff ? 0 : t;
+      if (tid == 0) *out = t == 0x7fffffff ? 0 : t;
     }
     return;
   }
@@ -254,39 +246,70 @@ __global__ void __launch_bounds__(SM_THREADS) sample_kernel(const float* __restr
           if (order_key(x[i] / r.temperature) >= key_floor) { last_kept = i; break; }
       pick = last_kept < 0 ? 0 : last_kept;
     }
-    out[blockIdx.x] = pick;
+    *out = pick;
   }
+}
+
+__global__ void __launch_bounds__(SM_THREADS) sample_kernel(const float* __restrict__ logits,
+                                                            const SampleRow* __restrict__ rows,
+                                                            int* __restrict__ out, int vocab, size_t row_stride) {
+  __shared__ float red[33];
+  __shared__ int redi[33];
+  __shared__ float chunk_sum[SM_THREADS];
+  pdl_trigger();
+  pdl_wait();
+  sample_row(logits + (size_t)blockIdx.x * row_stride, rows[blockIdx.x], out + blockIdx.x, vocab, red, redi, chunk_sum);
 }
 
 // Greedy rows of a large vocabulary, spread over SG_CHUNKS blocks per row: one block alone reads a row of
 // half a megabyte at the speed of one SM.  Each block finds the maximum of its slice and its first index,
 // takes a ticket of the row, and the block with the last ticket picks the best slice (ties: lowest index,
-// as argmax does).  Rows that are not greedy are left to sample_kernel, which then skips the greedy ones.
-#define SG_CHUNKS 16
+// as argmax does).  A row that is not greedy is sampled by its first block in the same launch (the other blocks of
+// that row leave at once): one launch answers every row, whatever the mix.
+#ifndef SG_CHUNKS
+#define SG_CHUNKS 64
+#endif
 #define SG_MAX_ROWS 4096
 __device__ float g_sg_val[SG_MAX_ROWS * SG_CHUNKS];
 __device__ int g_sg_idx[SG_MAX_ROWS * SG_CHUNKS];
 __device__ unsigned int g_sg_ticket[SG_MAX_ROWS];   // zero between launches
 
-__global__ void __launch_bounds__(256) greedy_split_kernel(const float* __restrict__ logits,
-                                                           const SampleRow* __restrict__ rows, int* __restrict__ out,
-                                                           int vocab, size_t row_stride) {
-  __shared__ float sv[8];
-  __shared__ int si[8];
+__global__ void __launch_bounds__(SM_THREADS) greedy_split_kernel(const float* __restrict__ logits,
+                                                                  const SampleRow* __restrict__ rows, int* __restrict__ out,
+                                                                  int vocab, size_t row_stride) {
+  __shared__ float sv[32];
+  __shared__ int si[32];
   __shared__ unsigned int last;
+  __shared__ float red[33];
+  __shared__ int redi[33];
+  __shared__ float chunk_sum[SM_THREADS];
   pdl_trigger();
   pdl_wait();
   const int row = blockIdx.y, chunk = blockIdx.x;
-  if (rows[row].temperature > 0.f) return;            // not a greedy row
+  if (rows[row].temperature > 0.f) {                  // not a greedy row: its first block samples it
+    if (chunk == 0) sample_row(logits + (size_t)row * row_stride, rows[row], out + row, vocab, red, redi, chunk_sum);
+    return;
+  }
   const int per = (vocab + SG_CHUNKS - 1) / SG_CHUNKS;
   const int lo = chunk * per, hi = min(vocab, lo + per);
   const float* x = logits + (size_t)row * row_stride;
-  float best = -INFINITY;
-  int best_i = 0x7fffffff;
-  for (int i = lo + threadIdx.x; i < hi; i += 256) {
-    const float v = x[i];
-    if (v > best || best_i == 0x7fffffff) { best = v; best_i = i; }   // i ascends: the first maximum stays
+  // four candidates a thread, each walking its own indices upwards (the first maximum of each stays), so that the
+  // loads of a round are in flight together; then the lowest index among equal maxima wins, as everywhere below
+  float cb[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+  int ci[4] = {0x7fffffff, 0x7fffffff, 0x7fffffff, 0x7fffffff};
+  for (int i0 = lo + threadIdx.x; i0 < hi; i0 += 4 * SM_THREADS) {
+    float v[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) v[k] = (i0 + k * SM_THREADS < hi) ? x[i0 + k * SM_THREADS] : -INFINITY;
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+      if (i0 + k * SM_THREADS < hi && (v[k] > cb[k] || ci[k] == 0x7fffffff)) { cb[k] = v[k]; ci[k] = i0 + k * SM_THREADS; }
   }
+  float best = cb[0];
+  int best_i = ci[0];
+#pragma unroll
+  for (int k = 1; k < 4; ++k)
+    if (ci[k] != 0x7fffffff && (best_i == 0x7fffffff || cb[k] > best || (cb[k] == best && ci[k] < best_i))) { best = cb[k]; best_i = ci[k]; }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     const float ov = __shfl_xor_sync(0xffffffffu, best, o);
@@ -297,7 +320,7 @@ __global__ void __launch_bounds__(256) greedy_split_kernel(const float* __restri
   if (lane == 0) { sv[warp] = best; si[warp] = best_i; }
   __syncthreads();
   if (threadIdx.x == 0) {
-    for (int w = 1; w < 8; ++w)
+    for (int w = 1; w < SM_THREADS / 32; ++w)
       if (sv[w] > best || (sv[w] == best && si[w] < best_i)) { best = sv[w]; best_i = si[w]; }
     g_sg_val[row * SG_CHUNKS + chunk] = best;
     g_sg_idx[row * SG_CHUNKS + chunk] = best_i;
@@ -323,13 +346,10 @@ extern "C" int ie_sample(const float* logits, const void* rows, int* out, int n_
   if (n_rows <= 0) return IE_OK;
   if (vocab <= 0) return IE_BAD_SIZE;
   if (vocab >= 32768 && n_rows <= SG_MAX_ROWS) {
-    // greedy rows here, everything else (and nothing, when all rows are greedy) in sample_kernel
-    int rc = launch_k(greedy_split_kernel, dim3(SG_CHUNKS, n_rows), 256, 0, stream, logits, (const SampleRow*)rows, out,
-                      vocab, (size_t)row_stride);
-    if (rc) return rc;
-    return launch_k(sample_kernel, n_rows, SM_THREADS, 0, stream, logits, (const SampleRow*)rows, out, vocab,
-                    (size_t)row_stride, 1);
+    // one launch: greedy rows over SG_CHUNKS blocks each, every other row by its first block
+    return launch_k(greedy_split_kernel, dim3(SG_CHUNKS, n_rows), SM_THREADS, 0, stream, logits, (const SampleRow*)rows, out,
+                    vocab, (size_t)row_stride);
   }
   return launch_k(sample_kernel, n_rows, SM_THREADS, 0, stream, logits, (const SampleRow*)rows, out, vocab,
-                  (size_t)row_stride, 0);
+                  (size_t)row_stride);
 }

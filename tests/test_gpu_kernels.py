@@ -810,7 +810,7 @@ def test_sampling_follows_the_plain_distribution_and_the_hashed_uniform(vocab):
 
 
 def test_greedy_rows_of_a_large_vocabulary_beside_sampled_rows():
-    """Above 32,768 entries greedy rows are answered by sixteen blocks a row; the other rows by the sampling kernel."""
+    """Above 32,768 entries greedy rows are answered by 64 blocks a row; the other rows by the sampling kernel."""
     from inf_engine_b200.sampling import SamplingConfig, uniform_of
     torch.manual_seed(9)
     vocab = 40003
