@@ -12,26 +12,31 @@
 //               end is replaced by page 0: its keys are masked, and the value rows from the block's last key on
 //               are cleared in shared memory before the MMA reads them, so that nothing stored there, not
 //               even a NaN, reaches the output)
-//   warp 1      allocates tensor memory, issues  S = Q K^T  and  O += P V  (V is the MN-major operand: its rows
-//               are keys, as the cache stores them).  S has two buffers in tensor memory: the scores of tile j+1
-//               are issued before the thread waits for the softmax of tile j, so a softmax thread finds its next
-//               scores ready when it has written P
+//   warp 1      allocates tensor memory and issues  S = Q K^T.  S has two buffers in tensor memory: the scores of
+//               tile j+2 go out as soon as the softmax has read those of tile j, so a softmax thread finds its
+//               next scores ready when it has written P
 //   warps 2-5   thread r owns row r: reads S from tensor memory, masks, keeps the running maximum and sum in
 //               float32, rescales O in tensor memory when the maximum moved, writes P as bfloat16 into shared
-//               memory in the 128-byte swizzle that the MMA expects
+//               memory in the 128-byte swizzle that the MMA expects (two P buffers where shared memory has room
+//               for them: the exponentials of tile j+1 are then written while the MMAs of tile j still read)
+//   warp 6      issues  O += P V  (V is the MN-major operand: its rows are keys, as the cache stores them).  A
+//               thread of its own, because issuing a tile's MMAs and waiting for their barriers takes one thread
+//               about as long as the softmax of a tile takes: with one issuing thread for both products the
+//               softmax waited for it half of the time
 //
 // Every wait on an mbarrier is bounded; on a timeout the block records an error word, stops, frees its tensor
 // memory and leaves.
 #include "common.cuh"
 #include <cuda.h>
+#include <type_traits>
 
 namespace {
 
 constexpr int ROWS = 128;            // rows of a block's tile
-// threads that share a row of the softmax (1 or 2).  Measured at 2,048 tokens, head size 64: 44.9 us with one thread a
-// row, 48.7 us with two (more warps to hide latency, but an exchange per tile and twice the hand-overs).
-constexpr int FA_SOFTMAX_SPLIT = 1;
-constexpr int FA_THREADS = 64 + 128 * FA_SOFTMAX_SPLIT;
+// One softmax thread a row.  (Two threads a row, each with half of the keys of a tile and an exchange of maxima
+// through shared memory, were measured: 48.7 us against 44.9 us at 2,048 tokens, head size 64.)
+constexpr int FA_PV_WARP = 6;
+constexpr int FA_THREADS = 64 + 128 + 32;
 constexpr unsigned FA_SPIN_LIMIT = 1u << 20;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr uint32_t ATOM_BYTES = 128 * 64 * 2;   // 16 KB: 128 rows of one 128-byte swizzle atom (64 bfloat16)
@@ -39,7 +44,8 @@ constexpr uint32_t ATOM_BYTES = 128 * 64 * 2;   // 16 KB: 128 rows of one 128-by
 // Shared-memory geometry for head size HD, key tiles of KT keys and a ring of STAGES key/value stages.  Operands are kept as "halves" of 64
 // elements along their contiguous dimension (one swizzle atom wide): Q is HD/64 halves of [128 rows][64 dims],
 // a K or V stage HD/64 halves of [KT keys][64 dims], P is KT/64 (at least one) halves of [128 rows][64 keys].
-template <int HD, int KT, int STAGES>
+// PBUF: P buffers (1 or 2); SBUF: S buffers in tensor memory (1 or 2).
+template <int HD, int KT, int STAGES, int PBUF, int SBUF>
 struct Geo {
   static constexpr int HALVES = HD / 64;
   static constexpr uint32_t Q_BYTES = HALVES * ATOM_BYTES;
@@ -47,14 +53,14 @@ struct Geo {
   static constexpr uint32_t KV_STAGE = HALVES * KV_HALF;
   static constexpr uint32_t P_BYTES = (KT / 64 > 0 ? KT / 64 : 1) * ATOM_BYTES;
   static constexpr uint32_t K_OFF = Q_BYTES, V_OFF = K_OFF + STAGES * KV_STAGE, P_OFF = V_OFF + STAGES * KV_STAGE;
-  static constexpr uint32_t TILES_BYTES = P_OFF + P_BYTES;
-  // tensor memory: two S buffers in columns [0, 2 KT), O in [2 KT, 2 KT + HD), rounded up to a power of two
-  static constexpr int O_COL = 2 * KT;
+  static constexpr uint32_t TILES_BYTES = P_OFF + PBUF * P_BYTES;
+  // tensor memory: the S buffers in columns [0, SBUF KT), O in [SBUF KT, SBUF KT + HD), rounded up to a power of two
+  static constexpr int O_COL = SBUF * KT;
   static constexpr int TMEM_COLS = O_COL + HD <= 128 ? 128 : (O_COL + HD <= 256 ? 256 : 512);
   // blocks that fit an SM (shared memory, tensor memory); the register budget follows from it
   static constexpr int BLOCKS_PER_SM = (TILES_BYTES + 1152) * 3 <= 232448 && TMEM_COLS * 3 <= 512 ? 3
                                        : ((TILES_BYTES + 1152) * 2 <= 232448 && TMEM_COLS * 2 <= 512 ? 2 : 1);
-  static_assert(HD % 64 == 0 && HD <= 128 && KT % 64 == 0 && KT <= 128 && STAGES >= 2 && STAGES <= 4, "geometry");
+  static_assert(HD % 64 == 0 && HD <= 128 && KT % 64 == 0 && KT <= 128 && STAGES >= 2 && STAGES <= 4 && PBUF >= 1 && PBUF <= 2 && SBUF >= 1 && SBUF <= 2, "geometry");
 };
 
 __device__ int g_fa_error = 0;
@@ -185,18 +191,18 @@ __device__ __forceinline__ uint32_t fa_pack(float lo, float hi) {
 // byte offset of 16-byte chunk `chunk` (0..7) of row `row` in a tile of 128-byte rows under the 128-byte swizzle
 __device__ __forceinline__ uint32_t sw128(int row, int chunk) { return (uint32_t)(row * 128 + ((chunk ^ (row & 7)) << 4)); }
 
-template <int HD, int KT, int STAGES>
-__global__ void __launch_bounds__(FA_THREADS, Geo<HD, KT, STAGES>::BLOCKS_PER_SM) attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
+template <int HD, int KT, int STAGES, int PBUF, int SBUF>
+__global__ void __launch_bounds__(FA_THREADS, Geo<HD, KT, STAGES, PBUF, SBUF>::BLOCKS_PER_SM) attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
                                                                           const __grid_constant__ CUtensorMap map_v,
                                                                           FaParams p) {
-  // The tiles (Q, STAGES stages of K, as many of V, P), then the barriers (kv_full[4], kv_empty[4], s_full[2],
-  // p_ready, pv_done), the tensor-memory slot and the failure flag.  No static shared memory and no padding: two
-  // blocks have to fit one SM.
-  using G = Geo<HD, KT, STAGES>;
+  // The tiles (Q, STAGES stages of K, as many of V, PBUF of P), then the barriers (kv_full[4], kv_empty[4], s_full[2],
+  // p_ready[2], pv_done[2], q_ready), the tensor-memory slot and the failure flag.  No static shared memory and no
+  // padding: two blocks have to fit one SM.
+  using G = Geo<HD, KT, STAGES, PBUF, SBUF>;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem_raw + G::TILES_BYTES);
-  uint32_t* tmem_slot_p = reinterpret_cast<uint32_t*>(smem_raw + G::TILES_BYTES + 104);
-  volatile int* failed_p = reinterpret_cast<volatile int*>(smem_raw + G::TILES_BYTES + 112);
+  uint32_t* tmem_slot_p = reinterpret_cast<uint32_t*>(smem_raw + G::TILES_BYTES + 120);
+  volatile int* failed_p = reinterpret_cast<volatile int*>(smem_raw + G::TILES_BYTES + 124);
 #define tmem_slot (*tmem_slot_p)
 #define failed (*failed_p)
 
@@ -210,7 +216,10 @@ __global__ void __launch_bounds__(FA_THREADS, Geo<HD, KT, STAGES>::BLOCKS_PER_SM
   const uint32_t q_sm = base, k_sm = base + G::K_OFF, v_sm = base + G::V_OFF, p_sm = base + G::P_OFF;
   unsigned char* gen_base = smem_raw;
   const uint32_t kv_full0 = saddr(&bars[0]), kv_empty0 = saddr(&bars[4]);
-  const uint32_t s_full0 = saddr(&bars[8]), p_ready = saddr(&bars[10]), pv_done = saddr(&bars[11]);
+  // p_ready0 + 8 (j & 1): P of tile j is written and S of tile j has been read; pv_done0 + 8 (j & 1): the MMAs
+  // that read P of tile j are done.  Two of each, so that a waiter always waits for the newest phase of its barrier
+  // or the one before (a tile's barrier is not used again before tile j + 2, which needs what the waiter gives).
+  const uint32_t s_full0 = saddr(&bars[8]), p_ready0 = saddr(&bars[10]), pv_done0 = saddr(&bars[12]), q_ready = saddr(&bars[14]);
 
   // heads are the fast index and the work list is walked from its end: in a long prompt the tiles with the
   // most keys start first, and the short ones fill the tail of the launch
@@ -236,8 +245,11 @@ __global__ void __launch_bounds__(FA_THREADS, Geo<HD, KT, STAGES>::BLOCKS_PER_SM
     }
     fa_mbar_init(s_full0, 1);
     fa_mbar_init(s_full0 + 8, 1);
-    fa_mbar_init(p_ready, 4 * FA_SOFTMAX_SPLIT);
-    fa_mbar_init(pv_done, 1);
+    fa_mbar_init(p_ready0, 4);
+    fa_mbar_init(p_ready0 + 8, 4);
+    fa_mbar_init(pv_done0, 1);
+    fa_mbar_init(pv_done0 + 8, 1);
+    fa_mbar_init(q_ready, 4);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -288,64 +300,53 @@ __global__ void __launch_bounds__(FA_THREADS, Geo<HD, KT, STAGES>::BLOCKS_PER_SM
     }
     if (!ok) for (int i = 0; i < 2048; ++i) __nanosleep(64);
   } else if (warp == 1) {
-    // ------------------------------------------------------------- MMA issue
+    // ------------------------------------------------------------- MMA issue: S_t = Q K_t^T into buffer t & 1
     if (lane == 0) {
-      const uint32_t idesc_s = idesc_f32_bf16(ROWS, KT, 0), idesc_o = idesc_f32_bf16(ROWS, HD, 1);
+      const uint32_t idesc_s = idesc_f32_bf16(ROWS, KT, 0);
       // descriptors differ only in their address field (bits 0-13, in units of 16 bytes): one base each, offsets added
-      const uint64_t q_desc = desc_k_major(q_sm), k_desc = desc_k_major(k_sm), p_desc = desc_k_major(p_sm);
-      const uint64_t v_desc = desc_mn_major(v_sm, G::KV_HALF);
-      auto issue_s = [&](int j) {                          // S_j = Q K_j^T into buffer j & 1
-        const uint64_t kd = k_desc + (uint64_t)(((uint32_t)(j % STAGES) * G::KV_STAGE) >> 4);
-        const uint32_t d = tmem_s + (uint32_t)((j & 1) * KT);
+      const uint64_t q_desc = desc_k_major(q_sm), k_desc = desc_k_major(k_sm);
+      // the queries are written to shared memory by the softmax warps
+      bool ok = !failed && fa_mbar_wait(q_ready, 0);
+      if (!ok) { atomicExch(&g_fa_error, 5); failed = 1; }
+      for (int t = 0; t < n_tiles && ok; ++t) {
+        if (failed || !fa_mbar_wait(kv_full0 + 8 * (t % STAGES), (uint32_t)(t / STAGES) & 1u)) { atomicExch(&g_fa_error, 2); failed = 1; break; }
+        // the buffer was read last for tile t - SBUF
+        if (t >= SBUF && !fa_mbar_wait(p_ready0 + 8 * ((t - SBUF) & 1), (uint32_t)((t - SBUF) >> 1) & 1u)) { atomicExch(&g_fa_error, 3); failed = 1; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint64_t kd = k_desc + (uint64_t)(((uint32_t)(t % STAGES) * G::KV_STAGE) >> 4);
+        const uint32_t d = tmem_s + (uint32_t)((t % SBUF) * KT);
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks)
           fa_umma(d, q_desc + (uint64_t)(((ks >> 2) * ATOM_BYTES + (ks & 3) * 32) >> 4),
                   kd + (uint64_t)(((ks >> 2) * G::KV_HALF + (ks & 3) * 32) >> 4), idesc_s, ks > 0 ? 1u : 0u);
-        fa_commit(s_full0 + 8 * (j & 1));
-      };
-      // the queries are written to shared memory by the softmax warps: p_ready's phase 0 announces them
-      bool ok = !failed && fa_mbar_wait(p_ready, 0);
-      if (!ok) { atomicExch(&g_fa_error, 5); failed = 1; }
-      if (ok) {
-        if (fa_mbar_wait(kv_full0, 0)) {
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          issue_s(0);
-        } else { atomicExch(&g_fa_error, 2); failed = 1; ok = false; }
+        fa_commit(s_full0 + 8 * (t & 1));
       }
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        // the scores of the next tile go out before the softmax of this one is waited for: their buffer was
-        // read last for tile j - 1, whose P this thread has already seen
-        if (j + 1 < n_tiles) {
-          const int sn = (j + 1) % STAGES;
-          if (failed || !fa_mbar_wait(kv_full0 + 8 * sn, (uint32_t)((j + 1) / STAGES) & 1u)) { atomicExch(&g_fa_error, 2); failed = 1; break; }
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          issue_s(j + 1);
-        }
-        // P of this tile (phase j+1 of p_ready: phase 0 was the queries)
-        if (!fa_mbar_wait(p_ready, (uint32_t)(j + 1) & 1u)) { atomicExch(&g_fa_error, 3); failed = 1; break; }
+    }
+  } else if (warp == FA_PV_WARP) {
+    // ------------------------------------------------------------- MMA issue: O += P_j V_j
+    if (lane == 0) {
+      const uint32_t idesc_o = idesc_f32_bf16(ROWS, HD, 1);
+      const uint64_t p_desc = desc_k_major(p_sm), v_desc = desc_mn_major(v_sm, G::KV_HALF);
+      for (int j = 0; j < n_tiles; ++j) {
+        if (failed || !fa_mbar_wait(p_ready0 + 8 * (j & 1), (uint32_t)(j >> 1) & 1u)) { atomicExch(&g_fa_error, 3); failed = 1; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const int s = j % STAGES;
         const uint64_t vd = v_desc + (uint64_t)(((uint32_t)s * G::KV_STAGE) >> 4);
+        const uint64_t pd = p_desc + (uint64_t)(((uint32_t)(j % PBUF) * G::P_BYTES) >> 4);
 #pragma unroll
         for (int kk = 0; kk < KT / 16; ++kk)
-          fa_umma(tmem_o, p_desc + (uint64_t)(((kk >> 2) * ATOM_BYTES + (kk & 3) * 32) >> 4), vd + (uint64_t)((kk * 2048) >> 4),
+          fa_umma(tmem_o, pd + (uint64_t)(((kk >> 2) * ATOM_BYTES + (kk & 3) * 32) >> 4), vd + (uint64_t)((kk * 2048) >> 4),
                   idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
-        fa_commit(kv_empty0 + 8 * s);                      // K of the stage was read by S_j, V by these
-        fa_commit(pv_done);
+        // K of the stage was read by S_j, which was complete before the softmax of tile j read it; V by these
+        fa_commit(kv_empty0 + 8 * s);
+        fa_commit(pv_done0 + 8 * (j & 1));
       }
     }
   } else {
     // ------------------------------------------------------------- softmax
-    // FA_SOFTMAX_SPLIT threads share a row: thread (row r, part h) takes columns [h*KT/SPLIT, (h+1)*KT/SPLIT) of S
-    // and [h*HD/SPLIT, ...) of O.  Warps 2-5 are part 0, warps 6-9 part 1; a warp reads the 32 lanes of tensor
-    // memory of quarter warp % 4.  The parts of a row tell each other their maximum (and at the end their sum)
-    // through shared memory: a part writes {value, tag} into the first 8 bytes of the OTHER part's stretch of the
-    // P tile (which that part overwrites with its own P only after it has read them) and polls its own, bounded.
-    constexpr int SPLIT = FA_SOFTMAX_SPLIT;
-    constexpr int SCOLS = KT / SPLIT, OCOLS = HD / SPLIT;
-    static_assert(SCOLS % 32 == 0 && OCOLS % 32 == 0, "a part takes whole loads of 32 columns");
+    // Thread r owns row r of the tile; a warp reads the 32 lanes of tensor memory of quarter warp % 4.
+    static_assert(KT % 32 == 0 && HD % 32 == 0, "whole loads of 32 columns");
     const int quarter = warp & 3;
-    const int part = (warp - 2) >> 2;
     const int r = quarter * 32 + lane;                    // row of the tile = TMEM lane
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     const int pr = pair0 + r;
@@ -353,30 +354,11 @@ __global__ void __launch_bounds__(FA_THREADS, Geo<HD, KT, STAGES>::BLOCKS_PER_SM
     const int t = valid ? pr / group : 0;
     const int head = c * group + (valid ? pr - t * group : 0);
     const int limit = valid ? ctx + t : 0x3fffffff;       // last visible key (rows past the end are not stored)
-    const int c_base = part * SCOLS;                      // first S column of this part
-    // where a part's stretch of the P tile begins, for row r
-    auto p_slot = [&](int which) -> unsigned char* {
-      const int col = which * SCOLS;
-      return gen_base + G::P_OFF + (col >> 6) * ATOM_BYTES + sw128(r, (col & 63) >> 3);
-    };
-    // hand `value` to the other part and take its value; false if it never came
-    auto exchange = [&](float value, uint32_t tag, float& other) -> bool {
-      if (SPLIT == 1) { other = value; return true; }
-      asm volatile("st.volatile.shared.v2.b32 [%0], {%1, %2};" ::"r"(saddr(p_slot(part ^ 1))), "r"(__float_as_uint(value)), "r"(tag) : "memory");
-      const uint32_t mine = saddr(p_slot(part));
-      for (unsigned i = 0; i < FA_SPIN_LIMIT; ++i) {
-        uint32_t v, tg;
-        asm volatile("ld.volatile.shared.v2.b32 {%0, %1}, [%2];" : "=r"(v), "=r"(tg) : "r"(mine) : "memory");
-        if (tg == tag) { other = __uint_as_float(v); return true; }
-      }
-      return false;
-    };
 
     // queries -> shared memory in the MMA's swizzle, rotated on the way if they arrive unrotated
     {
       const bf16* src = p.q + (size_t)(q0 + t) * p.q_stride + head * HD;
-      constexpr int NCH = HD / 8 / SPLIT;                  // 16-byte chunks of the row that this thread stages
-      if (p.cos_t != nullptr && SPLIT == 1) {
+      if (p.cos_t != nullptr) {
         const int pos = valid ? p.positions[q0 + t] : 0;
         const float* cr = p.cos_t + (size_t)pos * (HD / 2);
         const float* sr = p.sin_t + (size_t)pos * (HD / 2);
@@ -406,8 +388,7 @@ __global__ void __launch_bounds__(FA_THREADS, Geo<HD, KT, STAGES>::BLOCKS_PER_SM
         }
       } else {
 #pragma unroll
-        for (int cc = 0; cc < NCH; ++cc) {
-          const int ch = part * NCH + cc;
+        for (int ch = 0; ch < HD / 8; ++ch) {
           uint4 v = make_uint4(0u, 0u, 0u, 0u);
           if (valid) v = *reinterpret_cast<const uint4*>(src + ch * 8);
           *reinterpret_cast<uint4*>(gen_base + (ch >> 3) * ATOM_BYTES + sw128(r, ch & 7)) = v;
@@ -415,27 +396,37 @@ __global__ void __launch_bounds__(FA_THREADS, Geo<HD, KT, STAGES>::BLOCKS_PER_SM
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> visible to the tensor core
       __syncwarp();
-      if (lane == 0) fa_mbar_arrive(p_ready);
+      if (lane == 0) fa_mbar_arrive(q_ready);
     }
+
+    // a bounded wait of the whole warp; false (and the error word set) when it ran out
+    // a bounded wait of the whole warp; false (and the error word set) when it ran out.  Every lane polls the same
+    // barrier; the failure flag is looked at only when a wait runs out (the other roles' waits are bounded too).
+    auto wait_all = [&](uint32_t bar, uint32_t parity, int code) -> bool {
+      const bool got = fa_mbar_wait(bar, parity);
+      if (!__all_sync(0xffffffffu, got)) {
+        if (lane == 0) { atomicExch(&g_fa_error, code); failed = 1; }
+        return false;
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      return true;
+    };
 
     float m = -INFINITY, l = 0.f;
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
-      ok = ok && !failed && fa_mbar_wait(s_full0 + 8 * (j & 1), (uint32_t)(j >> 1) & 1u);
-      if (!ok && lane == 0) { atomicExch(&g_fa_error, 4); failed = 1; }
-      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0 && !failed;
+      ok = wait_all(s_full0 + 8 * (j & 1), (uint32_t)(j >> 1) & 1u, 4);
       if (!ok) break;
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int k0 = j * KT;
       // a tile whose last key every row of the warp may see needs no mask
       const bool interior = __all_sync(0xffffffffu, k0 + KT - 1 <= limit);
-      // this part's scores of the row, 32 at a time, read twice from tensor memory (once for the maximum, once
-      // for the exponentials)
+      // the scores of the row, 32 at a time, read twice from tensor memory (once for the maximum, once for the
+      // exponentials)
       float mx = -INFINITY;
 #pragma unroll
-      for (int q4 = 0; q4 < SCOLS / 32; ++q4) {
+      for (int q4 = 0; q4 < KT / 32; ++q4) {
         float sc[32];
-        fa_tmem_ld32(tmem_s + lane_addr + (j & 1) * KT + c_base + q4 * 32, sc);
+        fa_tmem_ld32(tmem_s + lane_addr + (j % SBUF) * KT + q4 * 32, sc);
         if (interior) {
           float mb = -INFINITY;                              // two chains of three-input maxima
 #pragma unroll
@@ -447,31 +438,13 @@ __global__ void __launch_bounds__(FA_THREADS, Geo<HD, KT, STAGES>::BLOCKS_PER_SM
         } else {
 #pragma unroll
           for (int i = 0; i < 32; ++i)
-            if (k0 + c_base + q4 * 32 + i <= limit) mx = fmaxf(mx, sc[i]);
+            if (k0 + q4 * 32 + i <= limit) mx = fmaxf(mx, sc[i]);
         }
-      }
-      // O and the P buffer belong to the MMAs of the tile before until pv_done
-      if (j > 0) {
-        bool ok2 = fa_mbar_wait(pv_done, (uint32_t)(j - 1) & 1u);
-        if (!ok2 && lane == 0) { atomicExch(&g_fa_error, 6); failed = 1; }
-        ok = __shfl_sync(0xffffffffu, ok2 ? 1 : 0, 0) != 0 && !failed;
-        if (!ok) break;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      }
-      {
-        float other;
-        bool got = exchange(mx, 0x7fc00000u | (uint32_t)(2 * j + 1), other);
-        if (!__all_sync(0xffffffffu, got)) {
-          if (lane == 0) { atomicExch(&g_fa_error, 9); failed = 1; }
-          ok = false;
-          break;
-        }
-        mx = fmaxf(mx, other);
       }
       // The maximum in use follows the true one only when that has grown by more than 2^8 (or is the
       // first): until then the exponentials are at most 256, which neither bfloat16 nor the float32 sums
       // mind, and O in tensor memory needs no rescaling.  The result is the same: numerator and
-      // denominator carry the same factor.  (Both parts of a row see the same maximum and decide alike.)
+      // denominator carry the same factor.
       const float m_cand = fmaxf(m, mx * p.scale_log2);
       const bool moves = __any_sync(0xffffffffu, m_cand - m > 8.f || (m == -INFINITY && m_cand > -INFINITY));
       float corr = 1.f;
@@ -480,42 +453,59 @@ __global__ void __launch_bounds__(FA_THREADS, Geo<HD, KT, STAGES>::BLOCKS_PER_SM
         m = m_cand;
       }
       const float ms = m == -INFINITY ? 0.f : m;
+      // this tile's P buffer belongs to the MMAs of tile j - PBUF until they are done
+      if (j >= PBUF) {
+        ok = wait_all(pv_done0 + 8 * ((j - PBUF) & 1), (uint32_t)((j - PBUF) >> 1) & 1u, 6);
+        if (!ok) break;
+      }
       if (j > 0 && moves) {
+        // O belongs to the MMAs of the tile before until they are done
+        if (PBUF > 1) {
+          ok = wait_all(pv_done0 + 8 * ((j - 1) & 1), (uint32_t)((j - 1) >> 1) & 1u, 6);
+          if (!ok) break;
+        }
 #pragma unroll
-        for (int h = 0; h < OCOLS / 32; ++h) {
+        for (int h = 0; h < HD / 32; ++h) {
           float o[32];
-          fa_tmem_ld32(tmem_o + lane_addr + part * OCOLS + h * 32, o);
+          fa_tmem_ld32(tmem_o + lane_addr + h * 32, o);
 #pragma unroll
           for (int i = 0; i < 32; ++i) o[i] *= corr;
-          fa_tmem_st32(tmem_o + lane_addr + part * OCOLS + h * 32, o);
+          fa_tmem_st32(tmem_o + lane_addr + h * 32, o);
         }
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       }
+      unsigned char* const p_tile = gen_base + G::P_OFF + (uint32_t)(j % PBUF) * G::P_BYTES;
       const uint64_t scale2 = fa_pair(p.scale_log2, p.scale_log2), neg_m2 = fa_pair(-ms, -ms);
       uint64_t sum2a = fa_pair(0.f, 0.f), sum2b = sum2a;
+      // exponentials, their sums and P; a tile that needs no mask takes the loop without the comparisons
+      auto exp_pass = [&](auto masked) {
+        constexpr bool MASKED = decltype(masked)::value;
 #pragma unroll
-      for (int q4 = 0; q4 < SCOLS / 32; ++q4) {
-        float sc[32];
-        fa_tmem_ld32(tmem_s + lane_addr + (j & 1) * KT + c_base + q4 * 32, sc);
+        for (int q4 = 0; q4 < KT / 32; ++q4) {
+          float sc[32];
+          fa_tmem_ld32(tmem_s + lane_addr + (j % SBUF) * KT + q4 * 32, sc);
 #pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-          float e[8];
+          for (int ch = 0; ch < 4; ++ch) {
+            float e[8];
 #pragma unroll
-          for (int i = 0; i < 8; i += 2) {
-            float x0, x1;
-            fa_unpair(fa_fma2(fa_pair(sc[ch * 8 + i], sc[ch * 8 + i + 1]), scale2, neg_m2), x0, x1);
-            x0 = fa_exp2(x0);
-            x1 = fa_exp2(x1);
-            e[i] = (interior || k0 + c_base + q4 * 32 + ch * 8 + i <= limit) ? x0 : 0.f;
-            e[i + 1] = (interior || k0 + c_base + q4 * 32 + ch * 8 + i + 1 <= limit) ? x1 : 0.f;
-            if (i & 2) sum2b = fa_add2(sum2b, fa_pair(e[i], e[i + 1]));
-            else sum2a = fa_add2(sum2a, fa_pair(e[i], e[i + 1]));
+            for (int i = 0; i < 8; i += 2) {
+              float x0, x1;
+              fa_unpair(fa_fma2(fa_pair(sc[ch * 8 + i], sc[ch * 8 + i + 1]), scale2, neg_m2), x0, x1);
+              x0 = fa_exp2(x0);
+              x1 = fa_exp2(x1);
+              e[i] = (!MASKED || k0 + q4 * 32 + ch * 8 + i <= limit) ? x0 : 0.f;
+              e[i + 1] = (!MASKED || k0 + q4 * 32 + ch * 8 + i + 1 <= limit) ? x1 : 0.f;
+              if (i & 2) sum2b = fa_add2(sum2b, fa_pair(e[i], e[i + 1]));
+              else sum2a = fa_add2(sum2a, fa_pair(e[i], e[i + 1]));
+            }
+            const int col = q4 * 32 + ch * 8;                // key index inside the tile
+            const uint4 v = make_uint4(fa_pack(e[0], e[1]), fa_pack(e[2], e[3]), fa_pack(e[4], e[5]), fa_pack(e[6], e[7]));
+            *reinterpret_cast<uint4*>(p_tile + (col >> 6) * ATOM_BYTES + sw128(r, (col & 63) >> 3)) = v;
           }
-          const int col = c_base + q4 * 32 + ch * 8;       // key index inside the tile
-          const uint4 v = make_uint4(fa_pack(e[0], e[1]), fa_pack(e[2], e[3]), fa_pack(e[4], e[5]), fa_pack(e[6], e[7]));
-          *reinterpret_cast<uint4*>(gen_base + G::P_OFF + (col >> 6) * ATOM_BYTES + sw128(r, (col & 63) >> 3)) = v;
         }
-      }
+      };
+      if (interior) exp_pass(std::false_type{});
+      else exp_pass(std::true_type{});
       float sum;
       {
         float a0, a1, b0, b1;
@@ -531,7 +521,7 @@ __global__ void __launch_bounds__(FA_THREADS, Geo<HD, KT, STAGES>::BLOCKS_PER_SM
         // have landed (the scores of this tile, which this thread has read, were issued after them).
         const int first_dead = k_end - j * KT;
         unsigned char* vst = gen_base + G::V_OFF + (uint32_t)(j % STAGES) * G::KV_STAGE;
-        for (int idx = part * ROWS + r; idx < KT * G::HALVES; idx += ROWS * SPLIT) {
+        for (int idx = r; idx < KT * G::HALVES; idx += ROWS) {
           const int row = idx % KT, half = idx / KT;
           if (row >= first_dead) {
             uint4* dst = reinterpret_cast<uint4*>(vst + half * G::KV_HALF + row * 128);
@@ -543,32 +533,16 @@ __global__ void __launch_bounds__(FA_THREADS, Geo<HD, KT, STAGES>::BLOCKS_PER_SM
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
-      if (lane == 0) fa_mbar_arrive(p_ready);
+      if (lane == 0) fa_mbar_arrive(p_ready0 + 8 * (j & 1));
     }
+    if (ok) ok = wait_all(pv_done0 + 8 * ((n_tiles - 1) & 1), (uint32_t)((n_tiles - 1) >> 1) & 1u, 7);
     if (ok) {
-      bool ok2 = fa_mbar_wait(pv_done, (uint32_t)(n_tiles - 1) & 1u);
-      if (!ok2 && lane == 0) { atomicExch(&g_fa_error, 7); failed = 1; }
-      ok = __shfl_sync(0xffffffffu, ok2 ? 1 : 0, 0) != 0 && !failed;
-    }
-    if (ok) {
-      // the row's sum is the sum of its parts' sums (they used the same maximum)
-      float other;
-      bool got = exchange(l, 0x7fc00000u | (uint32_t)(2 * n_tiles + 2), other);
-      if (!__all_sync(0xffffffffu, got)) {
-        if (lane == 0) { atomicExch(&g_fa_error, 10); failed = 1; }
-        ok = false;
-      } else if (SPLIT > 1) {
-        l += other;
-      }
-    }
-    if (ok) {
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const float inv = l > 0.f ? 1.f / l : 0.f;
-      bf16* dst = p.out + (size_t)(q0 + t) * p.out_stride + head * HD + part * OCOLS;
+      bf16* dst = p.out + (size_t)(q0 + t) * p.out_stride + head * HD;
 #pragma unroll
-      for (int h = 0; h < OCOLS / 32; ++h) {
+      for (int h = 0; h < HD / 32; ++h) {
         float o[32];
-        fa_tmem_ld32(tmem_o + lane_addr + part * OCOLS + h * 32, o);
+        fa_tmem_ld32(tmem_o + lane_addr + h * 32, o);
         if (valid) {
 #pragma unroll
           for (int ch = 0; ch < 4; ++ch) {
@@ -631,7 +605,7 @@ extern "C" int ie_attention_tcgen05_error() {
 }
 
 // keys of a tile for a head size (0: not taken)
-static int fa_key_tile(int hd) { return (hd == 64 || hd == 128) ? 64 : 0; }
+static int fa_key_tile(int hd) { return (hd == 64 || hd == 128) ? 64 : 0; }   // pages must divide this many keys
 
 // 1 if the kernel takes the geometry: head size 64 or 128, pages of at least 8 keys, a power of two, that divide a
 // key tile (64 keys); no window
@@ -642,17 +616,17 @@ extern "C" int ie_attention_tcgen05_supports(int hd, int page_size, int window) 
   return 1;
 }
 
-template <int HD, int KT, int STAGES>
+template <int HD, int KT, int STAGES, int PBUF, int SBUF>
 static int fa_launch(const CUtensorMap& mk, const CUtensorMap& mv, const FaParams& p, int n_work, int n_kv_heads,
                      cudaStream_t stream) {
-  const size_t smem = Geo<HD, KT, STAGES>::TILES_BYTES + 128;
+  const size_t smem = Geo<HD, KT, STAGES, PBUF, SBUF>::TILES_BYTES + 128;
   static bool attr = false;
   if (!attr) {
-    cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel<HD, KT, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel<HD, KT, STAGES, PBUF, SBUF>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     attr = true;
   }
-  return launch_k(attention_tcgen05_kernel<HD, KT, STAGES>, dim3((unsigned)((long long)n_work * n_kv_heads)), FA_THREADS, smem,
+  return launch_k(attention_tcgen05_kernel<HD, KT, STAGES, PBUF, SBUF>, dim3((unsigned)((long long)n_work * n_kv_heads)), FA_THREADS, smem,
                   stream, mk, mv, p);
 }
 
@@ -666,7 +640,7 @@ extern "C" int ie_attention_tcgen05(const void* q, void* out, const void* kpool,
                                     const int* positions, cudaStream_t stream) {
   if (n_work <= 0) return IE_OK;
   if ((cos_t == nullptr) != (sin_t == nullptr) || (cos_t && !positions)) return IE_BAD_SIZE;
-  if (cos_t && (FA_SOFTMAX_SPLIT != 1 || (((uintptr_t)cos_t | (uintptr_t)sin_t) & 15))) return IE_BAD_ALIGN;
+  if (cos_t && (((uintptr_t)cos_t | (uintptr_t)sin_t) & 15)) return IE_BAD_ALIGN;
   if (!ie_attention_tcgen05_supports(hd, page_size, 0)) return IE_BAD_SIZE;
   if (n_kv_heads <= 0 || n_heads % n_kv_heads || n_pool_pages <= 0) return IE_BAD_SIZE;
   if (((uintptr_t)q | (uintptr_t)out | (uintptr_t)kpool | (uintptr_t)vpool) & 15) return IE_BAD_ALIGN;
@@ -686,6 +660,15 @@ extern "C" int ie_attention_tcgen05(const void* q, void* out, const void* kpool,
   while ((1 << p.page_shift) < page_size) ++p.page_shift;
   p.scale_log2 = scale * LOG2E;
   p.cos_t = cos_t; p.sin_t = sin_t; p.positions = positions;
-  if (hd == 64) return fa_launch<64, 64, 4>(mk, mv, p, n_work, n_kv_heads, stream);
-  return fa_launch<128, 64, 2>(mk, mv, p, n_work, n_kv_heads, stream);
+  // head size 64: two P buffers beside a ring of four stages (two blocks an SM); at 128 the ring takes that room.
+  // (-DIE_FA_KT64=128 -DIE_FA_STAGES64=2 -DIE_FA_PBUF64=1 -DIE_FA_SBUF64=1, key tiles of 128 with one S buffer, was
+  // measured: 8,192 tokens 467 us against 450 us)
+#ifndef IE_FA_KT64
+#define IE_FA_KT64 64
+#define IE_FA_STAGES64 4
+#define IE_FA_PBUF64 2
+#define IE_FA_SBUF64 2
+#endif
+  if (hd == 64) return fa_launch<64, IE_FA_KT64, IE_FA_STAGES64, IE_FA_PBUF64, IE_FA_SBUF64>(mk, mv, p, n_work, n_kv_heads, stream);
+  return fa_launch<128, 64, 2, 1, 2>(mk, mv, p, n_work, n_kv_heads, stream);
 }
