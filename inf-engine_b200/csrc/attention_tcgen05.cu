@@ -127,6 +127,18 @@ __device__ __forceinline__ void fa_umma(uint32_t tmem_d, uint64_t adesc, uint64_
 __device__ __forceinline__ void fa_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
+// the load alone: the registers are good after fa_tmem_wait_ld()
+__device__ __forceinline__ void fa_tmem_ld32_issue(uint32_t taddr, float* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=f"(r[0]), "=f"(r[1]), "=f"(r[2]), "=f"(r[3]), "=f"(r[4]), "=f"(r[5]), "=f"(r[6]), "=f"(r[7]), "=f"(r[8]),
+        "=f"(r[9]), "=f"(r[10]), "=f"(r[11]), "=f"(r[12]), "=f"(r[13]), "=f"(r[14]), "=f"(r[15]), "=f"(r[16]),
+        "=f"(r[17]), "=f"(r[18]), "=f"(r[19]), "=f"(r[20]), "=f"(r[21]), "=f"(r[22]), "=f"(r[23]), "=f"(r[24]),
+        "=f"(r[25]), "=f"(r[26]), "=f"(r[27]), "=f"(r[28]), "=f"(r[29]), "=f"(r[30]), "=f"(r[31])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void fa_tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void fa_tmem_ld32(uint32_t taddr, float (&r)[32]) {
   uint32_t u[32];
   asm volatile(
@@ -420,25 +432,26 @@ __global__ void __launch_bounds__(FA_THREADS, Geo<HD, KT, STAGES, PBUF, SBUF>::B
       const int k0 = j * KT;
       // a tile whose last key every row of the warp may see needs no mask
       const bool interior = __all_sync(0xffffffffu, k0 + KT - 1 <= limit);
-      // the scores of the row, 32 at a time, read twice from tensor memory (once for the maximum, once for the
-      // exponentials)
+      // the scores of the row are read twice from tensor memory (once for the maximum, once for the exponentials),
+      // each time with all loads on their way before the one wait
       float mx = -INFINITY;
+      {
+        float sc[KT];
 #pragma unroll
-      for (int q4 = 0; q4 < KT / 32; ++q4) {
-        float sc[32];
-        fa_tmem_ld32(tmem_s + lane_addr + (j % SBUF) * KT + q4 * 32, sc);
+        for (int q4 = 0; q4 < KT / 32; ++q4) fa_tmem_ld32_issue(tmem_s + lane_addr + (j % SBUF) * KT + q4 * 32, sc + q4 * 32);
+        fa_tmem_wait_ld();
         if (interior) {
           float mb = -INFINITY;                              // two chains of three-input maxima
 #pragma unroll
-          for (int i = 0; i < 32; i += 4) {
+          for (int i = 0; i < KT; i += 4) {
             mx = fa_max3(mx, sc[i], sc[i + 1]);
             mb = fa_max3(mb, sc[i + 2], sc[i + 3]);
           }
           mx = fmaxf(mx, mb);
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (k0 + q4 * 32 + i <= limit) mx = fmaxf(mx, sc[i]);
+          for (int i = 0; i < KT; ++i)
+            if (k0 + i <= limit) mx = fmaxf(mx, sc[i]);
         }
       }
       // The maximum in use follows the true one only when that has grown by more than 2^8 (or is the
@@ -480,28 +493,27 @@ __global__ void __launch_bounds__(FA_THREADS, Geo<HD, KT, STAGES, PBUF, SBUF>::B
       // exponentials, their sums and P; a tile that needs no mask takes the loop without the comparisons
       auto exp_pass = [&](auto masked) {
         constexpr bool MASKED = decltype(masked)::value;
+        float sc[KT];
 #pragma unroll
-        for (int q4 = 0; q4 < KT / 32; ++q4) {
-          float sc[32];
-          fa_tmem_ld32(tmem_s + lane_addr + (j % SBUF) * KT + q4 * 32, sc);
+        for (int q4 = 0; q4 < KT / 32; ++q4) fa_tmem_ld32_issue(tmem_s + lane_addr + (j % SBUF) * KT + q4 * 32, sc + q4 * 32);
+        fa_tmem_wait_ld();
 #pragma unroll
-          for (int ch = 0; ch < 4; ++ch) {
-            float e[8];
+        for (int ch = 0; ch < KT / 8; ++ch) {
+          float e[8];
 #pragma unroll
-            for (int i = 0; i < 8; i += 2) {
-              float x0, x1;
-              fa_unpair(fa_fma2(fa_pair(sc[ch * 8 + i], sc[ch * 8 + i + 1]), scale2, neg_m2), x0, x1);
-              x0 = fa_exp2(x0);
-              x1 = fa_exp2(x1);
-              e[i] = (!MASKED || k0 + q4 * 32 + ch * 8 + i <= limit) ? x0 : 0.f;
-              e[i + 1] = (!MASKED || k0 + q4 * 32 + ch * 8 + i + 1 <= limit) ? x1 : 0.f;
-              if (i & 2) sum2b = fa_add2(sum2b, fa_pair(e[i], e[i + 1]));
-              else sum2a = fa_add2(sum2a, fa_pair(e[i], e[i + 1]));
-            }
-            const int col = q4 * 32 + ch * 8;                // key index inside the tile
-            const uint4 v = make_uint4(fa_pack(e[0], e[1]), fa_pack(e[2], e[3]), fa_pack(e[4], e[5]), fa_pack(e[6], e[7]));
-            *reinterpret_cast<uint4*>(p_tile + (col >> 6) * ATOM_BYTES + sw128(r, (col & 63) >> 3)) = v;
+          for (int i = 0; i < 8; i += 2) {
+            float x0, x1;
+            fa_unpair(fa_fma2(fa_pair(sc[ch * 8 + i], sc[ch * 8 + i + 1]), scale2, neg_m2), x0, x1);
+            x0 = fa_exp2(x0);
+            x1 = fa_exp2(x1);
+            e[i] = (!MASKED || k0 + ch * 8 + i <= limit) ? x0 : 0.f;
+            e[i + 1] = (!MASKED || k0 + ch * 8 + i + 1 <= limit) ? x1 : 0.f;
+            if (i & 2) sum2b = fa_add2(sum2b, fa_pair(e[i], e[i + 1]));
+            else sum2a = fa_add2(sum2a, fa_pair(e[i], e[i + 1]));
           }
+          const int col = ch * 8;                            // key index inside the tile
+          const uint4 v = make_uint4(fa_pack(e[0], e[1]), fa_pack(e[2], e[3]), fa_pack(e[4], e[5]), fa_pack(e[6], e[7]));
+          *reinterpret_cast<uint4*>(p_tile + (col >> 6) * ATOM_BYTES + sw128(r, (col & 63) >> 3)) = v;
         }
       };
       if (interior) exp_pass(std::false_type{});
