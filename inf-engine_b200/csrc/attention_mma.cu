@@ -499,13 +499,17 @@ __device__ __forceinline__ unsigned long long trace_now() {
 // of them adds the blocks up in ascending order, reading the others' shared memory.  With more blocks each
 // writes one partial result to global memory and takes a ticket, and the block that takes the last ticket adds
 // the blocks up, again in ascending order: the result does not depend on which block that is, nor on the path.
+// Six warps a block at both head sizes, 96 KB of tiles per block (two blocks share an SM): tiles of 32 keys at head
+// size 64, of 16 keys at 128.  (Three warps with tiles of 32 keys at head size 128 read 64 requests of 8,192 keys at
+// 4.4 TB/s, six warps with tiles of 16 at 6.4 TB/s: a tile's MMAs and softmax are one dependent chain per warp, and
+// three warps a block left the SM waiting on it.)
 #ifndef IE_DC_WARPS
-#define IE_DC_WARPS (HD <= 64 ? 6 : 3)   // 96 KB of tiles per block: two blocks share an SM
+#define IE_DC_WARPS 6
 #endif
 constexpr int DC_WARPS = IE_DC_WARPS;
 constexpr int DC_THREADS = DC_WARPS * 32;
 #ifndef IE_DC_KT
-#define IE_DC_KT 32
+#define IE_DC_KT (HD <= 64 ? 32 : 16)
 #endif
 #ifndef IE_DC_STAGES
 #define IE_DC_STAGES 2
