@@ -261,8 +261,9 @@ __global__ void __launch_bounds__(SM_THREADS) sample_kernel(const float* __restr
   sample_row(logits + (size_t)blockIdx.x * row_stride, rows[blockIdx.x], out + blockIdx.x, vocab, red, redi, chunk_sum);
 }
 
-// Greedy rows of a large vocabulary, spread over SG_CHUNKS blocks per row: one block alone reads a row of
-// half a megabyte at the speed of one SM.  Each block finds the maximum of its slice and its first index,
+// Greedy rows of a large vocabulary, spread over up to SG_CHUNKS blocks per row (fewer when there are many rows: the
+// launch is kept near four blocks an SM; 64 rows over 64 blocks each were 4,096 blocks of two elements a thread): one
+// block alone reads a row of half a megabyte at the speed of one SM.  Each block finds the maximum of its slice and its first index,
 // takes a ticket of the row, and the block with the last ticket picks the best slice (ties: lowest index,
 // as argmax does).  A row that is not greedy is sampled by its first block in the same launch (the other blocks of
 // that row leave at once): one launch answers every row, whatever the mix.
@@ -276,7 +277,7 @@ __device__ unsigned int g_sg_ticket[SG_MAX_ROWS];   // zero between launches
 
 __global__ void __launch_bounds__(SM_THREADS) greedy_split_kernel(const float* __restrict__ logits,
                                                                   const SampleRow* __restrict__ rows, int* __restrict__ out,
-                                                                  int vocab, size_t row_stride) {
+                                                                  int vocab, size_t row_stride, int n_chunks) {
   __shared__ float sv[32];
   __shared__ int si[32];
   __shared__ unsigned int last;
@@ -290,7 +291,7 @@ __global__ void __launch_bounds__(SM_THREADS) greedy_split_kernel(const float* _
     if (chunk == 0) sample_row(logits + (size_t)row * row_stride, rows[row], out + row, vocab, red, redi, chunk_sum);
     return;
   }
-  const int per = (vocab + SG_CHUNKS - 1) / SG_CHUNKS;
+  const int per = (vocab + n_chunks - 1) / n_chunks;
   const int lo = chunk * per, hi = min(vocab, lo + per);
   const float* x = logits + (size_t)row * row_stride;
   // four candidates a thread, each walking its own indices upwards (the first maximum of each stays), so that the
@@ -326,11 +327,11 @@ __global__ void __launch_bounds__(SM_THREADS) greedy_split_kernel(const float* _
     g_sg_idx[row * SG_CHUNKS + chunk] = best_i;
     __threadfence();
     last = atomicAdd(&g_sg_ticket[row], 1u);
-    if (last == SG_CHUNKS - 1) {
+    if (last == (unsigned int)n_chunks - 1) {
       __threadfence();
       float b = -INFINITY;
       int bi = 0x7fffffff;
-      for (int c = 0; c < SG_CHUNKS; ++c) {
+      for (int c = 0; c < n_chunks; ++c) {
         const float v = __ldcg(&g_sg_val[row * SG_CHUNKS + c]);
         const int i = __ldcg(&g_sg_idx[row * SG_CHUNKS + c]);
         if (i != 0x7fffffff && (v > b || bi == 0x7fffffff || (v == b && i < bi))) { b = v; bi = i; }
@@ -346,9 +347,11 @@ extern "C" int ie_sample(const float* logits, const void* rows, int* out, int n_
   if (n_rows <= 0) return IE_OK;
   if (vocab <= 0) return IE_BAD_SIZE;
   if (vocab >= 32768 && n_rows <= SG_MAX_ROWS) {
-    // one launch: greedy rows over SG_CHUNKS blocks each, every other row by its first block
-    return launch_k(greedy_split_kernel, dim3(SG_CHUNKS, n_rows), SM_THREADS, 0, stream, logits, (const SampleRow*)rows, out,
-                    vocab, (size_t)row_stride);
+    // one launch: greedy rows over several blocks each, every other row by its first block
+    int n_chunks = (4 * 148 + n_rows - 1) / n_rows;
+    n_chunks = n_chunks < 1 ? 1 : (n_chunks > SG_CHUNKS ? SG_CHUNKS : n_chunks);
+    return launch_k(greedy_split_kernel, dim3(n_chunks, n_rows), SM_THREADS, 0, stream, logits, (const SampleRow*)rows, out,
+                    vocab, (size_t)row_stride, n_chunks);
   }
   return launch_k(sample_kernel, n_rows, SM_THREADS, 0, stream, logits, (const SampleRow*)rows, out, vocab,
                   (size_t)row_stride);
