@@ -605,7 +605,7 @@ int launch_tma(const TmaParams& p, int nt, int n_sms, size_t smem, cudaStream_t 
 // 1 if the kernel takes this product (M <= 16, K a multiple of 256, activations fit in shared memory)
 // Activations are kept in shared memory when they take at most this much; beyond it the plain prologue
 // reads them from L2 and the RMSNorm prologue is not offered.
-constexpr size_t X_SMEM_LIMIT = 72 * 1024;
+constexpr size_t X_SMEM_LIMIT = 100 * 1024;
 
 extern "C" int ie_gemm_stream_tma_supports(int M, int N, int K, int pro) {
   if (M <= 0 || M > 16 || N <= 0 || K <= 0 || (K % 256)) return 0;

@@ -362,6 +362,12 @@ def stream_error(lib=None) -> int:
     return int((lib or stream_library()).ie_gemm_stream_tma_error())
 
 
+def gemm_stream_ring_supports(m: int, n: int, k: int, normed: bool) -> bool:
+    """Whether the streaming kernel with the shared-memory ring takes m rows of k columns (with a norm in its
+    prologue: the rows must then fit in shared memory beside the ring)."""
+    return bool(stream_library().ie_gemm_stream_tma_supports(m, n, k, 1 if normed else 0))
+
+
 def gemm_stream(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, m: int, epi: str = "bf16",
                 gain: torch.Tensor | None = None, eps: float = 0.0, row_index: torch.Tensor | None = None,
                 nt: int | None = None, prenormed=None, normout=None, lib=None) -> None:

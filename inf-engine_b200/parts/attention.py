@@ -74,7 +74,7 @@ class PagedAttention:
                                 dtype=self.rt.act_dtype)
 
     def can_fuse(self, n_tokens: int, norm) -> bool:
-        return hasattr(norm, "fusable_rms") and self.qkv.streams(n_tokens) and self.o.streams(n_tokens)
+        return hasattr(norm, "fusable_rms") and self.qkv.streams(n_tokens, normed=True) and self.o.streams(n_tokens)
 
     def forward_fused(self, residual: torch.Tensor, norm, ctx, cache: CacheView) -> None:
         """residual += o(attention(qkv(norm(residual)))): the norm rides in the qkv product's prologue and the

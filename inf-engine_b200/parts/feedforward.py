@@ -40,7 +40,8 @@ class GatedMLP:
         self.down = Linear(tensors[spec.down_proj], rt, "down")
 
     def can_fuse(self, n_tokens: int, norm) -> bool:
-        return (hasattr(norm, "fusable_rms") and self.gate_up.streams(n_tokens) and self.down.streams(n_tokens))
+        return (hasattr(norm, "fusable_rms") and self.gate_up.streams(n_tokens, normed=True)
+                and self.down.streams(n_tokens))
 
     def forward_fused(self, residual: torch.Tensor, norm, ctx) -> None:
         """residual += down(silu(gate(n)) * up(n)) with n = norm(residual), in two launches: the norm rides in

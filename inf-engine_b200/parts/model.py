@@ -107,7 +107,7 @@ class DecoderModel:
     def _head_logits(self, residual, pending, ctx, n: int, m: int) -> torch.Tensor:
         rt, spec = self.rt, self.spec
         logits = rt.ws.take("logits", (m, spec.vocab_size), torch.float32)
-        if self.head.streams(m) and hasattr(self.final_norm, "fusable_rms"):
+        if self.head.streams(m, normed=True) and hasattr(self.final_norm, "fusable_rms"):
             # final norm on the gathered rows inside the head product
             if pending is not None:
                 kernels.residual_add(residual, pending)

@@ -173,7 +173,7 @@ def test_gemm_stream_plain_and_fused(M, N, K):
 
 
 @pytest.mark.parametrize("M", [1, 5, 8, 9, 16])
-@pytest.mark.parametrize("N,K", [(389, 256), (1000, 768), (2050, 2048), (520, 8192)])
+@pytest.mark.parametrize("N,K", [(389, 256), (1000, 768), (2050, 2048), (776, 3072), (520, 8192)])
 def test_gemm_stream_bulk_copy_kernel(M, N, K):
     """The persistent kernel (weights by cp.async.bulk through a shared-memory ring), default for K % 256 == 0."""
     from inf_engine_b200 import kernels
@@ -217,7 +217,7 @@ def test_gemm_stream_bulk_copy_kernel(M, N, K):
     assert kernels.stream_error() == 0
 
 
-@pytest.mark.parametrize("M,hidden,inter", [(8, 2048, 8192), (3, 1024, 2048), (13, 512, 1024)])
+@pytest.mark.parametrize("M,hidden,inter", [(8, 2048, 8192), (3, 1024, 2048), (13, 512, 1024), (16, 3072, 1024)])
 def test_norm_handed_over_between_streaming_products(M, hidden, inter):
     """residual += h W_down^T with the next norm's input prepared on the way (bfloat16(residual * gain) and per-block
     sums of squares), then a product that takes that input instead of normalising the residual itself: both against
@@ -242,7 +242,7 @@ def test_norm_handed_over_between_streaming_products(M, hidden, inter):
         assert torch.equal(xg.float().cpu(), (res.cpu() * gain.float().cpu()).to(bf).float())
         total = ssq[:M].sum(dim=1).cpu()
         assert torch.allclose(total, (res.cpu() ** 2).sum(dim=1), rtol=1e-5)
-        assert torch.isfinite(ssq).all() and float(ssq[M:].abs().max()) == 0.0
+        assert torch.isfinite(ssq).all() and (M == kernels.SSQ_SLOT or float(ssq[M:].abs().max()) == 0.0)
         # the product that takes it, against the one that normalises for itself
         out_a = torch.empty(M, wq.shape[0], device=DEV, dtype=bf)
         out_b = torch.empty_like(out_a)
