@@ -54,6 +54,7 @@ class DecodeGraphs:
         self._buckets: dict = {}
         self.replays = 0
         self.captures = 0
+        self._capture_stream = None
 
     def usable(self, entries) -> bool:
         if not self.runner.model.graph_safe:
@@ -186,12 +187,13 @@ class DecodeGraphs:
             if b.graph is None or b.generation != self.generation:
                 # warm-up outside capture (sizes the buffers, builds the work lists), then capture
                 before = self.ws.moves
-                s = torch.cuda.Stream()
-                s.wait_stream(torch.cuda.current_stream())
-                with torch.cuda.stream(s):
-                    for _ in range(2):
-                        self._forward(b)
-                torch.cuda.current_stream().wait_stream(s)
+                cs = self._capture_stream
+                if cs is None:
+                    cs = self._capture_stream = torch.cuda.Stream()
+                cs.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(cs):
+                    self._forward(b)
+                torch.cuda.current_stream().wait_stream(cs)
                 torch.cuda.synchronize()
                 if self.ws.moves != before:
                     # a buffer was replaced by a larger one: graphs captured earlier point at freed memory.  (A buffer
@@ -203,16 +205,22 @@ class DecodeGraphs:
                 n0 = kernels.LAUNCHES
                 # The collector must not run inside the capture: garbage that owns CUDA objects (an engine
                 # dropped earlier, with graphs of its own) would free them there, which a capture forbids and
-                # which invalidates it.  So collect before, and hold the collector until the capture ends.
-                gc.collect()
+                # which invalidates it.  So the collector is held until the capture ends.  The capture is begun
+                # and ended by hand: torch.cuda.graph() would first run a full collection and empty the
+                # allocator's cache, tens of milliseconds for every graph of a long generation.
                 gc_was_on = gc.isenabled()
                 gc.disable()
                 try:
-                    with torch.cuda.graph(g, capture_error_mode="thread_local"):
-                        b.logits = self._forward(b)
+                    with torch.cuda.stream(cs):
+                        g.capture_begin(capture_error_mode="thread_local")
+                        try:
+                            b.logits = self._forward(b)
+                        finally:
+                            g.capture_end()
                 finally:
                     if gc_was_on:
                         gc.enable()
+                torch.cuda.current_stream().wait_stream(cs)
                 b.n_kernels = kernels.LAUNCHES - n0
                 b.graph, b.generation = g, self.generation
                 self.captures += 1

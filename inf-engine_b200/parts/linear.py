@@ -28,14 +28,15 @@ class Linear:
     def streams(self, n_rows: int, normed: bool = False) -> bool:
         """True when the weight-streaming kernel of this package takes this product:
         bfloat16 weight and activations, few rows, K a multiple of 8.  ``normed``: the product is to
-        carry a norm in its prologue.  A weight of real size is streamed only by the kernel with the
-        shared-memory ring (the other one, for the widths of tiny models, reads such a weight at a
-        fraction of the HBM rate); that kernel keeps the rows of a normed input in shared memory, and
-        where they do not fit (9 to 16 rows of 3,072 columns and more) the library product stands in."""
+        carry a norm in its prologue.  A weight of real size (four million elements and more) is
+        streamed only by the kernel with the shared-memory ring: the other one, for the widths of tiny
+        models, reads such a weight at a fraction of the HBM rate.  The ring kernel wants K a multiple
+        of 256 and keeps the rows of a normed input in shared memory; where it does not take the
+        product (9 to 16 rows of more than 3,072 columns, say) the library product stands in."""
         if not (self.weight.dtype is torch.bfloat16 and self.rt.act_dtype is torch.bfloat16
                 and 0 < n_rows <= kernels.STREAM_BEST_ROWS and self.in_features % 8 == 0):
             return False
-        if self.in_features % 256 == 0 and self.out_features * self.in_features >= (1 << 22):
+        if self.out_features * self.in_features >= (1 << 22):
             return kernels.gemm_stream_ring_supports(n_rows, self.out_features, self.in_features, normed)
         return True
 
