@@ -35,13 +35,25 @@ def _bucket(n: int, choices) -> int | None:
     return None
 
 
+def keys_bucket(keys: int) -> int:
+    """The longest context a graph is cut for, given the step's: the next multiple of KEYS_STEP up to 4,096 keys, of a
+    sixteenth of the power of two below beyond that.  The decode attention's split is part of the captured launch, so a
+    graph cut for more keys than the step has leaves some of its warps without keys (at most a sixteenth of them
+    here), and every new bucket is a capture of some 20 ms: a capture per 256 keys of a context of 32,768 would be
+    one every 256 steps for good."""
+    step = KEYS_STEP
+    if keys > 16 * KEYS_STEP:
+        step = (1 << (int(keys - 1).bit_length() - 1)) // 16
+    return -(-keys // step) * step
+
+
 class _Captured:
     def __init__(self):
         self.graph = None
         self.generation = -1
 
 
-KEYS_STEP = 256      # graphs are captured per this many keys of the longest context
+KEYS_STEP = 256      # graphs are captured per this many keys of the longest context (more when it is long: keys_bucket)
 MAX_GRAPHS = 48      # captured graphs kept; the one unused for longest goes first
 
 
@@ -171,7 +183,7 @@ class DecodeGraphs:
                        for g in cache.kv_groups)
         # the split-key attention is cut for the longest context of the step, in steps of KEYS_STEP keys: a
         # graph serves until some request has grown past its step
-        keys_hint = -(-(max(cache.lengths[e.rid] for e in entries) + 1) // KEYS_STEP) * KEYS_STEP
+        keys_hint = keys_bucket(max(cache.lengths[e.rid] for e in entries) + 1)
         b = self._get(B, widths, keys_hint)
         self._fill(b, entries, sample_rows, token_src)
         if device_tokens is not None:
