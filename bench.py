@@ -14,6 +14,7 @@ larger than L2, so every step streams them from HBM: no L2 flush is needed.
 from __future__ import annotations
 
 import argparse
+import gc
 import json
 import os
 import subprocess
@@ -183,6 +184,7 @@ def run_ours(args):
         entries = [StepEntry(r, [0], [0]) for r in rids]
         for _ in range(warmup):
             _, ids = runner.step_and_sample(entries, rows, device_tokens=ids)
+        gc.collect()          # a full collection of the host's garbage inside the timed steps would stall the launches
         torch.cuda.synchronize()
         ctx0 = runner.length(rids[0])
         n0 = kernels.LAUNCHES
@@ -212,6 +214,7 @@ def run_ours(args):
             engine.step()
         for _ in range(warmup):
             engine.step()
+        gc.collect()
         torch.cuda.synchronize()
         n_before = sum(len(r.generated) for r in reqs)
         t0 = time.perf_counter()
@@ -248,7 +251,6 @@ def run_ours(args):
     # the other two configurations of the baseline: continuous batching at their sizes, wall clock
     workloads = {}
     if not args.no_workloads:
-        import gc
         del engine, runner
         gc.collect()
         torch.cuda.empty_cache()
@@ -299,7 +301,6 @@ def measure_workload(model, n_req, lo, hi, new, temperatures, seed=0, layers=0):
     wall clock around the whole run; every run is made twice and the second one counts (the first one also captures
     the decode graphs).  One engine serves every temperature; returns one record per temperature."""
     import dataclasses
-    import gc
 
     import numpy as np
     import torch

@@ -10,6 +10,7 @@ sampled ids.
 
 from __future__ import annotations
 
+import gc
 import tempfile
 import time
 from pathlib import Path
@@ -229,8 +230,16 @@ class Engine:
         """Submit everything, run to completion; ``{req_id: generated}``
         (engine/llama_paged_engine.py:445-455).  Requests refused at submit map to []."""
         refused = [r for r in requests if not self.submit(r)]
-        while self.has_work:
-            self.step(time.perf_counter())
+        # A decode step is some 50 us of host work in front of a millisecond of GPU work; a full collection of the
+        # host's garbage (10 ms and more with a model's objects to walk) in the middle of the run leaves the GPU
+        # without launches for ten steps.  What exists now is set aside from the collector for the run.
+        gc.collect()
+        gc.freeze()
+        try:
+            while self.has_work:
+                self.step(time.perf_counter())
+        finally:
+            gc.unfreeze()
         kernels.check_device_errors()
         out = {r.req_id: r.generated for r in self.completed}
         out.update({r.req_id: [] for r in refused})
