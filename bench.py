@@ -133,7 +133,7 @@ def run_ours(args):
     with tempfile.TemporaryDirectory(prefix="bench_model_") as tmp:
         write_random_model(cfg, args.seed, tmp)
         engine = Engine.from_dir(tmp, dtype="bfloat16", n_total_blocks=args.pool_requests * POOL_CONTEXT // PAGE, block_size=PAGE,
-                                 max_requests=64, max_tokens_per_step=8192, chunk=2048)
+                                 max_requests=max(64, args.pool_requests), max_tokens_per_step=8192, chunk=2048)
     t_build = time.perf_counter() - t_build
     runner = engine.runner
     V = cfg.vocab_size
