@@ -593,8 +593,10 @@ DECODE_CASES = [
     # long contexts: more blocks per stream than one round of the last block's merge takes
     (8, 2, 64, 16, [1, 1], [9000, 5], None, 64),
     (4, 1, 128, 16, [1, 2], [7, 6100], None, 64),
-    # every size of the cluster that adds the blocks of a (request, kv head) up: 4 to 8 blocks of six warps
-    # (head size 64) or three (128) for the long request, while the short one's other blocks have no keys
+    # head size 128 walks the keys in tiles of 16: splits that are no multiple of a page, pages of 32, a group of 3
+    (24, 8, 128, 32, [1, 1], [3000, 40], None, 96),
+    # every size of the cluster that adds the blocks of a (request, kv head) up: 4 to 8 blocks of six warps for
+    # the long request, while the short one's other blocks have no keys
     (8, 2, 64, 16, [1, 1], [1394, 5], None, 64),
     (8, 2, 64, 16, [1, 1], [1778, 900], None, 64),
     (8, 2, 64, 16, [1, 2], [2162, 5], None, 64),
@@ -636,6 +638,7 @@ FUSED_DECODE_CASES = [
     (8, 2, 64, 16, [64, 200], None, 64, False, True),
     (8, 2, 64, 16, [64, 200], None, 64, True, False),
     (8, 2, 64, 16, [6000, 100], None, 64, True, True),
+    (24, 8, 128, 16, [2100, 97, 15], None, 96, True, True),
 ]
 
 
