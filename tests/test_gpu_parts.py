@@ -160,6 +160,30 @@ def test_gated_mlp_keeps_a_32bit_weight_in_32bit():
     assert torch.allclose(part.forward(x.to(DEV), None).float().cpu(), want, atol=2e-2, rtol=2e-2)
 
 
+def test_a_product_the_ring_kernel_cannot_keep_goes_to_the_library():
+    """Few rows of a weight of real size are streamed only by the kernel with the shared-memory ring; where that one
+    does not take the product (a normed input of 9 to 16 rows that does not fit beside the ring, a K that is no multiple
+    of 256) the part says so and the library product stands in: the ring-less kernel is for the widths of tiny models."""
+    from inf_engine_b200.parts import Runtime
+    from inf_engine_b200.parts.linear import Linear
+    rt = Runtime(DEV, torch.bfloat16)
+    mk = lambda n, k: Linear(torch.zeros(n, k, device=DEV, dtype=torch.bfloat16), rt)
+    wide, wider, odd, tiny = mk(2048, 3072), mk(1024, 4096), mk(4096, 1160), mk(96, 120)
+    assert wide.streams(8, normed=True) and wide.streams(16, normed=True)        # 16 rows x 3,072 fit: 99 KB
+    assert wider.streams(8, normed=True) and not wider.streams(9, normed=True)     # 16 rows x 4,096 do not
+    assert wider.streams(16)                                                       # plain rows are read from L2
+    assert not odd.streams(4) and not odd.streams(4, normed=True)                  # K % 256 != 0 at real size
+    assert tiny.streams(4) and tiny.streams(16, normed=True) and not tiny.streams(17)
+    # and the library's answer is the product
+    torch.manual_seed(5)
+    lin = Linear((torch.randn(4096, 1160, device=DEV) * 0.05).bfloat16(), rt)
+    x = torch.randn(4, 1160, device=DEV).bfloat16()
+    out = torch.empty(4, 4096, device=DEV, dtype=torch.bfloat16)
+    lin(x, out)
+    want = x.float().cpu() @ lin.weight.float().cpu().T
+    assert float((out.float().cpu() - want).abs().max()) <= 1e-2 * float(want.abs().max())
+
+
 # ------------------------------------------------------------------ a toy mixer
 @dataclass(frozen=True)
 class ToyDecaySpec:

@@ -50,3 +50,16 @@ def test_small_requests_of_a_step_are_counted_once():
     graph_ctx = StepContext(None, 16)
     graph_ctx.host = {"q_lens": [1, 1]}                         # a captured step has no host copy of the lengths
     assert graph_ctx.keys_of_small_requests(4, 16) == (0, 0)
+
+
+def test_graph_buckets_of_the_longest_context():
+    from inf_engine_b200.engine.graphs import KEYS_STEP, keys_bucket
+    last = 0
+    for keys in sorted(list(range(1, 9000, 37)) + [8192, 8193, 16384, 16385, 40000, 131072, 1 << 20]):
+        b = keys_bucket(keys)
+        assert b >= keys and b >= last                       # holds the step's keys; never shrinks as they grow
+        assert b - keys < max(KEYS_STEP, keys // 8)          # and is cut for at most an eighth more keys than there are
+        last = b
+    assert keys_bucket(2049) == 2304 and keys_bucket(8192) == 8192 and keys_bucket(8193) == 8704
+    # a context that doubles crosses 16 buckets once it is long, not one per 256 keys
+    assert len({keys_bucket(k) for k in range(32769, 65537)}) == 16
