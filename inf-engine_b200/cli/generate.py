@@ -49,6 +49,9 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--stats-json", default=None, help="write timing and engine counters here")
     p.add_argument("--trace-jsonl", default=None, help="write one JSON line per engine step here (batch make-up, pages free, host time)")
     p.add_argument("--nvtx", action="store_true", help="an NVTX range around every engine step, for a timeline tool")
+    p.add_argument("--checks", action="store_true",
+                   help="a checks build of the kernels: every page id, cache slot and token id they read is compared with "
+                        "the pool and the vocabulary; one out of range is reported and not used (slower; for debugging)")
     p.add_argument("--list-presets", action="store_true")
     return p
 
@@ -95,6 +98,9 @@ def main(argv=None) -> int:
     kw = dict(dtype=args.dtype, device=args.device, n_total_blocks=n_blocks, block_size=args.block_size,
               max_requests=args.max_batch, eos_token=args.eos_id, max_tokens_per_step=args.max_tokens_per_step,
               chunk=args.chunk, trace_path=args.trace_jsonl, nvtx=args.nvtx)
+    if args.checks:
+        from .. import kernels
+        kernels.enable_checks()
     t0 = time.perf_counter()
     if model_dir is not None:
         engine = Engine.from_dir(model_dir, **kw)

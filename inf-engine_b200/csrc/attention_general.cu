@@ -117,7 +117,7 @@ __global__ void __launch_bounds__(AG_THREADS) attention_general_kernel(AttnGener
       const int kp = kt + kk;
       float kv = 0.f, vv = 0.f;
       if (kp < key_end) {
-        const int page = table[kp / p.page_size];
+        const int page = IE_PAGE(table[kp / p.page_size]);
         if (page >= 0) {
           const size_t a = (((size_t)page * p.n_kv_heads + c) * p.page_size + (kp % p.page_size)) * hd + d;
           kv = to_f32(kpool[a]);
@@ -223,3 +223,5 @@ extern "C" int ie_attention_general(const void* q, void* out, const void* kpool,
   }
   return IE_BAD_DTYPE;
 }
+
+IE_CHECK_API(attention_general)

@@ -147,7 +147,7 @@ __device__ __forceinline__ void load_kv_tile(const MmaAttnParams& p, const int* 
     if (row < KT && kp < k_end && kp >= 0) {
       int pi, po;
       page_of(p, kp, pi, po);
-      const int page = __ldg(table + pi);
+      const int page = IE_PAGE(__ldg(table + pi));
       if (page >= 0) src_row[it] = (page * p.n_kv_heads + c) * p.page_size + po;
     }
   }
@@ -626,7 +626,7 @@ __global__ void __launch_bounds__(DC_THREADS, HD <= 64 ? 3 : 2) attention_decode
     *reinterpret_cast<float2*>(s_cos + lane * 2) = ld_nc_f2(p.cos_t + (size_t)pos * (HD / 2) + lane * 2);
     *reinterpret_cast<float2*>(s_sin + lane * 2) = ld_nc_f2(p.sin_t + (size_t)pos * (HD / 2) + lane * 2);
   }
-  if (owner && p.slot_mapping) new_slot = p.slot_mapping[q0];
+  if (owner && p.slot_mapping) new_slot = IE_SLOT(p.slot_mapping[q0]);
   TRACE(1);                                                  // early tiles requested
   pdl_wait();
   __syncthreads();                                           // the tables' row is in shared memory
@@ -1054,3 +1054,5 @@ extern "C" int ie_attention_decode_noalloc(const void* q, void* out, const void*
                              out_stride, table_stride, n_requests, n_tokens, n_heads, n_kv_heads, hd, page_size,
                              window, scale, n_splits, split_keys, stream);
 }
+
+IE_CHECK_API(attention_mma)

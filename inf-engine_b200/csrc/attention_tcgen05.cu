@@ -290,7 +290,7 @@ __global__ void __launch_bounds__(FA_THREADS, Geo<HD, KT, STAGES, PBUF, SBUF>::B
       if (lane < pages_per_tile) {
         const int kp = j * KT + lane * ps;
         if (kp < k_end) {
-          const int page = __ldg(table + (kp >> p.page_shift));
+          const int page = IE_PAGE(__ldg(table + (kp >> p.page_shift)));
           if (page > 0) row = (page * p.n_kv_heads + c) * ps;
         }
       }
@@ -684,3 +684,5 @@ extern "C" int ie_attention_tcgen05(const void* q, void* out, const void* kpool,
   if (hd == 64) return fa_launch<64, IE_FA_KT64, IE_FA_STAGES64, IE_FA_PBUF64, IE_FA_SBUF64>(mk, mv, p, n_work, n_kv_heads, stream);
   return fa_launch<128, 64, 2, 1, 2>(mk, mv, p, n_work, n_kv_heads, stream);
 }
+
+IE_CHECK_API(attention_tcgen05)

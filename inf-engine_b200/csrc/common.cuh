@@ -23,6 +23,49 @@
 
 typedef __nv_bfloat16 bf16;
 
+// A checks build (-DIE_CHECKS=1; `kernels.enable_checks()`): every page id, cache slot and token id that a kernel reads
+// from memory is compared with limits that the host has set (ie_check_limits_<unit>).  A value out of range is
+// recorded in a device word of the unit (the first one with its code, value and limit, and a count of all) and
+// replaced by a safe one (no page, no slot, token 0): nothing is read or written out of bounds and nothing traps;
+// the host reads the word (ie_check_read_<unit>) when the step is done.  Without the switch the macros are the value.
+// Codes: 1 page id, 2 cache slot, 3 token id.
+#ifdef IE_CHECKS
+static __device__ int g_check_word[4];
+static __device__ int g_check_limit[3] = {0x7fffffff, 0x7fffffff, 0x7fffffff};   // pages, slots, vocabulary
+__device__ __forceinline__ void ie_check_record(int code, int value, int limit) {
+  if (atomicCAS(&g_check_word[0], 0, code) == 0) {
+    g_check_word[1] = value;
+    g_check_word[2] = limit;
+  }
+  atomicAdd(&g_check_word[3], 1);
+}
+__device__ __forceinline__ int ie_checked(int v, int lo, int code, int safe) {
+  const int hi = g_check_limit[code - 1];
+  if (v >= lo && v < hi) return v;
+  ie_check_record(code, v, hi);
+  return safe;
+}
+#define IE_PAGE(v) ie_checked((v), -1, 1, -1)     /* -1: a page that is not held */
+#define IE_SLOT(v) ie_checked((v), -1, 2, -1)     /* -1: nothing is stored */
+#define IE_TOKEN(v) ie_checked((v), 0, 3, 0)
+#define IE_CHECK_API(unit)                                                                              \
+  extern "C" int ie_check_limits_##unit(int pages, int slots, int vocab) {                              \
+    const int lim[3] = {pages, slots, vocab};                                                           \
+    return (int)cudaMemcpyToSymbol(g_check_limit, lim, sizeof(lim));                                    \
+  }                                                                                                     \
+  extern "C" int ie_check_read_##unit(int* out4) {                                                      \
+    const int zero[4] = {0, 0, 0, 0};                                                                   \
+    cudaError_t e = cudaMemcpyFromSymbol(out4, g_check_word, sizeof(zero));                             \
+    if (e == cudaSuccess && out4[3]) e = cudaMemcpyToSymbol(g_check_word, zero, sizeof(zero));          \
+    return (int)e;                                                                                      \
+  }
+#else
+#define IE_PAGE(v) (v)
+#define IE_SLOT(v) (v)
+#define IE_TOKEN(v) (v)
+#define IE_CHECK_API(unit)
+#endif
+
 __device__ __forceinline__ float to_f32(float x) { return x; }
 __device__ __forceinline__ float to_f32(bf16 x) { return __bfloat162float(x); }
 

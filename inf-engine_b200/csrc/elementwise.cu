@@ -15,6 +15,9 @@ __global__ void embed_gather_kernel(const int* __restrict__ ids, const TW* __res
   const int n = blockIdx.x;
   int id = ids[n];
   const bool ok = id >= 0 && id < vocab;
+#ifdef IE_CHECKS
+  if (threadIdx.x == 0) (void)IE_TOKEN(id);
+#endif
   const TW* row = table + (size_t)(ok ? id : 0) * d;
   float* out = residual + (size_t)n * d;
   for (int i = threadIdx.x; i < d; i += blockDim.x) out[i] = ok ? to_f32(row[i]) : 0.f;
@@ -229,7 +232,7 @@ __global__ void rope_kv_write_kernel(TA* __restrict__ q, const TA* __restrict__ 
     x[i + half] = from_f32<TA>(b * cc + a * ss);
   }
   if (!(write_kv & 1)) return;
-  const int slot = slot_mapping[n];
+  const int slot = IE_SLOT(slot_mapping[n]);
   if (slot < 0) return;
   const int page = slot / page_size, off = slot - page * page_size;
   const TA* krow = k + (size_t)n * kv_stride;
@@ -259,7 +262,7 @@ __global__ void rope_kv_write_bf16_vec_kernel(bf16* __restrict__ q, const bf16* 
   const int half = hd >> 1;
   const int groups = half >> 3;                 // groups of eight pairs per head
   const int pos = positions[n];
-  const int slot = (write_kv & 1) ? slot_mapping[n] : -1;
+  const int slot = (write_kv & 1) ? IE_SLOT(slot_mapping[n]) : -1;
   const int page = slot >= 0 ? slot / page_size : 0, off = slot >= 0 ? slot - page * page_size : 0;
   const int total = (n_heads + n_kv_heads) * groups;
   const int first = (write_kv & 2) ? n_heads * groups : 0;     // bit 1: q is rotated elsewhere
@@ -413,3 +416,5 @@ extern "C" int ie_silu_mul(const void* in, void* out, int n_rows, int inter, int
     return launch_k(silu_mul_kernel<bf16>, blocks, 256, 0, stream, (const bf16*)in, (bf16*)out, inter, in_stride, total, interleaved);
   return IE_BAD_DTYPE;
 }
+
+IE_CHECK_API(elementwise)

@@ -13,6 +13,7 @@ from pathlib import Path
 
 import torch
 
+from .. import kernels
 from ..cache.manager import CacheManager
 from ..config.registry import detect_config
 from ..parts.registry import build_model, expected_tensors
@@ -53,6 +54,9 @@ class ModelRunner:
         self.cache.poison_free_pages = poison_free_pages      # a debugging aid: NaN in every page that nobody holds
         self.cache.allocate_storage(self.device)
         self.model.bind_cache(self.cache)
+        if kernels.checks_enabled():
+            # a checks build compares every page id, slot and token id the kernels read with this pool and vocabulary
+            kernels.set_check_limits(n_pages, n_pages * page_size, self.spec.vocab_size)
         self.page_size = page_size
         self.steps = 0
         self.use_graphs = use_graphs

@@ -89,6 +89,7 @@ def core():
                      "ie_attention_general", "ie_gemm_simt", "ie_argmax", "ie_repetition_penalty", "ie_sample"):
             getattr(lib, name).restype = c_int
         _core = lib
+        _apply_check_limits()
     return _core
 
 
@@ -243,6 +244,7 @@ def attention_mma_library(head_dim: int):
         lib.ie_attention_decode_warps.restype = c_int
         lib.ie_attention_decode_max_blocks.restype = c_int
         _mma[head_dim] = lib
+        _apply_check_limits()
     return lib
 
 
@@ -477,6 +479,7 @@ def attention_tcgen05_library():
         lib.ie_attention_tcgen05_supports.restype = c_int
         lib.ie_attention_tcgen05_error.restype = c_int
         _fa5_lib = lib
+        _apply_check_limits()
     return _fa5_lib
 
 
@@ -504,6 +507,70 @@ def attention_tcgen05(q, out, kpool, vpool, block_table, q_start, ctx_before, wo
         _stream()), "attention_tcgen05")
 
 
+# ------------------------------------------------ a checks build: page ids, slots and token ids compared with limits
+# (the device has no sanitizer here: this is what stands in for one while debugging a cache manager or a new part)
+CHECK_LIBRARIES = ("core", "attn_mma", "attn_tcgen05")
+CHECK_UNITS = ("elementwise", "attention_general", "attention_mma", "attention_tcgen05")
+CHECK_CODES = {1: "page id", 2: "cache slot", 3: "token id"}
+_check_limits: tuple[int, int, int] | None = None
+
+
+def enable_checks() -> None:
+    """Build the kernels that read page ids, cache slots and token ids from memory with ``-DIE_CHECKS=1``: a value out
+    of range is recorded and replaced by a safe one instead of being used.  Call before the first kernel runs (a
+    library that is already loaded stays as it was built); then ``set_check_limits``, and ``check_device_errors`` or
+    ``read_check_words`` after the steps in question."""
+    for name in CHECK_LIBRARIES:
+        BUILD_DEFINES.setdefault(name, {})["IE_CHECKS"] = 1
+
+
+def checks_enabled() -> bool:
+    return any(BUILD_DEFINES.get(name, {}).get("IE_CHECKS") for name in CHECK_LIBRARIES)
+
+
+def _loaded_check_functions(prefix: str):
+    from .csrc import build as _build
+    for lib in list(_build._loaded.values()):
+        for unit in CHECK_UNITS:
+            try:
+                fn = getattr(lib, f"{prefix}_{unit}")
+            except AttributeError:
+                continue
+            yield unit, fn
+
+
+def _apply_check_limits() -> None:
+    if _check_limits is None:
+        return
+    for unit, fn in _loaded_check_functions("ie_check_limits"):
+        fn.argtypes = [c_int, c_int, c_int]
+        fn.restype = c_int
+        _check(fn(*_check_limits), f"ie_check_limits_{unit}")
+
+
+def set_check_limits(n_pages: int, n_slots: int, vocab: int) -> None:
+    """The limits of a checks build: page ids below ``n_pages``, cache slots below ``n_slots``, token ids below
+    ``vocab`` (libraries that load later get them when they load)."""
+    global _check_limits
+    _check_limits = (int(n_pages), int(n_slots), int(vocab))
+    _apply_check_limits()
+
+
+def read_check_words() -> list[tuple[str, str, int, int, int]]:
+    """(unit, what, first bad value, its limit, how many) for every unit of a checks build that saw a value out of
+    range since the last call; synchronises the device."""
+    import ctypes
+    out = []
+    for unit, fn in _loaded_check_functions("ie_check_read"):
+        word = (ctypes.c_int * 4)()
+        fn.argtypes = [c_void_p]
+        fn.restype = c_int
+        _check(fn(ctypes.addressof(word)), f"ie_check_read_{unit}")
+        if word[3]:
+            out.append((unit, CHECK_CODES.get(word[0], str(word[0])), int(word[1]), int(word[2]), int(word[3])))
+    return out
+
+
 def check_device_errors() -> None:
     """Reads the error words of the kernels that wait on barriers (a wait that ran out records a code and the
     kernel leaves early) and raises if any is set.  It synchronises the device, so it belongs where the
@@ -517,3 +584,8 @@ def check_device_errors() -> None:
         found.append(f"tcgen05 attention: code {e}")
     if found:
         raise KernelError("a kernel gave up a bounded wait; its results are not valid (" + "; ".join(found) + ")")
+    if checks_enabled():
+        bad = read_check_words()
+        if bad:
+            raise KernelError("checks build: " + "; ".join(
+                f"{unit} read {n} value(s) out of range, the first a {what} of {v} (limit {lim})" for unit, what, v, lim, n in bad))
