@@ -183,3 +183,39 @@ def test_steps_booked_before_their_tokens_are_read():
     assert b.generated == [6, 6, 6]                      # ended by max_new_tokens at booking time
     assert sorted(r.req_id for r in finished) == [0, 1] and s.completed == finished
     assert cache.n_free_pages() == 64 and cache.n_free_slots == 4
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_page_reservations_that_fail_out_of_the_blue_are_survived(seed):
+    """Failure injection on the host: ``reserve`` says no (and takes nothing) at random calls, as if the pool had just
+    run dry.  The scheduler never raises: a portion waits or shrinks, a decoding request preempts the youngest; every
+    request still gets exactly its tokens, and every page and slot is back at the end."""
+    rng = random.Random(100 + seed)
+    cache, s = make(n_pages=rng.choice([8, 16]), page_size=rng.choice([2, 4]), max_requests=4,
+                    max_tokens_per_step=rng.choice([4, 16]), chunk=rng.choice([None, 3]))
+    true_reserve = cache.reserve
+    calls = {"n": 0, "refused": 0}
+
+    def flaky_reserve(rid, new_length):
+        calls["n"] += 1
+        if rng.random() < 0.25:
+            calls["refused"] += 1
+            return False
+        return true_reserve(rid, new_length)
+
+    cache.reserve = flaky_reserve
+    reqs = []
+    for i in range(10):
+        r = Request(i, [rng.randrange(50) for _ in range(rng.randrange(1, 10))], rng.randrange(1, 6))
+        if s.submit(r):
+            reqs.append(r)
+    assert reqs
+    steps = 0
+    while s.has_work:
+        run_step(cache, s, token_of=lambda r: len(r.generated))
+        steps += 1
+        assert steps < 5000
+    assert calls["refused"] > 0
+    for r in reqs:
+        assert r.generated == list(range(r.max_new_tokens)) and r.error is None
+    assert cache.n_free_pages() == cache.n_pages and cache.n_free_slots == 4
