@@ -44,7 +44,8 @@ constexpr uint32_t ATOM_BYTES = 128 * 64 * 2;   // 16 KB: 128 rows of one 128-by
 // Shared-memory geometry for head size HD, key tiles of KT keys and a ring of STAGES key/value stages.  Operands are kept as "halves" of 64
 // elements along their contiguous dimension (one swizzle atom wide): Q is HD/64 halves of [128 rows][64 dims],
 // a K or V stage HD/64 halves of [KT keys][64 dims], P is KT/64 (at least one) halves of [128 rows][64 keys].
-// PBUF: P buffers (1 or 2); SBUF: S buffers in tensor memory (1 or 2).
+// PBUF: P buffers in shared memory (1 or 2), or 0: P stays in tensor memory, in the columns of the S buffer it was made
+// from, and is the MMA's A operand from there (needs SBUF == 2); SBUF: S buffers in tensor memory (1 or 2).
 template <int HD, int KT, int STAGES, int PBUF, int SBUF>
 struct Geo {
   static constexpr int HALVES = HD / 64;
@@ -60,7 +61,7 @@ struct Geo {
   // blocks that fit an SM (shared memory, tensor memory); the register budget follows from it
   static constexpr int BLOCKS_PER_SM = (TILES_BYTES + 1152) * 3 <= 232448 && TMEM_COLS * 3 <= 512 ? 3
                                        : ((TILES_BYTES + 1152) * 2 <= 232448 && TMEM_COLS * 2 <= 512 ? 2 : 1);
-  static_assert(HD % 64 == 0 && HD <= 128 && KT % 64 == 0 && KT <= 128 && STAGES >= 2 && STAGES <= 4 && PBUF >= 1 && PBUF <= 2 && SBUF >= 1 && SBUF <= 2, "geometry");
+  static_assert(HD % 64 == 0 && HD <= 128 && KT % 64 == 0 && KT <= 128 && STAGES >= 2 && STAGES <= 4 && PBUF >= 0 && PBUF <= 2 && SBUF >= 1 && SBUF <= 2 && (PBUF > 0 || SBUF == 2), "geometry");
 };
 
 __device__ int g_fa_error = 0;
@@ -124,6 +125,11 @@ __device__ __forceinline__ void fa_umma(uint32_t tmem_d, uint64_t adesc, uint64_
   asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
                ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
+// the same with A in tensor memory (rows are lanes, 16 bfloat16 of K are 8 columns of two each)
+__device__ __forceinline__ void fa_umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
+               ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
 __device__ __forceinline__ void fa_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -166,6 +172,13 @@ __device__ __forceinline__ void fa_tmem_st32(uint32_t taddr, const float (&r)[32
         "r"(__float_as_uint(r[23])), "r"(__float_as_uint(r[24])), "r"(__float_as_uint(r[25])), "r"(__float_as_uint(r[26])),
         "r"(__float_as_uint(r[27])), "r"(__float_as_uint(r[28])), "r"(__float_as_uint(r[29])), "r"(__float_as_uint(r[30])),
         "r"(__float_as_uint(r[31]))
+      : "memory");
+}
+__device__ __forceinline__ void fa_tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
       : "memory");
 }
 __device__ __forceinline__ float fa_exp2(float x) {
@@ -322,8 +335,12 @@ __global__ void __launch_bounds__(FA_THREADS, Geo<HD, KT, STAGES, PBUF, SBUF>::B
       if (!ok) { atomicExch(&g_fa_error, 5); failed = 1; }
       for (int t = 0; t < n_tiles && ok; ++t) {
         if (failed || !fa_mbar_wait(kv_full0 + 8 * (t % STAGES), (uint32_t)(t / STAGES) & 1u)) { atomicExch(&g_fa_error, 2); failed = 1; break; }
-        // the buffer was read last for tile t - SBUF
-        if (t >= SBUF && !fa_mbar_wait(p_ready0 + 8 * ((t - SBUF) & 1), (uint32_t)((t - SBUF) >> 1) & 1u)) { atomicExch(&g_fa_error, 3); failed = 1; break; }
+        // the buffer was read last for tile t - SBUF: by the softmax, and with P kept in it by the MMAs of that tile
+        if (PBUF > 0) {
+          if (t >= SBUF && !fa_mbar_wait(p_ready0 + 8 * ((t - SBUF) & 1), (uint32_t)((t - SBUF) >> 1) & 1u)) { atomicExch(&g_fa_error, 3); failed = 1; break; }
+        } else {
+          if (t >= 2 && !fa_mbar_wait(pv_done0 + 8 * (t & 1), (uint32_t)((t - 2) >> 1) & 1u)) { atomicExch(&g_fa_error, 3); failed = 1; break; }
+        }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint64_t kd = k_desc + (uint64_t)(((uint32_t)(t % STAGES) * G::KV_STAGE) >> 4);
         const uint32_t d = tmem_s + (uint32_t)((t % SBUF) * KT);
@@ -344,11 +361,19 @@ __global__ void __launch_bounds__(FA_THREADS, Geo<HD, KT, STAGES, PBUF, SBUF>::B
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const int s = j % STAGES;
         const uint64_t vd = v_desc + (uint64_t)(((uint32_t)s * G::KV_STAGE) >> 4);
-        const uint64_t pd = p_desc + (uint64_t)(((uint32_t)(j % PBUF) * G::P_BYTES) >> 4);
+        if (PBUF > 0) {
+          const uint64_t pd = p_desc + (uint64_t)(((uint32_t)(j % (PBUF > 0 ? PBUF : 1)) * G::P_BYTES) >> 4);
 #pragma unroll
-        for (int kk = 0; kk < KT / 16; ++kk)
-          fa_umma(tmem_o, pd + (uint64_t)(((kk >> 2) * ATOM_BYTES + (kk & 3) * 32) >> 4), vd + (uint64_t)((kk * 2048) >> 4),
-                  idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+          for (int kk = 0; kk < KT / 16; ++kk)
+            fa_umma(tmem_o, pd + (uint64_t)(((kk >> 2) * ATOM_BYTES + (kk & 3) * 32) >> 4), vd + (uint64_t)((kk * 2048) >> 4),
+                    idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+        } else {
+          // P of tile j sits in the first KT/2 columns of S buffer j & 1 (two bfloat16 a column)
+          const uint32_t pa = tmem_s + (uint32_t)((j & 1) * KT);
+#pragma unroll
+          for (int kk = 0; kk < KT / 16; ++kk)
+            fa_umma_ts(tmem_o, pa + (uint32_t)(kk * 8), vd + (uint64_t)((kk * 2048) >> 4), idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+        }
         // K of the stage was read by S_j, which was complete before the softmax of tile j read it; V by these
         fa_commit(kv_empty0 + 8 * s);
         fa_commit(pv_done0 + 8 * (j & 1));
@@ -467,13 +492,13 @@ __global__ void __launch_bounds__(FA_THREADS, Geo<HD, KT, STAGES, PBUF, SBUF>::B
       }
       const float ms = m == -INFINITY ? 0.f : m;
       // this tile's P buffer belongs to the MMAs of tile j - PBUF until they are done
-      if (j >= PBUF) {
+      if (PBUF > 0 && j >= PBUF) {
         ok = wait_all(pv_done0 + 8 * ((j - PBUF) & 1), (uint32_t)((j - PBUF) >> 1) & 1u, 6);
         if (!ok) break;
       }
       if (j > 0 && moves) {
         // O belongs to the MMAs of the tile before until they are done
-        if (PBUF > 1) {
+        if (PBUF != 1) {
           ok = wait_all(pv_done0 + 8 * ((j - 1) & 1), (uint32_t)((j - 1) >> 1) & 1u, 6);
           if (!ok) break;
         }
@@ -487,12 +512,14 @@ __global__ void __launch_bounds__(FA_THREADS, Geo<HD, KT, STAGES, PBUF, SBUF>::B
         }
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       }
-      unsigned char* const p_tile = gen_base + G::P_OFF + (uint32_t)(j % PBUF) * G::P_BYTES;
+      unsigned char* const p_tile = gen_base + G::P_OFF + (uint32_t)(j % (PBUF > 0 ? PBUF : 1)) * G::P_BYTES;
+      const uint32_t p_tmem = tmem_s + lane_addr + (uint32_t)((j & 1) * KT);   // PBUF == 0: where this row's P goes
       const uint64_t scale2 = fa_pair(p.scale_log2, p.scale_log2), neg_m2 = fa_pair(-ms, -ms);
       uint64_t sum2a = fa_pair(0.f, 0.f), sum2b = sum2a;
       // exponentials, their sums and P; a tile that needs no mask takes the loop without the comparisons
       auto exp_pass = [&](auto masked) {
         constexpr bool MASKED = decltype(masked)::value;
+        uint32_t pk[16];
         float sc[KT];
 #pragma unroll
         for (int q4 = 0; q4 < KT / 32; ++q4) fa_tmem_ld32_issue(tmem_s + lane_addr + (j % SBUF) * KT + q4 * 32, sc + q4 * 32);
@@ -513,7 +540,13 @@ __global__ void __launch_bounds__(FA_THREADS, Geo<HD, KT, STAGES, PBUF, SBUF>::B
           }
           const int col = ch * 8;                            // key index inside the tile
           const uint4 v = make_uint4(fa_pack(e[0], e[1]), fa_pack(e[2], e[3]), fa_pack(e[4], e[5]), fa_pack(e[6], e[7]));
-          *reinterpret_cast<uint4*>(p_tile + (col >> 6) * ATOM_BYTES + sw128(r, (col & 63) >> 3)) = v;
+          if (PBUF > 0) {
+            *reinterpret_cast<uint4*>(p_tile + (col >> 6) * ATOM_BYTES + sw128(r, (col & 63) >> 3)) = v;
+          } else {
+            // 32 keys (16 columns) at a time into the S buffer's own columns: every score of the tile is in registers
+            pk[(ch & 3) * 4] = v.x; pk[(ch & 3) * 4 + 1] = v.y; pk[(ch & 3) * 4 + 2] = v.z; pk[(ch & 3) * 4 + 3] = v.w;
+            if ((ch & 3) == 3) fa_tmem_st16(p_tmem + (uint32_t)((ch >> 2) * 16), pk);
+          }
         }
       };
       if (interior) exp_pass(std::false_type{});
@@ -542,7 +575,13 @@ __global__ void __launch_bounds__(FA_THREADS, Geo<HD, KT, STAGES, PBUF, SBUF>::B
           }
         }
       }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      if (PBUF > 0) {
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      } else {
+        // P went to tensor memory; shared memory was written only if value rows were cleared (the last tile)
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        if (j == n_tiles - 1) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) fa_mbar_arrive(p_ready0 + 8 * (j & 1));
@@ -682,7 +721,14 @@ extern "C" int ie_attention_tcgen05(const void* q, void* out, const void* kpool,
 #define IE_FA_SBUF64 2
 #endif
   if (hd == 64) return fa_launch<64, IE_FA_KT64, IE_FA_STAGES64, IE_FA_PBUF64, IE_FA_SBUF64>(mk, mv, p, n_work, n_kv_heads, stream);
-  return fa_launch<128, 64, 2, 1, 2>(mk, mv, p, n_work, n_kv_heads, stream);
+  // head size 128: P stays in tensor memory, in the columns of the S buffer it was made from (shared memory has no
+  // room for a second P buffer beside the ring there, and the exponentials of tile j + 1 then need not wait for the
+  // MMAs of tile j either: 8,192 tokens 495 -> 447 us).  At head size 64 the same form (-DIE_FA_PBUF64=0) is no
+  // faster than two P buffers in shared memory (442 us both; 2,048 tokens 40.9 against 39.7 us).
+#ifndef IE_FA_PBUF128
+#define IE_FA_PBUF128 0
+#endif
+  return fa_launch<128, 64, 2, IE_FA_PBUF128, 2>(mk, mv, p, n_work, n_kv_heads, stream);
 }
 
 IE_CHECK_API(attention_tcgen05)
